@@ -1,0 +1,349 @@
+"""Benchmark of the quantized GEMV/GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the Llama-7B layer sweep (W4A16, group 128, asymmetric):
+(N,K) in {(12288,4096) fused QKV, (4096,4096) O, (22016,4096) gate+up, (4096,11008) down}
+x M in {1,4,16}.  One step = one forward of each of the 12 (shape, M) cases.  Every case
+owns its packed weights and two replicas of the whole set (632 MB, 5x the 126 MB L2) are
+alternated between steps, so every launch streams its weights from HBM.
+
+metric / value: achieved GB/s = the reference's algorithmic-bytes model
+(activations + outputs + packed codes + fp16 scales + packed zeros) per step divided by
+the device time per step, inputs resident in HBM, the step replayed as a CUDA graph.
+e2e: the same bytes over the time of calling each case through the host-buffer entry
+(pinned host activations in, host result out, copies and the stream sync inside the
+timed region).  With N > 1 every rank runs its own replica of the sweep (the path has no
+cross-rank exchange; weak scaling) and value is the sum over ranks on the slowest rank's
+time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "qfactory-ae_b200"))
+sys.path.insert(0, ROOT)
+
+SHAPES = [("qkv", 12288, 4096), ("o", 4096, 4096), ("gate_up", 22016, 4096), ("down", 4096, 11008)]
+BATCHES = [1, 4, 16]
+BITS, GS = 4, 128
+METRIC = "w4a16_g128_gemv_achieved_hbm_bandwidth"
+UNIT = "GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over
+# the sweep, from the ncu capture summarised under profiles/ (None until one has been taken)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+WORKLOAD = "llama7b_layer_sweep_w4a16_g128_asym: (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)} x M in {1,4,16}"
+
+
+def algorithmic_bytes(M, N, K, bits=BITS, gs=GS, sym=False):
+    """Footprint model of the reference's bandwidth figures
+    (reference: reproduce/fig9/plot_bandwidth_size.py:37-44)."""
+    b = 2 * (M * K + M * N) + N * K * bits // 8
+    if gs != -1:
+        b += (K // gs) * N * 2
+        if not sym:
+            b += (K // gs) * N * bits // 8
+    return b
+
+
+def step_bytes():
+    return sum(algorithmic_bytes(M, N, K) for _, N, K in SHAPES for M in BATCHES)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_reference(args, rank, world):
+    """The reference's own CPU path for this workload (dequantize, then fp16 matmul, in torch
+    on the host cores), restated in oracle/qf_oracle.py.  Each step is a bounded sample of
+    the sweep: the four layer shapes at M = 1."""
+    if rank != 0:
+        return
+    import torch
+    from oracle import qf_oracle as O
+
+    cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
+    nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
+
+    def one_step():
+        for x, q, s, z in cases:
+            O.qlinear_fp16(x, O.dequant_effective(q, s, O.effective_zero(z.numpy(), BITS)))
+
+    for _ in range(min(args.warmup, 2)):
+        one_step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        one_step()
+        done += 1
+        if time.perf_counter() - t0 > 150:  # keep the arm within a few minutes
+            break
+    dt = (time.perf_counter() - t0) / done
+    val = nbytes / dt / 1e9
+    cores = torch.get_num_threads()
+    sample = f"4 layer shapes at M=1 per step, {done} steps timed"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
+        "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def cpu_baseline_sample(budget_s=12.0):
+    import torch
+    from oracle import qf_oracle as O
+
+    cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
+    nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
+    best, t_start, passes = float("inf"), time.perf_counter(), 0
+    while passes < 2 or (time.perf_counter() - t_start < budget_s and passes < 50):
+        t0 = time.perf_counter()
+        for x, q, s, z in cases:
+            O.qlinear_fp16(x, O.dequant_effective(q, s, O.effective_zero(z.numpy(), BITS)))
+        best = min(best, time.perf_counter() - t0)
+        passes += 1
+    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"dequant + fp16 matmul of the 4 layer shapes at M=1, best of {passes} passes"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--pdl", type=int, default=int(os.environ.get("QFB_BENCH_PDL", "0")))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--per-shape", type=int, default=1)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from qfactory import QLinear, _native
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    _native.lib()  # fail loudly if the native library is missing
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    REPL = 2
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    flags = _native.FLAG_PDL if args.pdl else 0
+
+    def make_layer(N, K):
+        L = QLinear.empty(16, K, N, BITS, GS, sym=False, device=dev)
+        L.w.copy_(torch.randint(-128, 128, L.w.shape, generator=g, dtype=torch.int8, device=dev))
+        L.s.copy_((torch.rand(L.s.shape, generator=g, device=dev) * 0.018 + 0.002).half())
+        L.z.copy_(torch.randint(0, 16, L.z.shape, generator=g, dtype=torch.int8, device=dev))
+        L.flags = flags
+        return L
+
+    cases = []  # replica -> list of (name, M, layer, x_dev, y_dev, x_host, y_host)
+    for rep in range(REPL):
+        row = []
+        for name, N, K in SHAPES:
+            for M in BATCHES:
+                layer = make_layer(N, K)
+                x = torch.randn(M, K, generator=g, device=dev).half()
+                y = torch.empty(M, N, dtype=torch.float16, device=dev)
+                xh = x.cpu().pin_memory()
+                yh = torch.empty(M, N, dtype=torch.float16).pin_memory()
+                row.append((name, M, layer, x, y, xh, yh))
+        cases.append(row)
+    n_cases = len(cases[0])
+
+    def run_step(rep):
+        for _, _, layer, x, y, _, _ in cases[rep]:
+            layer(x, out=y)
+
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for rep in range(REPL):
+            run_step(rep)  # builds descriptors / workspaces outside capture
+        torch.cuda.synchronize()
+        graphs = []
+        for rep in range(REPL):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                run_step(rep)
+            graphs.append(gr)
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for i in range(max(args.warmup, 3)):
+            graphs[i % REPL].replay()
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            graphs[i % REPL].replay()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+
+        # end to end through the host-buffer entry point
+        e2e_steps = max(3, min(args.steps, 50))
+        for i in range(3):
+            for _, _, layer, _, _, xh, yh in cases[i % REPL]:
+                layer.forward_host(xh, yh)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(e2e_steps):
+            for _, _, layer, _, _, xh, yh in cases[i % REPL]:
+                layer.forward_host(xh, yh)
+        f1.record()
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        clocks = sampler.stop() if rank == 0 else None
+
+        # per-case breakdown: single launches timed with events, a 256 MB write between
+        # launches flushes L2 so the weights come from HBM every time
+        per_shape = []
+        if args.per_shape and rank == 0:
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            for ci in range(n_cases):
+                name, M, layer0, *_ = cases[0][ci]
+                N, K = layer0.out_features, layer0.in_features
+                reps = 40
+                evs = []
+                for i in range(reps):
+                    flush.fill_(i & 0xFF)
+                    _, _, layer, x, y, _, _ = cases[i % REPL][ci]
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    layer(x, out=y)
+                    b.record()
+                    evs.append((a, b))
+                torch.cuda.synchronize()
+                ts = sorted(a.elapsed_time(b) for a, b in evs[5:])
+                med = ts[len(ts) // 2]
+                nb = algorithmic_bytes(M, N, K)
+                per_shape.append({"layer": name, "N": N, "K": K, "M": M, "us": round(med * 1e3, 2),
+                                  "GBps": round(nb / (med * 1e-3) / 1e9, 1), "launch": _native.last_launch()})
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        sb = step_bytes()
+        value = sb * args.steps * world / (ms * 1e-3) / 1e9
+        e2e_val = sb * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+        launches = n_cases * args.steps
+        per_launch_s = ms * 1e-3 / launches
+        achieved = (sb / n_cases) / per_launch_s / 1e9
+        h2d = sum(2 * M * K for _, _, K in SHAPES for M in BATCHES)
+        d2h = sum(2 * M * N for _, N, _ in SHAPES for M in BATCHES)
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS, "launches_per_step": n_cases,
+                       "cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
+                       "graph": True, "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches * world,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "gemv_splitk_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                         "avg_launch_us": per_launch_s * 1e6, "traffic": None},
+            "per_shape": per_shape,
+        }
+        out["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

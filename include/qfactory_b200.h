@@ -1,0 +1,144 @@
+/*
+ * qfactory_b200.h -- C ABI of the B200 (sm_100a) weight-only-quantized linear layer.
+ *
+ * Computes  y[M,N] = x[M,K] . dequant(W)[N,K]^T  for 2/3/4/8-bit group-quantized
+ * weights, fp16 activations, fp32 accumulation and fp16 output.
+ *
+ * Conventions (the same as the reference's FFI, whose `launch` symbols these replace):
+ *   - every pointer is a borrowed DEVICE pointer unless its name ends in `_host`;
+ *     the library never allocates or frees device memory in the entry points of this
+ *     section and never synchronises the device unless documented;
+ *   - work is ordered on the cudaStream_t passed as `stream` (NULL = legacy default);
+ *   - every entry point returns a qfb_status (0 = success); nothing is printed.
+ *   - re-entrancy: calls on different streams must use different workspaces.
+ *
+ * Packed layout ("tile-128 interleaved", produced by qfb_pack or by the Python
+ * `qfactory.convert.convert_params`):  rows (output features) are padded to a
+ * multiple of 128 and grouped in tiles of 128; along K the codes are cut in chunks of
+ * 16 bytes per row (128/bits codes; for 3 bits a unit of 128 codes is two 2-bit-plane
+ * chunks followed by one 1-bit-plane chunk).
+ *   qweight  u8 [Npad/128][K chunks][128 rows][16]      one 128-bit load per row and chunk
+ *   scales   f16[Npad/128][K/group ][128 rows]
+ *   zeros    u8 [Npad/128][K/group ][128 rows]          effective zero, see below
+ * Inside a 32-bit word the 2/4-bit fields are pair-interleaved (even elements in the low
+ * half-word, odd ones in the high half-word) so that one LOP3 yields an fp16x2 pair.
+ *
+ * Zero-point semantics follow the reference packer and kernel: the stored, effective
+ * zero is min(z + 1, 2^bits - 1) for GPTQ-convention zeros z
+ * (reference: qfactory/convert.py:76, qfactory/include/utils.h:53-60); symmetric layers
+ * (zeros == NULL) subtract 2^(bits-1) (reference: qfactory/include/gptq_gemv.h:72-73);
+ * group-less layers (scales == NULL, group_size == -1) multiply raw unsigned codes
+ * (reference: qfactory/include/gemv.h:12-94).
+ */
+#ifndef QFACTORY_B200_H_
+#define QFACTORY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum qfb_status {
+  QFB_OK = 0,
+  QFB_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+  QFB_ERR_BAD_SHAPE = 2,      /* M, N, K or group size violate the layout rules */
+  QFB_ERR_UNSUPPORTED = 3,    /* bit width / mode / kernel not available */
+  QFB_ERR_MISALIGNED = 4,     /* a pointer is not 16-byte aligned */
+  QFB_ERR_WORKSPACE = 5,      /* workspace missing or too small */
+  QFB_ERR_CUDA = 6,           /* a CUDA runtime call failed; see qfb_last_cuda_error */
+  QFB_ERR_TOO_LARGE = 7,      /* request exceeds a fixed capacity */
+  QFB_ERR_DEVICE_FLAG = 8     /* a kernel reported a bounded wait that ran out */
+} qfb_status;
+
+/* flags for qfb_linear_forward */
+#define QFB_FLAG_PDL 1u          /* launch with programmatic stream serialisation: the kernel
+                                    prefetches weights before it waits for the preceding kernel */
+#define QFB_FLAG_FORCE_SIMT 2u   /* always use the CUDA-core split-K kernel */
+#define QFB_FLAG_FORCE_TENSOR 4u /* always use the tcgen05 kernel (if the shape allows) */
+
+/* One packed layer.  Plain data; the caller owns the device buffers. */
+typedef struct qfb_layer {
+  const void* qweight;   /* packed codes, 16-byte aligned */
+  const void* scales;    /* packed fp16 scales, or NULL for a group-less layer */
+  const void* zeros;     /* packed effective zeros, or NULL for symmetric / group-less */
+  int32_t n;             /* out_features (unpadded) */
+  int32_t k;             /* in_features */
+  int32_t bits;          /* 2, 3, 4 or 8 */
+  int32_t group_size;    /* multiple of 64 dividing k, or -1 for group-less */
+} qfb_layer;
+
+/* Library / layout version (major*100 + minor). */
+int qfb_version(void);
+const char* qfb_status_string(int status);
+/* cudaError_t of the last failed runtime call seen by this thread (0 if none). */
+int qfb_last_cuda_error(void);
+
+/* Sizes of the packed buffers in bytes (0 on invalid arguments). */
+size_t qfb_packed_weight_bytes(int n, int k, int bits);
+size_t qfb_packed_scale_bytes(int n, int k, int group_size);
+size_t qfb_packed_zero_bytes(int n, int k, int group_size);
+
+/* Bytes of workspace qfb_linear_forward needs for up to m_max activation rows.
+ * The workspace holds split-K partial sums and per-tile arrival counters. */
+size_t qfb_workspace_bytes(int m_max, int n, int k, int bits);
+/* Must be called once on a fresh workspace (zeroes the arrival counters, stream-ordered). */
+int qfb_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The hot path.  Replaces the reference's JIT-emitted
+ *   extern "C" void launch(void* activation, void* weight, void* output, void* scale,
+ *                          void* zero, void* stream, int& __return_code)
+ * (reference: qfactory/core/qfunc.py:140-152, launcher qfactory/include/gptq_gemv.h:156-205)
+ * and, with layer->scales == NULL, its group-less variant
+ *   extern "C" void launch(int m, void* activation, void* weight, void* output,
+ *                          void* stream, int& __return_code)
+ * (reference: qfactory/core/qfunc.py:280-292, launcher qfactory/include/gemv.h:96-135).
+ * Unlike the reference M is a run-time argument.
+ *   x  fp16 [m, k] row-major, 16-byte aligned;  y  fp16 [m, n] row-major.
+ */
+int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y,
+                       void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
+/*
+ * Same computation for callers that hold HOST buffers: copies x_host (pinned or pageable)
+ * into x_staging, runs the layer, copies the result into y_host and synchronises `stream`
+ * before returning.  x_staging / y_staging are caller-owned device buffers of m*k and m*n
+ * fp16 elements.  No counterpart in the reference (its callers hold device tensors).
+ */
+int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host,
+                            void* x_staging, void* y_staging, void* workspace,
+                            size_t workspace_bytes, unsigned flags, void* stream);
+
+/* Which kernel qfb_linear_forward picks: 1 = SIMT split-K GEMV, 2 = tcgen05 GEMM, 0 = invalid. */
+int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags);
+
+/* Debug / tuning override of the split-K heuristic of the SIMT kernel: split_k <= 0 and
+ * k_ways <= 0 restore the built-in choice.  Process-wide, not thread-safe. */
+void qfb_set_gemv_tuning(int split_k, int k_ways);
+/* The configuration the last qfb_linear_forward of this thread used (for reports). */
+void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes);
+
+/*
+ * Offline packer on the device.  Replaces qfactory/convert.py:84-97 (convert_params).
+ *   codes   i32 [k, n]  values in [0, 2^bits)
+ *   scales  f16 [k/group, n]            (NULL for group-less)
+ *   zeros   i32 [k/group, n] GPTQ convention (NULL for symmetric / group-less); the packer
+ *           stores min(z + 1, 2^bits - 1)
+ * Outputs are the three packed buffers described at the top of this file.
+ */
+int qfb_pack(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k,
+             int bits, int group_size, void* qweight_out, void* scales_out, void* zeros_out,
+             void* stream);
+
+/* Inverse of the code packing through the kernels' own bit-extraction path:
+ * writes i32 codes [k, n].  Used by the bit-exactness tests. */
+int qfb_unpack_codes(const qfb_layer* layer, int32_t* codes_out, void* stream);
+/* Dequantised fp16 weight [k, n] = (q - z_eff) * s, through the kernels' decode path. */
+int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QFACTORY_B200_H_ */

@@ -1,0 +1,303 @@
+// C-ABI entry points (see include/qfactory_b200.h): argument validation, kernel choice,
+// split-K heuristics and launches.  No entry point here allocates device memory.
+#include <algorithm>
+#include <cstring>
+
+#include "qfb_common.cuh"
+#include "qfb_kernels.h"
+
+namespace qfb {
+
+constexpr int kNumSMs = 148;
+constexpr size_t kCounterAlign = 256;
+constexpr int kMaxSimtRows = 8;  // activation rows one SIMT launch handles
+
+static thread_local int tl_last_cuda_error = 0;
+static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
+static int g_tune_split = 0, g_tune_kways = 0;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return QFB_OK;
+  tl_last_cuda_error = (int)e;
+  return QFB_ERR_CUDA;
+}
+
+static bool valid_bits(int bits) { return bits == 2 || bits == 3 || bits == 4 || bits == 8; }
+
+static int validate_shape(int n, int k, int bits, int group_size) {
+  if (!valid_bits(bits)) return QFB_ERR_UNSUPPORTED;
+  if (n <= 0 || k <= 0) return QFB_ERR_BAD_SHAPE;
+  if (k % 64 != 0 || k % unit_k(bits) != 0) return QFB_ERR_BAD_SHAPE;
+  if (group_size != -1) {
+    if (group_size <= 0 || group_size % 64 != 0 || k % group_size != 0 || group_size % unit_k(bits) != 0)
+      return QFB_ERR_BAD_SHAPE;
+  }
+  return QFB_OK;
+}
+
+static int make_view(const qfb_layer* L, LayerView* v) {
+  if (!L || !L->qweight) return QFB_ERR_NULL_POINTER;
+  int st = validate_shape(L->n, L->k, L->bits, L->group_size);
+  if (st != QFB_OK) return st;
+  if (L->group_size == -1 && (L->scales || L->zeros)) return QFB_ERR_BAD_SHAPE;
+  if (L->group_size != -1 && !L->scales) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(L->qweight) || !aligned16(L->scales) || !aligned16(L->zeros)) return QFB_ERR_MISALIGNED;
+  v->qw = static_cast<const uint4*>(L->qweight);
+  v->qs = static_cast<const __half*>(L->scales);
+  v->qz = static_cast<const uint8_t*>(L->zeros);
+  v->n = L->n;
+  v->k = L->k;
+  v->bits = L->bits;
+  v->group_size = L->group_size;
+  v->npad = padded_rows(L->n);
+  v->tiles = v->npad / kTileRows;
+  v->units = L->k / unit_k(L->bits);
+  v->groups = L->group_size == -1 ? 1 : L->k / L->group_size;
+  v->units_per_group = v->units / v->groups;
+  // symmetric layers subtract 2^(bits-1); group-less layers use the raw codes
+  v->zconst = (L->group_size == -1) ? 0u : (1u << (L->bits - 1));
+  return QFB_OK;
+}
+
+// Upper bound of the split-K factor for a shape; sizes the workspace.
+static int split_cap(int tiles, int units) {
+  int cap = (kNumSMs * 16 + tiles - 1) / tiles;
+  return std::max(1, std::min(cap, units));
+}
+
+static size_t counters_bytes(int tiles) {
+  return ((size_t)tiles * sizeof(unsigned) + kCounterAlign - 1) / kCounterAlign * kCounterAlign;
+}
+
+struct GemvPlan { int split, kways, mb; size_t smem; };
+
+static GemvPlan plan_gemv(const LayerView& v, int m_rows) {
+  GemvPlan pl;
+  pl.mb = m_rows <= 1 ? 1 : m_rows <= 2 ? 2 : m_rows <= 4 ? 4 : 8;
+  const int uk = unit_k(v.bits);
+  int kways = g_tune_kways > 0 ? g_tune_kways : 2;
+  kways = std::max(1, std::min(kways, 4));
+  // one register batch of units per thread: 8 vectors of 16 bytes in flight
+  const int batch = v.bits == 3 ? 2 : v.bits == 2 ? 4 : 8;
+  int split = g_tune_split > 0 ? g_tune_split : (v.units + batch * kways - 1) / (batch * kways);
+  // keep the staged activation slice of a CTA below 96 KiB
+  const size_t xrow_bytes = (size_t)v.k * 2;
+  const int split_min = (int)((xrow_bytes * pl.mb + 96 * 1024 - 1) / (96 * 1024));
+  split = std::max(split, split_min);
+  split = std::max(1, std::min(split, split_cap(v.tiles, v.units)));
+  while (kways > 1 && v.units / split < kways) --kways;
+  pl.split = split;
+  pl.kways = kways;
+  const int max_units = (v.units + split - 1) / split;
+  const size_t xbytes = (size_t)pl.mb * max_units * uk * 2;
+  const size_t rbytes = (size_t)(kways - 1) * pl.mb * kTileRows * sizeof(float);
+  pl.smem = std::max<size_t>(std::max(xbytes, rbytes), 16);
+  return pl;
+}
+
+static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
+                    unsigned flags, cudaStream_t st) {
+  for (int m0 = 0; m0 < m; m0 += kMaxSimtRows) {
+    const int rows = std::min(kMaxSimtRows, m - m0);
+    const GemvPlan pl = plan_gemv(v, rows);
+    GemvParams p;
+    p.qw = v.qw;
+    p.qs = v.qs;
+    p.qz = v.qz;
+    p.x = x + (size_t)m0 * v.k;
+    p.y = y + (size_t)m0 * v.n;
+    p.m = rows;
+    p.n = v.n;
+    p.k = v.k;
+    p.npad = v.npad;
+    p.units = v.units;
+    p.groups = v.groups;
+    p.units_per_group = v.units_per_group;
+    p.max_units_per_cta = (v.units + pl.split - 1) / pl.split;
+    p.zconst = v.zconst;
+    p.partial = nullptr;
+    p.counters = nullptr;
+    if (pl.split > 1) {
+      const size_t cb = counters_bytes(v.tiles);
+      const size_t need = cb + (size_t)pl.split * rows * v.npad * sizeof(float);
+      if (!workspace || ws_bytes < need) return QFB_ERR_WORKSPACE;
+      p.counters = static_cast<unsigned*>(workspace);
+      p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + cb);
+    }
+    const dim3 grid(pl.split, v.tiles);
+    const int block = kTileRows * pl.kways;
+    tl_last_launch[0] = 1;
+    tl_last_launch[1] = grid.x;
+    tl_last_launch[2] = grid.y;
+    tl_last_launch[3] = block;
+    tl_last_launch[4] = (int)pl.smem;
+    int stt = check_cuda(launch_gemv(p, v.bits, pl.mb, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st));
+    if (stt != QFB_OK) return stt;
+  }
+  return QFB_OK;
+}
+
+}  // namespace qfb
+
+using namespace qfb;
+
+extern "C" {
+
+int qfb_version(void) { return 100; }
+
+const char* qfb_status_string(int s) {
+  switch (s) {
+    case QFB_OK: return "ok";
+    case QFB_ERR_NULL_POINTER: return "null pointer";
+    case QFB_ERR_BAD_SHAPE: return "bad shape";
+    case QFB_ERR_UNSUPPORTED: return "unsupported";
+    case QFB_ERR_MISALIGNED: return "misaligned pointer";
+    case QFB_ERR_WORKSPACE: return "workspace missing or too small";
+    case QFB_ERR_CUDA: return "cuda runtime error";
+    case QFB_ERR_TOO_LARGE: return "request too large";
+    case QFB_ERR_DEVICE_FLAG: return "device-side bounded wait ran out";
+    default: return "unknown status";
+  }
+}
+
+int qfb_last_cuda_error(void) { return tl_last_cuda_error; }
+
+size_t qfb_packed_weight_bytes(int n, int k, int bits) {
+  if (validate_shape(n, k, bits, -1) != QFB_OK) return 0;
+  return (size_t)padded_rows(n) * (k / unit_k(bits)) * unit_vecs(bits) * 16;
+}
+
+size_t qfb_packed_scale_bytes(int n, int k, int group_size) {
+  if (n <= 0 || k <= 0 || group_size <= 0 || k % group_size) return 0;
+  return (size_t)padded_rows(n) * (k / group_size) * 2;
+}
+
+size_t qfb_packed_zero_bytes(int n, int k, int group_size) {
+  if (n <= 0 || k <= 0 || group_size <= 0 || k % group_size) return 0;
+  return (size_t)padded_rows(n) * (k / group_size);
+}
+
+size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
+  if (m_max <= 0 || validate_shape(n, k, bits, -1) != QFB_OK) return 0;
+  const int npad = padded_rows(n);
+  const int tiles = npad / kTileRows;
+  const int rows = std::min(m_max, kMaxSimtRows);
+  return counters_bytes(tiles) + (size_t)split_cap(tiles, k / unit_k(bits)) * rows * npad * sizeof(float);
+}
+
+int qfb_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  const size_t nb = std::min(workspace_bytes, (size_t)1 << 20);
+  return check_cuda(cudaMemsetAsync(workspace, 0, nb, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags) {
+  if (m <= 0 || validate_shape(n, k, bits, -1) != QFB_OK) return 0;
+  (void)flags;
+  return 1;
+}
+
+void qfb_set_gemv_tuning(int split_k, int k_ways) {
+  g_tune_split = split_k;
+  g_tune_kways = k_ways;
+}
+
+void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes) {
+  if (kernel) *kernel = tl_last_launch[0];
+  if (grid_x) *grid_x = tl_last_launch[1];
+  if (grid_y) *grid_y = tl_last_launch[2];
+  if (block) *block = tl_last_launch[3];
+  if (smem_bytes) *smem_bytes = tl_last_launch[4];
+}
+
+int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, void* workspace,
+                       size_t workspace_bytes, unsigned flags, void* stream) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (m < 0) return QFB_ERR_BAD_SHAPE;
+  if (m == 0) return QFB_OK;
+  if (!x || !y) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  return run_gemv(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host, void* x_staging,
+                            void* y_staging, void* workspace, size_t workspace_bytes, unsigned flags,
+                            void* stream) {
+  if (!layer || !x_host || !y_host || !x_staging || !y_staging) return QFB_ERR_NULL_POINTER;
+  if (m <= 0) return m == 0 ? QFB_OK : QFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int s = check_cuda(cudaMemcpyAsync(x_staging, x_host, (size_t)m * layer->k * 2, cudaMemcpyHostToDevice, st));
+  if (s != QFB_OK) return s;
+  s = qfb_linear_forward(layer, x_staging, m, y_staging, workspace, workspace_bytes, flags, stream);
+  if (s != QFB_OK) return s;
+  s = check_cuda(cudaMemcpyAsync(y_host, y_staging, (size_t)m * layer->n * 2, cudaMemcpyDeviceToHost, st));
+  if (s != QFB_OK) return s;
+  return check_cuda(cudaStreamSynchronize(st));
+}
+
+int qfb_pack(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k, int bits,
+             int group_size, void* qweight_out, void* scales_out, void* zeros_out, void* stream) {
+  int st = validate_shape(n, k, bits, group_size);
+  if (st != QFB_OK) return st;
+  if (!codes || !qweight_out) return QFB_ERR_NULL_POINTER;
+  if (group_size != -1 && (!scales || !scales_out)) return QFB_ERR_NULL_POINTER;
+  if (group_size == -1 && (scales || zeros)) return QFB_ERR_BAD_SHAPE;
+  if (zeros && !zeros_out) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(qweight_out) || !aligned16(scales_out) || !aligned16(zeros_out)) return QFB_ERR_MISALIGNED;
+  PackParams p;
+  p.codes = codes;
+  p.scales = static_cast<const __half*>(scales);
+  p.zeros = zeros;
+  p.qw = static_cast<uint32_t*>(qweight_out);
+  p.qs = group_size == -1 ? nullptr : static_cast<__half*>(scales_out);
+  p.qz = zeros ? static_cast<uint8_t*>(zeros_out) : nullptr;
+  p.n = n;
+  p.k = k;
+  p.bits = bits;
+  p.group_size = group_size;
+  p.npad = padded_rows(n);
+  p.tiles = p.npad / kTileRows;
+  p.units = k / unit_k(bits);
+  p.groups = group_size == -1 ? 1 : k / group_size;
+  return check_cuda(launch_pack(p, static_cast<cudaStream_t>(stream)));
+}
+
+static int run_unpack(const qfb_layer* layer, int32_t* codes_out, void* w_out, void* stream) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  UnpackParams p;
+  p.qw = v.qw;
+  p.qs = v.qs;
+  p.qz = v.qz;
+  p.codes_out = codes_out;
+  p.w_out = static_cast<__half*>(w_out);
+  p.n = v.n;
+  p.k = v.k;
+  p.bits = v.bits;
+  p.npad = v.npad;
+  p.tiles = v.tiles;
+  p.units = v.units;
+  p.groups = v.groups;
+  p.units_per_group = v.units_per_group;
+  p.zconst = v.zconst;
+  return check_cuda(launch_unpack(p, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_unpack_codes(const qfb_layer* layer, int32_t* codes_out, void* stream) {
+  if (!codes_out) return QFB_ERR_NULL_POINTER;
+  return run_unpack(layer, codes_out, nullptr, stream);
+}
+
+int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream) {
+  if (!w_out) return QFB_ERR_NULL_POINTER;
+  return run_unpack(layer, nullptr, w_out, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,197 @@
+// Shared device helpers: packed-layout geometry, streaming loads and the in-register
+// code extraction (LOP3 / PRMT magic-number trick) used by every kernel of the library.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/qfactory_b200.h"
+
+namespace qfb {
+
+constexpr int kTileRows = 128;  // rows (output features) per packed tile
+
+// ---------------------------------------------------------------------------
+// Geometry of the packed layout per bit width.  A "unit" is the smallest run of
+// codes along K one row decodes at a time: one 16-byte vector for 2/4/8 bits,
+// three vectors (two 2-bit-plane chunks + one 1-bit-plane chunk) for 3 bits.
+// ---------------------------------------------------------------------------
+template <int BITS> struct Geo;
+template <> struct Geo<8> { static constexpr int kUnitK = 16, kUnitVecs = 1; };
+template <> struct Geo<4> { static constexpr int kUnitK = 32, kUnitVecs = 1; };
+template <> struct Geo<2> { static constexpr int kUnitK = 64, kUnitVecs = 1; };
+template <> struct Geo<3> { static constexpr int kUnitK = 128, kUnitVecs = 3; };
+
+__host__ __device__ inline int unit_k(int bits) { return bits == 8 ? 16 : bits == 4 ? 32 : bits == 2 ? 64 : 128; }
+__host__ __device__ inline int unit_vecs(int bits) { return bits == 3 ? 3 : 1; }
+__host__ __device__ inline int padded_rows(int n) { return (n + kTileRows - 1) / kTileRows * kTileRows; }
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// (a & b) | c
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// a | (b & c)
+__device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xF8;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+// Programmatic dependent launch: both are no-ops when the grid was launched without
+// the programmatic-stream-serialisation attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Code extraction.  Every decoder produces fp16x2 pairs holding (q - z) EXACTLY:
+// a field is OR-ed into the mantissa of a power-of-two "magic" half whose unit in
+// the last place lines up with the field's bit offset, giving magic + q, and the
+// zero-point is subtracted as magic + z.  Both are exactly representable, so the
+// difference is exact (this is the reference's own trick, qfactory/include/utils.h:
+// 11-25,46-62, extended to un-shifted fields at several bit offsets).
+//
+// zmagic(z) builds the per-group subtrahends; decode8(...) hands the caller four
+// fp16x2 values = eight consecutive codes along K.
+// ---------------------------------------------------------------------------
+template <int BITS> struct Codec;
+
+template <> struct Codec<4> {
+  struct ZM { uint32_t lo, hi; };
+  __device__ static __forceinline__ ZM zmagic(uint32_t z) {
+    uint32_t zz = z * 0x00010001u;
+    return {0x64006400u | zz, 0x54005400u | (zz << 4)};
+  }
+  // word -> 8 codes (4 pairs).  nibble p of the word holds element (p<4 ? 2p : 2(p-4)+1).
+  __device__ static __forceinline__ void word(uint32_t w, const ZM& zm, __half2 (&d)[4]) {
+    uint32_t t = w >> 8;
+    d[0] = __hsub2(as_h2(lop3_and_or(w, 0x000f000fu, 0x64006400u)), as_h2(zm.lo));
+    d[1] = __hsub2(as_h2(lop3_and_or(w, 0x00f000f0u, 0x54005400u)), as_h2(zm.hi));
+    d[2] = __hsub2(as_h2(lop3_and_or(t, 0x000f000fu, 0x64006400u)), as_h2(zm.lo));
+    d[3] = __hsub2(as_h2(lop3_and_or(t, 0x00f000f0u, 0x54005400u)), as_h2(zm.hi));
+  }
+  // f(j8, d[4]) for each group of 8 codes of the unit, in K order
+  template <class F> __device__ static __forceinline__ void unit(const uint4* v, const ZM& zm, F&& f) {
+    const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 d[4];
+      word(w[j], zm, d);
+      f(j, d);
+    }
+  }
+};
+
+template <> struct Codec<8> {
+  struct ZM { uint32_t m; };
+  __device__ static __forceinline__ ZM zmagic(uint32_t z) { return {0x64006400u | (z * 0x00010001u)}; }
+  template <class F> __device__ static __forceinline__ void unit(const uint4* v, const ZM& zm, F&& f) {
+    const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      __half2 d[4];
+      d[0] = __hsub2(as_h2(prmt(w[2 * j], 0x64646464u, 0x4140u)), as_h2(zm.m));
+      d[1] = __hsub2(as_h2(prmt(w[2 * j], 0x64646464u, 0x4342u)), as_h2(zm.m));
+      d[2] = __hsub2(as_h2(prmt(w[2 * j + 1], 0x64646464u, 0x4140u)), as_h2(zm.m));
+      d[3] = __hsub2(as_h2(prmt(w[2 * j + 1], 0x64646464u, 0x4342u)), as_h2(zm.m));
+      f(j, d);
+    }
+  }
+};
+
+template <> struct Codec<2> {
+  struct ZM { uint32_t m[4]; };
+  __device__ static __forceinline__ ZM zmagic(uint32_t z) {
+    uint32_t zz = z * 0x00010001u;
+    return {{0x64006400u | zz, 0x5C005C00u | (zz << 2), 0x54005400u | (zz << 4), 0x4C004C00u | (zz << 6)}};
+  }
+  // 2-bit field f (bit offset 2f, f < 8) holds element 2f, the field 16 bits above it 2f+1
+  __device__ static __forceinline__ void half_word(uint32_t w, const ZM& zm, __half2 (&d)[4]) {
+    d[0] = __hsub2(as_h2(lop3_and_or(w, 0x00030003u, 0x64006400u)), as_h2(zm.m[0]));
+    d[1] = __hsub2(as_h2(lop3_and_or(w, 0x000c000cu, 0x5C005C00u)), as_h2(zm.m[1]));
+    d[2] = __hsub2(as_h2(lop3_and_or(w, 0x00300030u, 0x54005400u)), as_h2(zm.m[2]));
+    d[3] = __hsub2(as_h2(lop3_and_or(w, 0x00c000c0u, 0x4C004C00u)), as_h2(zm.m[3]));
+  }
+  template <class F> __device__ static __forceinline__ void unit(const uint4* v, const ZM& zm, F&& f) {
+    const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2 d[4];
+      half_word(w[j], zm, d);
+      f(2 * j, d);
+      half_word(w[j] >> 8, zm, d);
+      f(2 * j + 1, d);
+    }
+  }
+};
+
+// 3 bits = a 2-bit plane (low bits, laid out exactly like the 2-bit format) plus a 1-bit
+// plane whose bits are placed so that a single shift of the plane word lines the high bit
+// up with bit (o + 2) of the 2-bit field at offset o: v[0], v[1] are the two 2-bit chunks
+// (codes 0..63, 64..127 of the unit) and v[2] the 1-bit chunk (word j covers codes 32j..).
+template <> struct Codec<3> {
+  using ZM = Codec<2>::ZM;
+  __device__ static __forceinline__ ZM zmagic(uint32_t z) { return Codec<2>::zmagic(z); }
+  __device__ static __forceinline__ void half_word(uint32_t a, uint32_t b, const ZM& zm, __half2 (&d)[4]) {
+    d[0] = __hsub2(as_h2(lop3_or_and(lop3_and_or(a, 0x00030003u, 0x64006400u), b, 0x00040004u)), as_h2(zm.m[0]));
+    d[1] = __hsub2(as_h2(lop3_or_and(lop3_and_or(a, 0x000c000cu, 0x5C005C00u), b, 0x00100010u)), as_h2(zm.m[1]));
+    d[2] = __hsub2(as_h2(lop3_or_and(lop3_and_or(a, 0x00300030u, 0x54005400u), b, 0x00400040u)), as_h2(zm.m[2]));
+    d[3] = __hsub2(as_h2(lop3_or_and(lop3_and_or(a, 0x00c000c0u, 0x4C004C00u), b, 0x01000100u)), as_h2(zm.m[3]));
+  }
+  template <class F> __device__ static __forceinline__ void unit(const uint4* v, const ZM& zm, F&& f) {
+    const uint32_t a[8] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w};
+    const uint32_t b[4] = {v[2].x, v[2].y, v[2].z, v[2].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // 32 codes: 2-bit words a[2j], a[2j+1] with plane word b[j]
+      __half2 d[4];
+      half_word(a[2 * j], b[j] << 2, zm, d);
+      f(4 * j, d);
+      half_word(a[2 * j] >> 8, b[j] << 1, zm, d);
+      f(4 * j + 1, d);
+      half_word(a[2 * j + 1], b[j] >> 6, zm, d);
+      f(4 * j + 2, d);
+      half_word(a[2 * j + 1] >> 8, b[j] >> 7, zm, d);
+      f(4 * j + 3, d);
+    }
+  }
+};
+
+// Host-visible description of a validated layer (filled by the API layer).
+struct LayerView {
+  const uint4* qw;
+  const __half* qs;     // may be null (group-less)
+  const uint8_t* qz;    // may be null (symmetric / group-less)
+  int n, k, bits, group_size;
+  int npad, tiles, units, groups, units_per_group;
+  uint32_t zconst;      // zero used when qz == null
+};
+
+}  // namespace qfb

@@ -1,0 +1,51 @@
+// Internal launch interfaces between the C-ABI layer and the kernel translation units.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qfb {
+
+struct GemvParams {
+  const uint4* qw;
+  const __half* qs;      // null: scale 1 (group-less)
+  const uint8_t* qz;     // null: zconst
+  const __half* x;       // [m, k]
+  __half* y;             // [m, n]
+  float* partial;        // [S, m, npad] split-K partial sums
+  unsigned* counters;    // [tiles] arrival counters, zero between launches
+  int m, n, k, npad;
+  int units;             // K / unit_k(bits)
+  int groups;            // K / group_size (1 when group-less)
+  int units_per_group;
+  int max_units_per_cta; // ceil(units / S)
+  uint32_t zconst;
+};
+
+cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int block, size_t smem, bool pdl,
+                        cudaStream_t st);
+
+struct PackParams {
+  const int32_t* codes;   // [k, n]
+  const __half* scales;   // [groups, n] or null
+  const int32_t* zeros;   // [groups, n] or null
+  uint32_t* qw;           // packed words
+  __half* qs;
+  uint8_t* qz;
+  int n, k, bits, group_size, npad, tiles, units, groups;
+};
+cudaError_t launch_pack(const PackParams& p, cudaStream_t st);
+
+struct UnpackParams {
+  const uint4* qw;
+  const __half* qs;
+  const uint8_t* qz;
+  int32_t* codes_out;   // [k, n] or null
+  __half* w_out;        // [k, n] or null
+  int n, k, bits, npad, tiles, units, groups, units_per_group;
+  uint32_t zconst;
+};
+cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st);
+
+}  // namespace qfb

@@ -1,0 +1,159 @@
+// Offline packer (replaces qfactory/convert.py:55-81 of the reference) and its inverse.
+//
+// The packer turns GPTQ-style tensors -- int32 codes [K,N], fp16 scales [K/GS,N], int32
+// zeros [K/GS,N] -- into the tile-128 interleaved layout described in qfactory_b200.h.
+// The inverse kernels run the SAME Codec<> bit extraction the compute kernels use, so a
+// pack -> unpack round trip proves the in-kernel decode bit-exact.
+#include "qfb_common.cuh"
+#include "qfb_kernels.h"
+
+namespace qfb {
+
+// element held by field f of a 2/4/8-bit word (pair interleave: even elements low half)
+__device__ __forceinline__ int field_element(int bits, int f) {
+  if (bits == 8) return f;
+  const int half_fields = 16 / bits;
+  return f < half_fields ? 2 * f : 2 * (f - half_fields) + 1;
+}
+
+// bit position of element e (0..31) inside a word of the 3-bit format's 1-bit plane
+__device__ __forceinline__ int plane1_bit(int e) {
+  const int h = e >> 4, el = e & 15, f = el >> 1, parity = el & 1;
+  const int variant = 2 * h + (f >> 2);
+  const int base = (variant == 0) ? 0 : (variant == 1) ? 1 : (variant == 2) ? 8 : 9;
+  return base + 2 * (f & 3) + 16 * parity;
+}
+
+__global__ void pack_weight_kernel(const PackParams p) {
+  const int nv = unit_vecs(p.bits);
+  const long long total = (long long)p.tiles * p.units * nv * 4 * kTileRows;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int r = (int)(idx % kTileRows);
+  long long t = idx / kTileRows;
+  const int j = (int)(t % 4); t /= 4;
+  const int v = (int)(t % nv); t /= nv;
+  const int unit = (int)(t % p.units);
+  const int tile = (int)(t / p.units);
+  const int n = tile * kTileRows + r;
+  const int uk = unit_k(p.bits);
+  uint32_t word = 0;
+  if (n < p.n) {
+    if (p.bits != 3) {
+      const int pf = 32 / p.bits;
+      const int k0 = unit * uk + j * pf;
+      for (int f = 0; f < pf; ++f) {
+        const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + field_element(p.bits, f)) * p.n + n];
+        word |= (q & ((1u << p.bits) - 1u)) << (f * p.bits);
+      }
+    } else if (v < 2) {  // 2-bit plane: low two bits of 16 codes
+      const int k0 = unit * uk + v * 64 + j * 16;
+      for (int f = 0; f < 16; ++f) {
+        const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + field_element(2, f)) * p.n + n];
+        word |= (q & 3u) << (f * 2);
+      }
+    } else {  // 1-bit plane: bit 2 of 32 codes
+      const int k0 = unit * uk + j * 32;
+      for (int e = 0; e < 32; ++e) {
+        const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + e) * p.n + n];
+        word |= ((q >> 2) & 1u) << plane1_bit(e);
+      }
+    }
+  }
+  p.qw[((((size_t)tile * p.units + unit) * nv + v) * kTileRows + r) * 4 + j] = word;
+}
+
+__global__ void pack_scale_zero_kernel(const PackParams p) {
+  const long long total = (long long)p.tiles * p.groups * kTileRows;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int r = (int)(idx % kTileRows);
+  const int g = (int)((idx / kTileRows) % p.groups);
+  const int tile = (int)(idx / ((long long)kTileRows * p.groups));
+  const int n = tile * kTileRows + r;
+  if (p.qs) p.qs[idx] = (n < p.n) ? p.scales[(size_t)g * p.n + n] : __ushort_as_half(0);
+  if (p.qz) {
+    int z = 0;
+    if (n < p.n) {
+      z = p.zeros[(size_t)g * p.n + n] + 1;  // GPTQ "zero - 1" convention, clamped like the reference packer
+      const int zmax = (1 << p.bits) - 1;
+      z = z > zmax ? zmax : z;
+    }
+    p.qz[idx] = (uint8_t)z;
+  }
+}
+
+cudaError_t launch_pack(const PackParams& p, cudaStream_t st) {
+  const int nv = unit_vecs(p.bits);
+  const long long total = (long long)p.tiles * p.units * nv * 4 * kTileRows;
+  const int block = 256;
+  pack_weight_kernel<<<(unsigned)((total + block - 1) / block), block, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (p.qs || p.qz) {
+    const long long t2 = (long long)p.tiles * p.groups * kTileRows;
+    pack_scale_zero_kernel<<<(unsigned)((t2 + block - 1) / block), block, 0, st>>>(p);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+template <int BITS>
+__global__ void unpack_kernel(const UnpackParams p) {
+  using G = Geo<BITS>;
+  using C = Codec<BITS>;
+  const long long total = (long long)p.tiles * p.units * kTileRows;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int r = (int)(idx % kTileRows);
+  const int unit = (int)((idx / kTileRows) % p.units);
+  const int tile = (int)(idx / ((long long)kTileRows * p.units));
+  const int n = tile * kTileRows + r;
+  if (n >= p.n) return;
+  uint4 v[G::kUnitVecs];
+#pragma unroll
+  for (int i = 0; i < G::kUnitVecs; ++i)
+    v[i] = ldg_stream_v4(p.qw + (((size_t)tile * p.units + unit) * G::kUnitVecs + i) * kTileRows + r);
+  const int k0 = unit * G::kUnitK;
+  if (p.codes_out) {
+    const typename C::ZM zm = C::zmagic(0);
+    C::unit(v, zm, [&](int j8, __half2(&d)[4]) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(d[i]);
+        p.codes_out[(size_t)(k0 + j8 * 8 + 2 * i) * p.n + n] = (int32_t)f.x;
+        p.codes_out[(size_t)(k0 + j8 * 8 + 2 * i + 1) * p.n + n] = (int32_t)f.y;
+      }
+    });
+  }
+  if (p.w_out) {
+    const int g = unit / p.units_per_group;
+    const size_t sz = ((size_t)tile * p.groups + g) * kTileRows + r;
+    const __half2 s2 = __half2half2(p.qs ? p.qs[sz] : __ushort_as_half(0x3C00));
+    const typename C::ZM zm = C::zmagic(p.qz ? (uint32_t)p.qz[sz] : p.zconst);
+    C::unit(v, zm, [&](int j8, __half2(&d)[4]) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __half2 w = __hmul2(d[i], s2);
+        p.w_out[(size_t)(k0 + j8 * 8 + 2 * i) * p.n + n] = __low2half(w);
+        p.w_out[(size_t)(k0 + j8 * 8 + 2 * i + 1) * p.n + n] = __high2half(w);
+      }
+    });
+  }
+}
+
+cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st) {
+  const long long total = (long long)p.tiles * p.units * kTileRows;
+  const int block = 128;
+  const unsigned grid = (unsigned)((total + block - 1) / block);
+  switch (p.bits) {
+    case 2: unpack_kernel<2><<<grid, block, 0, st>>>(p); break;
+    case 3: unpack_kernel<3><<<grid, block, 0, st>>>(p); break;
+    case 4: unpack_kernel<4><<<grid, block, 0, st>>>(p); break;
+    case 8: unpack_kernel<8><<<grid, block, 0, st>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace qfb

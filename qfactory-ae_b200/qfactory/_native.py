@@ -1,0 +1,107 @@
+"""ctypes binding of the native library (lib/libqfactory_b200.so, C ABI in
+include/qfactory_b200.h).
+
+The reference binds its JIT-built kernels the same way: `ctypes.CDLL(...).launch` with
+`c_void_p` tensor pointers (reference: qfactory/jit/runtime.py:22-49).  There is no
+Python or CPU fallback: if the library is missing, `lib()` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_ROOT, "lib", "libqfactory_b200.so")
+
+QFB_OK = 0
+FLAG_PDL = 1
+FLAG_FORCE_SIMT = 2
+FLAG_FORCE_TENSOR = 4
+
+EXPORTS = (
+    "qfb_version", "qfb_status_string", "qfb_last_cuda_error",
+    "qfb_packed_weight_bytes", "qfb_packed_scale_bytes", "qfb_packed_zero_bytes",
+    "qfb_workspace_bytes", "qfb_workspace_init",
+    "qfb_linear_forward", "qfb_linear_forward_host", "qfb_select_kernel",
+    "qfb_set_gemv_tuning", "qfb_get_last_launch",
+    "qfb_pack", "qfb_unpack_codes", "qfb_dequantize",
+)
+
+
+class QfbLayer(ctypes.Structure):
+    """Mirror of `struct qfb_layer`."""
+
+    _fields_ = [
+        ("qweight", ctypes.c_void_p),
+        ("scales", ctypes.c_void_p),
+        ("zeros", ctypes.c_void_p),
+        ("n", ctypes.c_int32),
+        ("k", ctypes.c_int32),
+        ("bits", ctypes.c_int32),
+        ("group_size", ctypes.c_int32),
+    ]
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the native library once; raise loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NativeError(
+            f"native library {LIB_PATH} not found: build it with "
+            f"`python {os.path.join(_PKG_ROOT, 'build.py')}` (needs nvcc); there is no fallback path"
+        )
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i32, u32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
+    LP = ctypes.POINTER(QfbLayer)
+    L.qfb_version.restype = i32
+    L.qfb_status_string.restype = ctypes.c_char_p
+    L.qfb_status_string.argtypes = [i32]
+    L.qfb_last_cuda_error.restype = i32
+    for f in (L.qfb_packed_weight_bytes, L.qfb_packed_scale_bytes, L.qfb_packed_zero_bytes):
+        f.restype = sz
+        f.argtypes = [i32, i32, i32]
+    L.qfb_workspace_bytes.restype = sz
+    L.qfb_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    L.qfb_workspace_init.restype = i32
+    L.qfb_workspace_init.argtypes = [vp, sz, vp]
+    L.qfb_linear_forward.restype = i32
+    L.qfb_linear_forward.argtypes = [LP, vp, i32, vp, vp, sz, u32, vp]
+    L.qfb_linear_forward_host.restype = i32
+    L.qfb_linear_forward_host.argtypes = [LP, vp, i32, vp, vp, vp, vp, sz, u32, vp]
+    L.qfb_select_kernel.restype = i32
+    L.qfb_select_kernel.argtypes = [i32, i32, i32, i32, u32]
+    L.qfb_set_gemv_tuning.restype = None
+    L.qfb_set_gemv_tuning.argtypes = [i32, i32]
+    L.qfb_get_last_launch.restype = None
+    L.qfb_get_last_launch.argtypes = [ctypes.POINTER(i32)] * 5
+    L.qfb_pack.restype = i32
+    L.qfb_pack.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.qfb_unpack_codes.restype = i32
+    L.qfb_unpack_codes.argtypes = [LP, vp, vp]
+    L.qfb_dequantize.restype = i32
+    L.qfb_dequantize.argtypes = [LP, vp, vp]
+    _lib = L
+    return L
+
+
+def check(status: int, what: str = "qfactory_b200") -> None:
+    if status != QFB_OK:
+        L = lib()
+        msg = L.qfb_status_string(status).decode()
+        extra = f" (cudaError {L.qfb_last_cuda_error()})" if status == 6 else ""
+        raise NativeError(f"{what}: {msg}{extra}")
+
+
+def last_launch() -> dict:
+    v = [ctypes.c_int(0) for _ in range(5)]
+    lib().qfb_get_last_launch(*[ctypes.byref(x) for x in v])
+    return dict(zip(("kernel", "grid_x", "grid_y", "block", "smem"), (x.value for x in v)))

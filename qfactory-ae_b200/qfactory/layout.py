@@ -1,0 +1,178 @@
+"""The packed "tile-128 interleaved" layout, in vectorised torch (any device).
+
+Layout (the same one `qfb_pack` in the native library writes; see
+include/qfactory_b200.h): rows = output features, padded to a multiple of 128 and cut in
+tiles of 128; along K a row is cut in 16-byte vectors (128/bits codes; for 3 bits a unit
+of 128 codes = two 2-bit-plane vectors + one 1-bit-plane vector).
+
+    qweight  u8 [tiles][vectors along K][128 rows][16]
+    scales   f16[tiles][K/group][128 rows]
+    zeros    u8 [tiles][K/group][128 rows]      effective zero min(z+1, 2^b-1)
+
+This replaces the reference's N-major layout (reference: qfactory/convert.py:55-81); the
+intra-word field order of the 2/4/8-bit formats is the reference's PERMUTE_ORDER
+(qfactory/convert.py:49-53), which is what makes one LOP3 yield an fp16x2 pair.
+"""
+from __future__ import annotations
+
+import torch
+
+TILE = 128
+
+
+def unit_k(bits: int) -> int:
+    return {8: 16, 4: 32, 2: 64, 3: 128}[bits]
+
+
+def unit_vecs(bits: int) -> int:
+    return 3 if bits == 3 else 1
+
+
+def padded_rows(n: int) -> int:
+    return (n + TILE - 1) // TILE * TILE
+
+
+def check_shape(N: int, K: int, bits: int, GS: int) -> None:
+    if bits not in (2, 3, 4, 8):
+        raise ValueError(f"unsupported bit width {bits}")
+    assert K % 64 == 0 and K % unit_k(bits) == 0, f"K={K} must be a multiple of 64 and of {unit_k(bits)}"
+    if GS != -1:
+        assert GS > 0 and GS % 64 == 0 and K % GS == 0 and GS % unit_k(bits) == 0, \
+            f"group size {GS} must be a multiple of 64 (128 for 3-bit) dividing K={K}"
+
+
+def field_elements(bits: int) -> list[int]:
+    """Element held by field f of a 32-bit word (pair interleave for 2/4-bit)."""
+    pf = 32 // bits
+    if bits == 8:
+        return list(range(pf))
+    return list(range(0, pf, 2)) + list(range(1, pf, 2))
+
+
+def plane1_bit(e: int) -> int:
+    """Bit of element e (0..31) in a word of the 3-bit format's 1-bit plane."""
+    h, el = e >> 4, e & 15
+    f, parity = el >> 1, el & 1
+    base = (0, 1, 8, 9)[2 * h + (f >> 2)]
+    return base + 2 * (f & 3) + 16 * parity
+
+
+def _words_to_bytes(words: torch.Tensor) -> torch.Tensor:
+    sh = torch.arange(4, device=words.device, dtype=torch.int64) * 8
+    return ((words.unsqueeze(-1) >> sh) & 0xFF).to(torch.uint8)
+
+
+def _bytes_to_words(b: torch.Tensor) -> torch.Tensor:
+    sh = torch.arange(4, device=b.device, dtype=torch.int64) * 8
+    return (b.to(torch.int64) << sh).sum(-1)
+
+
+def _pack_fields(v: torch.Tensor, bits: int) -> torch.Tensor:
+    """v int64 [..., 32/bits] elements of one word in K order -> int64 words [...]."""
+    order = torch.tensor(field_elements(bits), device=v.device)
+    sh = torch.arange(32 // bits, device=v.device, dtype=torch.int64) * bits
+    return (v[..., order] << sh).sum(-1)
+
+
+def _unpack_fields(words: torch.Tensor, bits: int) -> torch.Tensor:
+    pf = 32 // bits
+    sh = torch.arange(pf, device=words.device, dtype=torch.int64) * bits
+    fields = (words.unsqueeze(-1) >> sh) & ((1 << bits) - 1)
+    out = torch.empty_like(fields)
+    out[..., torch.tensor(field_elements(bits), device=words.device)] = fields
+    return out
+
+
+def _rows_per_batch(K: int) -> int:
+    return max(TILE, (1 << 24) // K // TILE * TILE)
+
+
+def pack_weight(q: torch.Tensor, bits: int) -> torch.Tensor:
+    """int32 codes [K, N] -> int8 [Npad, K*bits/8] (flat tile-128 layout)."""
+    K, N = q.shape
+    Np = padded_rows(N)
+    uk, nv = unit_k(bits), unit_vecs(bits)
+    units = K // uk
+    out = torch.empty(Np // TILE, units * nv, TILE, 16, dtype=torch.uint8, device=q.device)
+    step = _rows_per_batch(K)
+    for r0 in range(0, Np, step):
+        r1 = min(Np, r0 + step)
+        blk = torch.zeros(r1 - r0, K, dtype=torch.int64, device=q.device)
+        n1 = min(r1, N)
+        if n1 > r0:
+            blk[: n1 - r0] = q[:, r0:n1].t()
+        T = (r1 - r0) // TILE
+        if bits != 3:
+            words = _pack_fields(blk.view(T, TILE, units, 4, 32 // bits), bits)  # [T,128,units,4]
+            by = _words_to_bytes(words).view(T, TILE, units, 16)
+            out[r0 // TILE : r1 // TILE] = by.permute(0, 2, 1, 3)
+        else:
+            lo = _pack_fields((blk & 3).view(T, TILE, units, 2, 4, 16), 2)  # [T,128,units,2,4]
+            pos = torch.tensor([plane1_bit(e) for e in range(32)], device=q.device, dtype=torch.int64)
+            hi = ((((blk >> 2) & 1).view(T, TILE, units, 4, 32)) << pos).sum(-1)  # [T,128,units,4]
+            by = torch.cat([_words_to_bytes(lo).view(T, TILE, units, 2, 16),
+                            _words_to_bytes(hi).view(T, TILE, units, 1, 16)], dim=3)  # [T,128,units,3,16]
+            out[r0 // TILE : r1 // TILE] = by.permute(0, 2, 3, 1, 4).reshape(T, units * 3, TILE, 16)
+    return out.view(Np, K * bits // 8).view(torch.int8)
+
+
+def unpack_weight(w: torch.Tensor, N: int, K: int, bits: int) -> torch.Tensor:
+    """Inverse of pack_weight: int8 [Npad, K*bits/8] -> int32 codes [K, N]."""
+    Np = padded_rows(N)
+    uk, nv = unit_k(bits), unit_vecs(bits)
+    units = K // uk
+    T = Np // TILE
+    b = w.contiguous().view(torch.uint8).view(T, units, nv, TILE, 16)
+    if bits != 3:
+        words = _bytes_to_words(b.view(T, units, TILE, 4, 4))
+        q = _unpack_fields(words, bits)  # [T,units,128,4,pf]
+        q = q.permute(0, 2, 1, 3, 4).reshape(Np, K)
+    else:
+        lo = _unpack_fields(_bytes_to_words(b[:, :, :2].reshape(T, units, 2, TILE, 4, 4)), 2)  # [T,u,2,128,4,16]
+        lo = lo.permute(0, 3, 1, 2, 4, 5).reshape(Np, K)
+        hw = _bytes_to_words(b[:, :, 2].reshape(T, units, TILE, 4, 4))  # [T,u,128,4]
+        pos = torch.tensor([plane1_bit(e) for e in range(32)], device=w.device, dtype=torch.int64)
+        hi = ((hw.unsqueeze(-1) >> pos) & 1).permute(0, 2, 1, 3, 4).reshape(Np, K)
+        q = lo | (hi << 2)
+    return q[:N].t().contiguous().to(torch.int32)
+
+
+def _tile_major(a: torch.Tensor, N: int) -> torch.Tensor:
+    """[G, N] -> [tiles, G, 128] with zero padding of the rows."""
+    G = a.shape[0]
+    Np = padded_rows(N)
+    buf = torch.zeros(Np, G, dtype=a.dtype, device=a.device)
+    buf[:N] = a.t()
+    return buf.view(Np // TILE, TILE, G).permute(0, 2, 1).contiguous()
+
+
+def pack_scale(s: torch.Tensor) -> torch.Tensor:
+    """fp16 [G, N] -> fp16 [Npad, G] (flat [tiles][G][128])."""
+    G, N = s.shape
+    return _tile_major(s, N).view(padded_rows(N), G)
+
+
+def effective_zero(z: torch.Tensor, bits: int) -> torch.Tensor:
+    """GPTQ-convention zero -> the value the kernel subtracts: min(z+1, 2^b-1)
+    (reference: qfactory/convert.py:76)."""
+    return (z + 1).clamp(max=(1 << bits) - 1)
+
+
+def pack_zero(z: torch.Tensor, bits: int) -> torch.Tensor:
+    """int32 GPTQ zeros [G, N] -> int8 [Npad, G] holding the effective zero per byte."""
+    G, N = z.shape
+    ze = effective_zero(z, bits).to(torch.uint8)
+    return _tile_major(ze, N).view(padded_rows(N), G).view(torch.int8)
+
+
+def unpack_scale(s: torch.Tensor, N: int) -> torch.Tensor:
+    """fp16 [Npad, G] packed -> fp16 [G, N]."""
+    Np, G = s.shape
+    return s.contiguous().view(Np // TILE, G, TILE).permute(1, 0, 2).reshape(G, Np)[:, :N].contiguous()
+
+
+def unpack_zero(z: torch.Tensor, N: int) -> torch.Tensor:
+    """int8 [Npad, G] packed -> effective zeros int32 [G, N]."""
+    Np, G = z.shape
+    zz = z.contiguous().view(torch.uint8).view(Np // TILE, G, TILE).permute(1, 0, 2).reshape(G, Np)
+    return zz[:, :N].to(torch.int32).contiguous()

@@ -1,0 +1,201 @@
+"""Module API of the quantized linear layer: `QLinear.init / QLinear.empty` return an
+`nn.Module` whose `forward(x)` computes `x @ dequant(W)^T` in fp16.
+
+Same names, arguments and error behaviour as the reference (reference:
+qfactory/qlinear.py:5-145).  Differences, all on purpose:
+  * the packed tensors `.w/.s/.z` use the tile-128 layout of `convert.py`;
+  * the batch size is a run-time property of `forward`, not a compile-time constant, and
+    `x` may have any number of leading dimensions;
+  * kernel selection is a static heuristic inside the native library, so `compile_flags`
+    and `base_impl` are accepted and ignored;
+  * `QLinear.from_float` builds a layer from an fp16 weight.
+The forward pass calls the native library through its C ABI; without it the module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native, layout
+from .convert import convert_params
+from .quantize import asymmetric_quant
+
+
+class _PackedLinear(torch.nn.Module):
+    """Shared implementation: owns the packed buffers, the split-K workspace and the
+    `qfb_layer` descriptor handed to the C ABI."""
+
+    def __init__(self, in_features, out_features, n_bits, group_size, w, s, z, max_batch=16):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.n_bits, self.group_size = n_bits, group_size
+        # buffers: they follow .to()/.cuda() and are saved by state_dict()
+        self.register_buffer("w", w)
+        self.register_buffer("s", s)
+        self.register_buffer("z", z)
+        self.flags = 0
+        self._desc = None
+        self._ws = None
+        self._ws_bytes = 0
+        self._max_batch = max_batch
+        self._host = None
+
+    # -- native plumbing ---------------------------------------------------
+    def _prepare(self):
+        if not self.w.is_cuda:
+            raise _native.NativeError("the quantized linear layer runs on CUDA only (no CPU path); move it with .to('cuda')")
+        L = _native.lib()
+        d = _native.QfbLayer()
+        d.qweight = self.w.data_ptr()
+        d.scales = self.s.data_ptr() if self.s is not None else None
+        d.zeros = self.z.data_ptr() if self.z is not None else None
+        d.n, d.k, d.bits, d.group_size = self.out_features, self.in_features, self.n_bits, self.group_size
+        nbytes = L.qfb_workspace_bytes(self._max_batch, self.out_features, self.in_features, self.n_bits)
+        self._ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.w.device)
+        self._ws_bytes = nbytes
+        self._desc = d
+        self._lib = L
+
+    def _apply(self, fn, *a, **kw):
+        r = super()._apply(fn, *a, **kw)
+        self._desc = None  # device pointers changed
+        self._host = None
+        return r
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        if self._desc is None:
+            self._prepare()
+        assert x.dtype == torch.float16, "activations must be fp16"
+        assert x.shape[-1] == self.in_features
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.in_features)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty(M, self.out_features, dtype=torch.float16, device=x.device)
+        else:
+            assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() == M * self.out_features
+        st = self._lib.qfb_linear_forward(
+            ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
+            self._ws.data_ptr(), self._ws_bytes, self.flags,
+            torch.cuda.current_stream(x.device).cuda_stream,
+        )
+        if st != 0:
+            _native.check(st, "qfb_linear_forward")
+        return out.view(*lead, self.out_features)
+
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None) -> torch.Tensor:
+        """Host-buffer entry: `x_host` (CPU fp16, ideally pinned) is copied in, the result is
+        copied back into `y_host` (CPU fp16) and the stream is synchronised."""
+        if self._desc is None:
+            self._prepare()
+        x2 = x_host.reshape(-1, self.in_features)
+        M = x2.shape[0]
+        assert x2.dtype == torch.float16 and x2.is_contiguous() and not x2.is_cuda
+        if y_host is None:
+            y_host = torch.empty(M, self.out_features, dtype=torch.float16, pin_memory=True)
+        if self._host is None or self._host[0].shape[0] < M:
+            dev = self.w.device
+            self._host = (torch.empty(M, self.in_features, dtype=torch.float16, device=dev),
+                          torch.empty(M, self.out_features, dtype=torch.float16, device=dev))
+        xs, ys = self._host
+        st = self._lib.qfb_linear_forward_host(
+            ctypes.byref(self._desc), x2.data_ptr(), M, y_host.data_ptr(), xs.data_ptr(), ys.data_ptr(),
+            self._ws.data_ptr(), self._ws_bytes, self.flags,
+            torch.cuda.current_stream(self.w.device).cuda_stream,
+        )
+        if st != 0:
+            _native.check(st, "qfb_linear_forward_host")
+        return y_host
+
+    # -- test / debug helpers through the kernels' own decode path ----------
+    def unpack_codes(self) -> torch.Tensor:
+        if self._desc is None:
+            self._prepare()
+        q = torch.empty(self.in_features, self.out_features, dtype=torch.int32, device=self.w.device)
+        _native.check(self._lib.qfb_unpack_codes(ctypes.byref(self._desc), q.data_ptr(),
+                                                 torch.cuda.current_stream(self.w.device).cuda_stream))
+        return q
+
+    def dequantize(self) -> torch.Tensor:
+        if self._desc is None:
+            self._prepare()
+        wd = torch.empty(self.in_features, self.out_features, dtype=torch.float16, device=self.w.device)
+        _native.check(self._lib.qfb_dequantize(ctypes.byref(self._desc), wd.data_ptr(),
+                                               torch.cuda.current_stream(self.w.device).cuda_stream))
+        return wd
+
+    def extra_repr(self):
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.n_bits}, "
+                f"group_size={self.group_size}, symmetric={self.z is None and self.s is not None}")
+
+
+class GPTQLinear(_PackedLinear):
+    """Group-quantized layer (reference: qfactory/qlinear.py:5-58)."""
+
+    def __init__(self, in_features, out_features, n_bits, weight, group_size, scale, zero, bias,
+                 compile_flags=None, skip_convert=False, batch_size=1, base_impl=False):
+        if bias:
+            raise NotImplementedError("Bias is not supported")
+        if skip_convert:
+            w, s, z = weight, scale, zero
+        else:
+            w, s, z = convert_params(
+                {"K": in_features, "N": out_features, "NBITS": n_bits, "GS": group_size}, (weight, scale, zero))
+        npad = layout.padded_rows(out_features)
+        layout.check_shape(out_features, in_features, n_bits, group_size)
+        assert w.dtype == torch.int8 and w.dim() == 2
+        assert w.numel() == npad * in_features * n_bits // 8
+        assert s.dtype == torch.float16 and s.shape == (npad, in_features // group_size)
+        if z is not None:
+            assert z.dtype == torch.int8 and z.shape == (npad, in_features // group_size)
+        super().__init__(in_features, out_features, n_bits, group_size, w, s, z, max_batch=max(16, batch_size))
+
+
+class GEMVLinear(_PackedLinear):
+    """Group-less layer on raw unsigned codes: y = x @ codes^T, no scale or zero
+    (reference: qfactory/qlinear.py:60-97, kernel qfactory/include/gemv.h:12-94)."""
+
+    def __init__(self, in_features, out_features, n_bits, weight, bias, compile_flags=None, skip_convert=False):
+        if bias:
+            raise NotImplementedError("Bias is not supported")
+        w = weight if skip_convert else convert_params(
+            {"K": in_features, "N": out_features, "NBITS": n_bits}, (weight,))
+        layout.check_shape(out_features, in_features, n_bits, -1)
+        assert w.dtype == torch.int8 and w.dim() == 2
+        assert w.numel() == layout.padded_rows(out_features) * in_features * n_bits // 8
+        super().__init__(in_features, out_features, n_bits, -1, w, None, None)
+
+
+class QLinear:
+    """Factory with the reference's static methods (reference: qfactory/qlinear.py:99-145)."""
+
+    @staticmethod
+    def init(batch_size, in_features, out_features, n_bits, weight, group_size=-1, scale=None, zero=None,
+             bias=False, compile_flags={}):
+        if group_size == -1:
+            return GEMVLinear(in_features, out_features, n_bits, weight, bias, compile_flags, skip_convert=False)
+        return GPTQLinear(in_features, out_features, n_bits, weight, group_size, scale, zero, bias, compile_flags,
+                          skip_convert=False, batch_size=batch_size)
+
+    @staticmethod
+    def empty(M, K, N, NBITS, GS, sym, compile_flags={}, base_impl=False, device="cuda"):
+        """Uninitialised packed buffers of the right shapes (benchmarks, the vLLM hook)."""
+        npad = layout.padded_rows(N)
+        w = torch.empty(npad, K * NBITS // 8, dtype=torch.int8, device=device)
+        if GS == -1:
+            return GEMVLinear(K, N, NBITS, w, False, compile_flags, skip_convert=True)
+        s = torch.empty(npad, K // GS, dtype=torch.float16, device=device)
+        z = None if sym else torch.empty(npad, K // GS, dtype=torch.int8, device=device)
+        return GPTQLinear(K, N, NBITS, w, GS, s, z, False, compile_flags, skip_convert=True, batch_size=M,
+                          base_impl=base_impl)
+
+    @staticmethod
+    def from_float(weight: torch.Tensor, n_bits: int, group_size: int = 128, batch_size: int = 1):
+        """Quantize an fp16 weight [K, N] group-wise (asymmetric, as the reference's
+        tests/acc_gptq.py:10-29 does) and pack it."""
+        K, N = weight.shape
+        q, s, z = asymmetric_quant(weight, group_size, n_bits)
+        return QLinear.init(batch_size, K, N, n_bits, q, group_size, s, z)
