@@ -114,6 +114,12 @@ int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, v
 /* Which kernel qfb_linear_forward picks: 1 = SIMT split-K GEMV, 2 = tcgen05 GEMM, 0 = invalid. */
 int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags);
 
+/* Smallest batch that is routed to the tensor-core kernel (default 2).  Process-wide. */
+void qfb_set_tensor_min_batch(int min_m);
+/* Reads the workspace's status word (synchronises `stream`): returns QFB_ERR_DEVICE_FLAG and
+ * *status_out != 0 when a kernel gave up on a bounded wait since qfb_workspace_init. */
+int qfb_read_status(const void* workspace, void* stream, unsigned* status_out);
+
 /* Debug / tuning override of the split-K heuristic of the SIMT kernel: split_k <= 0 and
  * k_ways <= 0 restore the built-in choice.  Process-wide, not thread-safe. */
 void qfb_set_gemv_tuning(int split_k, int k_ways);

@@ -15,6 +15,7 @@ constexpr int kMaxSimtRows = 8;  // activation rows one SIMT launch handles
 static thread_local int tl_last_cuda_error = 0;
 static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
 static int g_tune_split = 0, g_tune_kways = 0;
+static int g_tc_min_m = 2;  // smallest batch routed to the tensor-core kernel
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -67,8 +68,109 @@ static int split_cap(int tiles, int units) {
   return std::max(1, std::min(cap, units));
 }
 
+// Workspace layout: [0, 256) status words (word 0: a kernel's bounded wait ran out);
+// [256, 256 + counters) arrival counters; then the fp32 split-K partial sums.
+constexpr size_t kHeaderBytes = 256;
 static size_t counters_bytes(int tiles) {
-  return ((size_t)tiles * sizeof(unsigned) + kCounterAlign - 1) / kCounterAlign * kCounterAlign;
+  const size_t n = (size_t)std::max(tiles, 512);
+  return (n * sizeof(unsigned) + kCounterAlign - 1) / kCounterAlign * kCounterAlign;
+}
+static size_t partial_offset(int tiles) { return kHeaderBytes + counters_bytes(tiles); }
+
+// ---- tensor-core path planning --------------------------------------------------------
+struct TcPlan { int nb, mtiles, split; bool post; };
+
+static bool tc_supported(const LayerView& v) { return v.bits != 3; }
+
+static TcPlan plan_tc(const LayerView& v, int m) {
+  TcPlan pl;
+  if (m <= 16) { pl.nb = 16; pl.post = true; }
+  else if (m <= 32) { pl.nb = 32; pl.post = true; }
+  else if (m <= 64) { pl.nb = 64; pl.post = true; }
+  else if (m <= 128) { pl.nb = 128; pl.post = false; }
+  else { pl.nb = 256; pl.post = false; }
+  pl.mtiles = (m + pl.nb - 1) / pl.nb;
+  const int kblocks = v.k / 64;
+  const long long ctas = (long long)v.tiles * pl.mtiles;
+  const int target = kNumSMs * (pl.nb <= 16 ? 2 : 1);
+  int split = (int)std::max<long long>(1, target / ctas);
+  split = std::min(split, std::max(1, kblocks / 8));
+  split = std::min(split, 32);
+  if (ctas > 512) split = 1;  // the counter array holds 512 tiles
+  pl.split = split;
+  return pl;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  }
+  return fn;
+}
+
+static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
+                  unsigned flags, cudaStream_t st) {
+  const TcPlan pl = plan_tc(v, m);
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return QFB_ERR_UNSUPPORTED;
+  CUtensorMap tm;
+  const cuuint64_t gdim[2] = {(cuuint64_t)v.k, (cuuint64_t)m};
+  const cuuint64_t gstr[1] = {(cuuint64_t)v.k * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)pl.nb};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), gdim, gstr, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return QFB_ERR_CUDA;
+  TcParams p;
+  p.qw = v.qw;
+  p.qs = v.qs;
+  p.qz = v.qz;
+  p.y = y;
+  p.m = m;
+  p.n = v.n;
+  p.k = v.k;
+  p.npad = v.npad;
+  p.groups = v.groups;
+  p.kblocks = v.k / 64;
+  p.kb_per_group = v.group_size == -1 ? p.kblocks : v.group_size / 64;
+  p.zconst = v.zconst;
+  p.partial = nullptr;
+  p.counters = nullptr;
+  p.status = nullptr;
+  if (workspace && ws_bytes >= kHeaderBytes) p.status = static_cast<unsigned*>(workspace);
+  if (pl.split > 1) {
+    const size_t off = partial_offset(v.tiles);
+    const size_t need = off + (size_t)pl.split * m * v.npad * sizeof(float);
+    if (!workspace || ws_bytes < need) return QFB_ERR_WORKSPACE;
+    p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
+    p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
+  }
+  const dim3 grid(v.tiles, pl.mtiles, pl.split);
+  tl_last_launch[0] = 2;
+  tl_last_launch[1] = grid.x * grid.y;
+  tl_last_launch[2] = grid.z;
+  tl_last_launch[3] = 512;
+  tl_last_launch[4] = (int)gemm_tc_smem_bytes(v.bits, pl.nb, pl.post);
+  return check_cuda(launch_gemm_tc(tm, p, v.bits, pl.nb, pl.post, grid, (flags & QFB_FLAG_PDL) != 0, st));
+}
+
+static int choose_kernel(const LayerView& v, int m, unsigned flags) {
+  if (flags & QFB_FLAG_FORCE_SIMT) return 1;
+  if (!tc_supported(v)) return 1;
+  if (flags & QFB_FLAG_FORCE_TENSOR) return 2;
+  return m >= g_tc_min_m ? 2 : 1;
 }
 
 struct GemvPlan { int split, kways, mb; size_t smem; };
@@ -120,11 +222,11 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
     p.partial = nullptr;
     p.counters = nullptr;
     if (pl.split > 1) {
-      const size_t cb = counters_bytes(v.tiles);
-      const size_t need = cb + (size_t)pl.split * rows * v.npad * sizeof(float);
+      const size_t off = partial_offset(v.tiles);
+      const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);
       if (!workspace || ws_bytes < need) return QFB_ERR_WORKSPACE;
-      p.counters = static_cast<unsigned*>(workspace);
-      p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + cb);
+      p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
+      p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
     }
     const dim3 grid(pl.split, v.tiles);
     const int block = kTileRows * pl.kways;
@@ -184,7 +286,18 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
   const int npad = padded_rows(n);
   const int tiles = npad / kTileRows;
   const int rows = std::min(m_max, kMaxSimtRows);
-  return counters_bytes(tiles) + (size_t)split_cap(tiles, k / unit_k(bits)) * rows * npad * sizeof(float);
+  size_t partial = (size_t)split_cap(tiles, k / unit_k(bits)) * rows * npad * sizeof(float);
+  if (bits != 3) {
+    LayerView v = {};
+    v.n = n; v.k = k; v.bits = bits; v.npad = npad; v.tiles = tiles;
+    const int probes[] = {16, 32, 64, 128, 256, 512, 768, 1024, 1536, 2048, 4096, m_max};
+    for (int m : probes) {
+      if (m > m_max) continue;
+      const TcPlan pl = plan_tc(v, m);
+      if (pl.split > 1) partial = std::max(partial, (size_t)pl.split * m * npad * sizeof(float));
+    }
+  }
+  return partial_offset(tiles) + partial;
 }
 
 int qfb_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -196,8 +309,21 @@ int qfb_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
 
 int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags) {
   if (m <= 0 || validate_shape(n, k, bits, -1) != QFB_OK) return 0;
-  (void)flags;
-  return 1;
+  LayerView v = {};
+  v.bits = bits;
+  return choose_kernel(v, m, flags);
+}
+
+void qfb_set_tensor_min_batch(int min_m) { g_tc_min_m = min_m > 0 ? min_m : 2; }
+
+int qfb_read_status(const void* workspace, void* stream, unsigned* status_out) {
+  if (!workspace || !status_out) return QFB_ERR_NULL_POINTER;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int s = check_cuda(cudaMemcpyAsync(status_out, workspace, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+  if (s != QFB_OK) return s;
+  s = check_cuda(cudaStreamSynchronize(st));
+  if (s != QFB_OK) return s;
+  return *status_out ? QFB_ERR_DEVICE_FLAG : QFB_OK;
 }
 
 void qfb_set_gemv_tuning(int split_k, int k_ways) {
@@ -222,6 +348,9 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
   if (m == 0) return QFB_OK;
   if (!x || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  if (choose_kernel(v, m, flags) == 2)
+    return run_tc(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                  static_cast<cudaStream_t>(stream));
   return run_gemv(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                   static_cast<cudaStream_t>(stream));
 }

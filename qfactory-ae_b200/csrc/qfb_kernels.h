@@ -1,6 +1,7 @@
 // Internal launch interfaces between the C-ABI layer and the kernel translation units.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -25,6 +26,25 @@ struct GemvParams {
 
 cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int block, size_t smem, bool pdl,
                         cudaStream_t st);
+
+struct TcParams {
+  const uint4* qw;
+  const __half* qs;      // null: group-less (no scaling)
+  const uint8_t* qz;     // null: zconst
+  __half* y;             // [m, n]
+  float* partial;        // [S, m, npad] split-K partial sums
+  unsigned* counters;    // [m tiles, n tiles] arrival counters, zero between launches
+  unsigned* status;      // set to 1 when a bounded wait ran out
+  int m, n, k, npad;
+  int groups;
+  int kblocks;           // K / 64
+  int kb_per_group;      // group_size / 64 (kblocks when group-less)
+  uint32_t zconst;
+};
+// activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
+cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, dim3 grid,
+                           bool pdl, cudaStream_t st);
+size_t gemm_tc_smem_bytes(int bits, int nb, bool post);
 
 struct PackParams {
   const int32_t* codes;   // [k, n]
