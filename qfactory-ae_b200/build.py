@@ -59,6 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB_DIR, exist_ok=True)
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += os.environ.get("QFB_NVCC_EXTRA", "").split()
 
     def compile_one(src: str) -> str:
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")

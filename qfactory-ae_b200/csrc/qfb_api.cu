@@ -72,7 +72,7 @@ static int split_cap(int tiles, int units) {
 // [256, 256 + counters) arrival counters; then the fp32 split-K partial sums.
 constexpr size_t kHeaderBytes = 256;
 static size_t counters_bytes(int tiles) {
-  const size_t n = (size_t)std::max(tiles, 512);
+  const size_t n = (size_t)std::max(tiles, 2048);
   return (n * sizeof(unsigned) + kCounterAlign - 1) / kCounterAlign * kCounterAlign;
 }
 static size_t partial_offset(int tiles) { return kHeaderBytes + counters_bytes(tiles); }
@@ -80,24 +80,36 @@ static size_t partial_offset(int tiles) { return kHeaderBytes + counters_bytes(t
 // ---- tensor-core path planning --------------------------------------------------------
 struct TcPlan { int nb, mtiles, split; bool post; };
 
-static bool tc_supported(const LayerView& v) { return v.bits != 3; }
+static bool tc_supported(const LayerView& v) { return v.k % 128 == 0; }
 
 static TcPlan plan_tc(const LayerView& v, int m) {
   TcPlan pl;
-  if (m <= 16) { pl.nb = 16; pl.post = true; }
-  else if (m <= 32) { pl.nb = 32; pl.post = true; }
-  else if (m <= 64) { pl.nb = 64; pl.post = true; }
-  else if (m <= 128) { pl.nb = 128; pl.post = false; }
-  else { pl.nb = 256; pl.post = false; }
-  pl.mtiles = (m + pl.nb - 1) / pl.nb;
-  const int kblocks = v.k / 64;
-  const long long ctas = (long long)v.tiles * pl.mtiles;
-  const int target = kNumSMs * (pl.nb <= 16 ? 2 : 1);
-  int split = (int)std::max<long long>(1, target / ctas);
-  split = std::min(split, std::max(1, kblocks / 8));
-  split = std::min(split, 32);
-  if (ctas > 512) split = 1;  // the counter array holds 512 tiles
-  pl.split = split;
+  pl.split = 1;
+  // per-stage accumulators need quantisation groups made of whole 128-k stages
+  const bool post_ok = v.group_size == -1 || v.group_size % 128 == 0;
+  if (m <= 64) {
+    // HBM-bound regime: split K until the SMs are covered
+    pl.post = post_ok;
+    pl.nb = !post_ok ? 64 : m <= 16 ? 16 : m <= 32 ? 32 : 64;
+    pl.mtiles = 1;
+    const int kblocks = v.k / 128;
+    const int target = kNumSMs * ((pl.post && pl.nb <= 16) ? 2 : 1);
+    int split = std::max(1, target / v.tiles);
+    split = std::min(split, std::max(1, kblocks / 4));
+    split = std::min(split, 32);
+    if (v.tiles > 512) split = 1;  // the counter array holds 512 tiles x 4 row quarters
+    pl.split = split;
+  } else {
+    // tensor-bound regime: scale in the decode, one accumulator over all of K, no split;
+    // pick the widest batch tile that still yields at least one CTA per SM
+    pl.post = false;
+    pl.nb = 64;
+    for (int nb : {256, 128}) {
+      if (m >= nb && (long long)v.tiles * ((m + nb - 1) / nb) >= kNumSMs) { pl.nb = nb; break; }
+    }
+    if (pl.nb == 64 && (long long)v.tiles * ((m + 127) / 128) >= kNumSMs / 2) pl.nb = 128;
+    pl.mtiles = (m + pl.nb - 1) / pl.nb;
+  }
   return pl;
 }
 
@@ -143,12 +155,18 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   p.k = v.k;
   p.npad = v.npad;
   p.groups = v.groups;
-  p.kblocks = v.k / 64;
-  p.kb_per_group = v.group_size == -1 ? p.kblocks : v.group_size / 64;
+  p.kblocks = v.k / 128;
+  const int gs = v.group_size == -1 ? v.k : v.group_size;
+  p.steps_per_group = gs / 16;
+  p.halfstages_per_group = gs / 64;
   p.zconst = v.zconst;
   p.partial = nullptr;
   p.counters = nullptr;
   p.status = nullptr;
+  p.dbg = nullptr;
+#ifdef QFB_TC_TIMING
+  if (workspace && ws_bytes >= kHeaderBytes) p.dbg = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 16);  // header words 2..31
+#endif
   if (workspace && ws_bytes >= kHeaderBytes) p.status = static_cast<unsigned*>(workspace);
   if (pl.split > 1) {
     const size_t off = partial_offset(v.tiles);
@@ -162,7 +180,7 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   tl_last_launch[1] = grid.x * grid.y;
   tl_last_launch[2] = grid.z;
   tl_last_launch[3] = 512;
-  tl_last_launch[4] = (int)gemm_tc_smem_bytes(v.bits, pl.nb, pl.post);
+  tl_last_launch[4] = pl.nb;
   return check_cuda(launch_gemm_tc(tm, p, v.bits, pl.nb, pl.post, grid, (flags & QFB_FLAG_PDL) != 0, st));
 }
 
@@ -287,14 +305,17 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
   const int tiles = npad / kTileRows;
   const int rows = std::min(m_max, kMaxSimtRows);
   size_t partial = (size_t)split_cap(tiles, k / unit_k(bits)) * rows * npad * sizeof(float);
-  if (bits != 3) {
+  if (k % 128 == 0) {
     LayerView v = {};
     v.n = n; v.k = k; v.bits = bits; v.npad = npad; v.tiles = tiles;
-    const int probes[] = {16, 32, 64, 128, 256, 512, 768, 1024, 1536, 2048, 4096, m_max};
-    for (int m : probes) {
-      if (m > m_max) continue;
-      const TcPlan pl = plan_tc(v, m);
-      if (pl.split > 1) partial = std::max(partial, (size_t)pl.split * m * npad * sizeof(float));
+    const int probes[] = {16, 32, 64, m_max};
+    for (int gs : {64, 128}) {  // the group size selects between the two accumulation modes
+      v.group_size = gs;
+      for (int m : probes) {
+        if (m > m_max) continue;
+        const TcPlan pl = plan_tc(v, m);
+        if (pl.split > 1) partial = std::max(partial, (size_t)pl.split * m * npad * sizeof(float));
+      }
     }
   }
   return partial_offset(tiles) + partial;
@@ -311,6 +332,7 @@ int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags) {
   if (m <= 0 || validate_shape(n, k, bits, -1) != QFB_OK) return 0;
   LayerView v = {};
   v.bits = bits;
+  v.k = k;
   return choose_kernel(v, m, flags);
 }
 

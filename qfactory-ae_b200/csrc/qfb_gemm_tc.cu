@@ -3,16 +3,22 @@
 // activation row fills the 5th-generation tensor core.  No counterpart in the reference, whose
 // kernels are CUDA-core GEMVs only (qfactory/include/gptq_gemv.h:14-154).
 //
-// Data flow of one CTA (one 128-row weight tile x one batch tile x one K split):
+// Data flow of one CTA (one 128-row weight tile x one batch tile x one K split), in stages
+// of 128 k:
 //
-//   TMA (warp 0)      packed weights (contiguous bulk copy), zeros, scales, and the fp16
-//                     activation tile (128-byte-swizzled tensor copy) -> shared-memory ring
+//   TMA (2 threads)   packed weights (one contiguous bulk copy per stage) and the fp16
+//                     activation tile (two 128-byte-swizzled tensor boxes) -> two independent
+//                     shared-memory rings; the weight ring is released by the decode warps as
+//                     soon as the codes are in registers, the activation ring by MMA completion
 //   decode (8 warps)  packed codes -> exact (q - z) fp16 pairs in registers (LOP3 / PRMT magic
 //                     numbers) -> tcgen05.st into TENSOR MEMORY as the A operand.  The fp16
 //                     weights never touch shared memory, whose bandwidth could not carry the
-//                     4x-expanded stream at HBM rate.
-//   MMA (1 thread)    tcgen05.mma kind::f16, A from tensor memory, B (activations) from shared
-//                     memory, fp32 accumulators in tensor memory
+//                     4x-expanded stream at HBM rate.  Thread (row, half) owns 64 codes of a stage.
+//   MMA (1-2 threads) tcgen05.mma kind::f16, A from tensor memory, B (activations) from shared
+//                     memory, fp32 accumulators in tensor memory.  ONE tcgen05.commit per stage
+//                     feeds every consumer of "stage done".  With per-stage accumulators (POST)
+//                     two threads issue alternate stages, since a skinny MMA costs more to issue
+//                     than to execute.
 //   scale (4 warps)   POST mode (small batches): one accumulator per quantisation group; the
 //                     group's fp32 partial is read back with tcgen05.ld and folded into register
 //                     accumulators with ONE fp32 FMA by the row's scale, so the decode needs a
@@ -29,51 +35,81 @@ namespace qfb {
 
 using namespace ptx;
 
+// Optional per-role cycle accounting for CTA (0,0,0), compiled in with -DQFB_TC_TIMING.
+#ifdef QFB_TC_TIMING
+#define TT_DECL(n) long long tt_[n] = {}; long long tt_t0_ = 0; (void)tt_t0_
+#define TT_START() (tt_t0_ = clock64())
+#define TT_ADD(i) do { const long long tt_now_ = clock64(); tt_[i] += tt_now_ - tt_t0_; tt_t0_ = tt_now_; } while (0)
+#define TT_DUMP(base, n) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) for (int ti_ = 0; ti_ < n; ++ti_) p.dbg[(base) + ti_] = tt_[ti_]; } while (0)
+#else
+#define TT_DECL(n)
+#define TT_START()
+#define TT_ADD(i)
+#define TT_DUMP(base, n)
+#endif
+
 constexpr int kTcThreads = 512;
-constexpr int kASlots = 4;         // A-operand slots in tensor memory, 32 columns (64 k) each
-constexpr int kAColsTotal = kASlots * 32;
+constexpr int kStageK = 128;              // k per pipeline stage
+constexpr int kStepsPerStage = kStageK / 16;
+constexpr int kAColsPerSlot = kStageK / 2;  // one 32-bit column holds two fp16 k
 constexpr int kDecodeWarps = 8;
 
 template <int BITS, int NB, bool POST>
 struct TcCfg {
-  static constexpr int kWBytes = 128 * 64 * BITS / 8;
-  static constexpr int kXBytes = NB * 128;
-  static constexpr int kZBytes = 128;
-  static constexpr int kSBytes = 256;
-  static constexpr int kStageBytes = kWBytes + kXBytes + kZBytes + kSBytes;
-  static constexpr int kBudget = (NB <= 64) ? 100 * 1024 : 200 * 1024;
-  static constexpr int kStagesRaw = kBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 12 ? 12 : (kStagesRaw < 3 ? 3 : kStagesRaw);
-  static constexpr int kDBufs = POST ? 2 : 1;
-  static constexpr int kColsNeeded = kAColsTotal + kDBufs * NB;
-  static constexpr int kTmemCols = kColsNeeded <= 256 ? 256 : 512;
-  static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes;
+  static constexpr int kWBytes = 128 * kStageK * BITS / 8;
+  static constexpr int kXBytes = NB * kStageK * 2;
+  static constexpr int kZSlot = 256;   // effective zeros of a stage: 128 rows x up to 2 groups
+  static constexpr int kSSlot = 512;   // fp16 scales of a stage (PRE mode only)
+  static constexpr int kQBytes = kZSlot + (POST ? 0 : kSSlot);
+#ifdef QFB_EXP_ONE_CTA
+  static constexpr bool kTwoPerSM = false;
+#else
+  static constexpr bool kTwoPerSM = POST && NB <= 16;   // smallest batches: two CTAs share an SM
+#endif
+  static constexpr int kBudget = kTwoPerSM ? 98 * 1024 : 224 * 1024;
+  static constexpr int kXStages = NB <= 16 ? 6 : NB <= 32 ? 8 : NB <= 64 ? 6 : NB <= 128 ? 4 : (BITS == 8 ? 2 : 3);
+  static constexpr int kWStagesRaw = (kBudget - kXStages * kXBytes) / (kWBytes + kQBytes);
+  static constexpr int kWStages = kWStagesRaw > 10 ? 10 : kWStagesRaw;
+  static constexpr int kTmemCols = kTwoPerSM ? 256 : 512;
+  // ring of R slots in tensor memory: A operand (64 columns) + in POST mode one accumulator each
+  static constexpr int kSlotCols = kAColsPerSlot + (POST ? NB : 0);
+  static constexpr int kRingRaw = (kTmemCols - (POST ? 0 : NB)) / kSlotCols;
+  static constexpr int kRing = kRingRaw > 6 ? 6 : kRingRaw;
+  static constexpr int kDBase = kRing * kAColsPerSlot;
+  static constexpr int kIssuers = POST ? 2 : 1;
+  static constexpr size_t kSmemBytes = 1024 + (size_t)kXStages * kXBytes + (size_t)kWStages * (kWBytes + kQBytes);
+  static_assert(kWStages >= 2, "weight ring too shallow");
+  static_assert(kRing >= 2, "need at least two tensor-memory slots");
+  static_assert(kDBase + (POST ? kRing * NB : NB) <= kTmemCols, "tensor memory over-subscribed");
 };
 
-// ---- decode of the 32 codes one thread owns in a 64-k stage ---------------------------
+// ---- decode of the 64 codes thread (row, h) owns in a 128-k stage -> 32 fp16 pairs ------
 template <int BITS> struct StageDecode;
 template <> struct StageDecode<4> {
-  // stage = [2 units][128 rows][16 B]; thread (row, h) owns unit h
-  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[16]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(w + ((h * kTileRows + row) << 4));
+  // stage = [4 units][128 rows][16 B]; thread owns units 2h, 2h+1
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
     const Codec<4>::ZM zm = Codec<4>::zmagic(z);
-    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      __half2 t[4];
-      Codec<4>::word(ww[j], zm, t);
+    for (int u = 0; u < 2; ++u) {
+      const uint4 v = *reinterpret_cast<const uint4*>(w + (((2 * h + u) * kTileRows + row) << 4));
+      const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) d[4 * j + i] = t[i];
+      for (int j = 0; j < 4; ++j) {
+        __half2 t[4];
+        Codec<4>::word(ww[j], zm, t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[16 * u + 4 * j + i] = t[i];
+      }
     }
   }
 };
 template <> struct StageDecode<8> {
-  // stage = [4 units][128 rows][16 B]; thread (row, h) owns units 2h, 2h+1
-  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[16]) {
+  // stage = [8 units][128 rows][16 B]; thread owns units 4h .. 4h+3
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
     const Codec<8>::ZM zm = Codec<8>::zmagic(z);
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const uint4 v = *reinterpret_cast<const uint4*>(w + (((2 * h + u) * kTileRows + row) << 4));
+    for (int u = 0; u < 4; ++u) {
+      const uint4 v = *reinterpret_cast<const uint4*>(w + (((4 * h + u) * kTileRows + row) << 4));
       const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -84,13 +120,13 @@ template <> struct StageDecode<8> {
   }
 };
 template <> struct StageDecode<2> {
-  // stage = [1 unit][128 rows][16 B]; thread (row, h) owns words 2h, 2h+1 of the row's vector
-  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[16]) {
-    const uint2 v = *reinterpret_cast<const uint2*>(w + (row << 4) + (h << 3));
+  // stage = [2 units][128 rows][16 B]; thread owns unit h
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(w + ((h * kTileRows + row) << 4));
     const Codec<2>::ZM zm = Codec<2>::zmagic(z);
-    const uint32_t ww[2] = {v.x, v.y};
+    const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < 4; ++j) {
       __half2 t[4];
       Codec<2>::half_word(ww[j], zm, t);
 #pragma unroll
@@ -101,16 +137,45 @@ template <> struct StageDecode<2> {
     }
   }
 };
+template <> struct StageDecode<3> {
+  // stage = one 3-bit unit = [3 vectors][128 rows][16 B]: two 2-bit-plane vectors and the
+  // 1-bit-plane vector; thread owns 2-bit vector h and words 2h, 2h+1 of the plane vector
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const uint4 a = *reinterpret_cast<const uint4*>(w + ((h * kTileRows + row) << 4));
+    const uint2 b = *reinterpret_cast<const uint2*>(w + ((2 * kTileRows + row) << 4) + (h << 3));
+    const Codec<3>::ZM zm = Codec<3>::zmagic(z);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t bw[2] = {b.x, b.y};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {  // 32 codes: 2-bit words aw[2j], aw[2j+1] with plane word bw[j]
+      __half2 t[4];
+      Codec<3>::half_word(aw[2 * j], bw[j] << 2, zm, t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d[16 * j + i] = t[i];
+      Codec<3>::half_word(aw[2 * j] >> 8, bw[j] << 1, zm, t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d[16 * j + 4 + i] = t[i];
+      Codec<3>::half_word(aw[2 * j + 1], bw[j] >> 6, zm, t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d[16 * j + 8 + i] = t[i];
+      Codec<3>::half_word(aw[2 * j + 1] >> 8, bw[j] >> 7, zm, t);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d[16 * j + 12 + i] = t[i];
+    }
+  }
+};
 
 template <int BITS, int NB, bool POST>
-__global__ void __launch_bounds__(kTcThreads, (POST && NB <= 16) ? 2 : 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                  const TcParams p) {
+__global__ void __launch_bounds__(kTcThreads, (TcCfg<BITS, NB, POST>::kTwoPerSM ? 2 : 1))
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   using Cfg = TcCfg<BITS, NB, POST>;
-  constexpr int NS = Cfg::kStages;
-  constexpr int NA = kASlots;
+  constexpr int NS = Cfg::kWStages;   // weight ring
+  constexpr int NX = Cfg::kXStages;   // activation ring
+  constexpr int R = Cfg::kRing;       // tensor-memory slot ring
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_full[NS], bar_empty[NS], bar_afull[NA], bar_aempty[NA], bar_dfull[2], bar_dempty[2];
+  __shared__ uint64_t bar_wfull[NS], bar_wempty[NS], bar_xfull[NX], bar_xempty[NX];
+  __shared__ uint64_t bar_afull[R], bar_done[R], bar_dempty[R];
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -122,22 +187,23 @@ __global__ void __launch_bounds__(kTcThreads, (POST && NB <= 16) ? 2 : 1) qgemm_
 
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
-  const uint32_t x_off = 0;
-  const uint32_t w_off = NS * Cfg::kXBytes;
-  const uint32_t z_off = w_off + NS * Cfg::kWBytes;
-  const uint32_t s_off = z_off + NS * Cfg::kZBytes;
+  constexpr uint32_t x_off = 0;
+  constexpr uint32_t w_off = NX * Cfg::kXBytes;
+  constexpr uint32_t z_off = w_off + NS * Cfg::kWBytes;
+  constexpr uint32_t s_off = z_off + NS * Cfg::kZSlot;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) {
-      mbar_init(smem_u32(&bar_full[i]), 1);
-      mbar_init(smem_u32(&bar_empty[i]), 1);
+      mbar_init(smem_u32(&bar_wfull[i]), 1);
+      mbar_init(smem_u32(&bar_wempty[i]), kDecodeWarps);
     }
-    for (int i = 0; i < NA; ++i) {
+    for (int i = 0; i < NX; ++i) {
+      mbar_init(smem_u32(&bar_xfull[i]), 1);
+      mbar_init(smem_u32(&bar_xempty[i]), 1);
+    }
+    for (int i = 0; i < R; ++i) {
       mbar_init(smem_u32(&bar_afull[i]), kDecodeWarps);
-      mbar_init(smem_u32(&bar_aempty[i]), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&bar_dfull[i]), 1);
+      mbar_init(smem_u32(&bar_done[i]), 1);
       mbar_init(smem_u32(&bar_dempty[i]), 4);
     }
     abort_flag = 0;
@@ -158,97 +224,160 @@ __global__ void __launch_bounds__(kTcThreads, (POST && NB <= 16) ? 2 : 1) qgemm_
   const bool has_s = p.qs != nullptr;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+    // ------------------------------ weight producer ---------------------------
+    // (never depends on the preceding kernel: no dependency wait on this path)
+    if (lane == 0) {
+      const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.qw) + ((size_t)tile * p.kblocks + kb0) * Cfg::kWBytes;
+      int s = 0;
+      uint32_t ph = 1;  // first pass over the ring: parity 1 of a fresh barrier passes at once
+      TT_DECL(2);
+      TT_START();
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp)) break;
+        TT_ADD(0);
+        const uint32_t bar = smem_u32(&bar_wfull[s]);
+        // zeros / scales of the groups this stage touches: one group, or two when the group is 64
+        const int g0 = ((kb0 + i) * 2) / p.halfstages_per_group;
+        const uint32_t ng = p.halfstages_per_group == 1 ? 2u : 1u;
+        const uint32_t zb = has_z ? ng * 128u : 0u, sb = (!POST && has_s) ? ng * 256u : 0u;
+        mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
+        tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)i * Cfg::kWBytes, Cfg::kWBytes, bar);
+        if (zb) tma_bulk_g2s(sbase + z_off + s * Cfg::kZSlot, p.qz + ((size_t)tile * p.groups + g0) * kTileRows, zb, bar);
+        if (sb) tma_bulk_g2s(sbase + s_off + s * Cfg::kSSlot, p.qs + ((size_t)tile * p.groups + g0) * kTileRows, sb, bar);
+        if (++s == NS) { s = 0; ph ^= 1; }
+        TT_ADD(1);
+      }
+      TT_DUMP(0, 2);
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // ------------------------------ activation producer -----------------------
     if (lane == 0) {
       prefetch_tensormap(&tmap_x);
-      const uint32_t tx = Cfg::kWBytes + Cfg::kXBytes + (has_z ? Cfg::kZBytes : 0) + ((!POST && has_s) ? Cfg::kSBytes : 0);
-      const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.qw) + (size_t)tile * p.kblocks * Cfg::kWBytes;
-      auto issue_weights = [&](int i) {
-        const int s = i % NS, kb = kb0 + i;
-        const uint32_t bar = smem_u32(&bar_full[s]);
-        mbar_arrive_expect_tx(bar, tx);
-        tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)kb * Cfg::kWBytes, Cfg::kWBytes, bar);
-        const int g = kb / p.kb_per_group;
-        if (has_z)
-          tma_bulk_g2s(sbase + z_off + s * Cfg::kZBytes, p.qz + ((size_t)tile * p.groups + g) * kTileRows, Cfg::kZBytes, bar);
-        if (!POST && has_s)
-          tma_bulk_g2s(sbase + s_off + s * Cfg::kSBytes, p.qs + ((size_t)tile * p.groups + g) * kTileRows, Cfg::kSBytes, bar);
-      };
-      auto issue_x = [&](int i) {
-        const int s = i % NS, kb = kb0 + i;
-        tma_tensor_2d_g2s(sbase + x_off + s * Cfg::kXBytes, &tmap_x, kb * 64, mtile * NB, smem_u32(&bar_full[s]));
-      };
-      // weights never depend on the preceding kernel: start them before the dependency wait
-      const int pro = nkb < NS ? nkb : NS;
-      for (int i = 0; i < pro; ++i) issue_weights(i);
       grid_dependency_wait();
-      for (int i = 0; i < pro; ++i) issue_x(i);
-      for (int i = NS; i < nkb; ++i) {
-        const int s = i % NS;
-        if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / NS) & 1) ^ 1, abortp)) break;
-        issue_weights(i);
-        issue_x(i);
+      int s = 0;
+      uint32_t ph = 1;
+      for (int i = 0; i < nkb; ++i) {
+        if (!mbar_wait(smem_u32(&bar_xempty[s]), ph, abortp)) break;
+        const uint32_t bar = smem_u32(&bar_xfull[s]);
+        const uint32_t dst = sbase + x_off + s * Cfg::kXBytes;
+        mbar_arrive_expect_tx(bar, Cfg::kXBytes);
+        tma_tensor_2d_g2s(dst, &tmap_x, (kb0 + i) * kStageK, mtile * NB, bar);
+        tma_tensor_2d_g2s(dst + NB * 128, &tmap_x, (kb0 + i) * kStageK + 64, mtile * NB, bar);
+        if (++s == NX) { s = 0; ph ^= 1; }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
+  } else if (warp == 1 || (warp == 2 && Cfg::kIssuers == 2)) {
+    // ------------------------------ MMA issuer(s) -----------------------------
+    // POST: issuer e takes stages e, e+2, ...; every stage has its own accumulator.
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_f16_m128(NB);
-      int seg = 0;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % NS, a = i % NA, kb = kb0 + i;
-        const bool new_seg = (i == 0) || (POST && (kb % p.kb_per_group == 0));
-        const bool end_seg = (i == nkb - 1) || (POST && ((kb + 1) % p.kb_per_group == 0));
-        const int d = POST ? (seg & 1) : 0;
-        if (!mbar_wait(smem_u32(&bar_full[s]), (i / NS) & 1, abortp)) break;
-        if (!mbar_wait(smem_u32(&bar_afull[a]), (i / NA) & 1, abortp)) break;
-        if (POST && new_seg) {
-          if (!mbar_wait(smem_u32(&bar_dempty[d]), ((seg >> 1) & 1) ^ 1, abortp)) break;
+      const int e = (warp == 1) ? 0 : 1;
+      TT_DECL(5);
+      TT_START();
+      for (int i = e; i < nkb; i += Cfg::kIssuers) {
+        const int xs = i % NX, r = i % R;
+        const uint32_t phx = (uint32_t)(i / NX) & 1u, phr = (uint32_t)(i / R) & 1u;
+        if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp)) break;
+        TT_ADD(0);
+        if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp)) break;
+        TT_ADD(1);
+        if (POST) {
+          if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp)) break;
+          TT_ADD(3);
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + kAColsTotal + d * NB;
-        const uint32_t a_tmem = tmem_base + a * 32;
-        const uint64_t bdesc = smem_desc_k_sw128(sbase + x_off + s * Cfg::kXBytes);
+        const uint32_t a_tmem = tmem_base + r * kAColsPerSlot;
+        const uint32_t d_tmem = tmem_base + Cfg::kDBase + (POST ? r * NB : 0);
+        const uint32_t xsm = sbase + x_off + xs * Cfg::kXBytes;
+        const uint64_t bd0 = smem_desc_k_sw128(xsm), bd1 = smem_desc_k_sw128(xsm + NB * 128);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          mma_f16_ts(d_tmem, a_tmem + 8 * j, bdesc + (uint64_t)(2 * j), idesc, (new_seg && j == 0) ? 0u : 1u);
-        mma_commit(smem_u32(&bar_empty[s]));
-        mma_commit(smem_u32(&bar_aempty[a]));
-        if (end_seg) {
-          mma_commit(smem_u32(&bar_dfull[d]));
-          ++seg;
+        for (int j = 0; j < kStepsPerStage; ++j) {
+          const uint32_t accumulate = POST ? (j != 0) : (i != 0 || j != 0);
+          mma_f16_ts(d_tmem, a_tmem + 8 * j, (j < 4 ? bd0 : bd1) + (uint64_t)(2 * (j & 3)), idesc, accumulate);
         }
+        mma_commit(smem_u32(&bar_done[r]));
+        TT_ADD(2);
       }
+      if (e == 0) { TT_DUMP(8, 5); }
     }
     __syncwarp();
   } else if (warp >= 4 && warp < 4 + kDecodeWarps) {
     // ------------------------------ decode warps ------------------------------
     const int q = warp & 3, h = (warp - 4) >> 2;
     const int row = q * 32 + lane;
+    // with groups of 64 the two halves of a stage belong to different groups: half h reads
+    // the second record of the stage's zero / scale slot
+    const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
+    int s = 0, r = 0, r_prev = 0, xrel = 0;
+    uint32_t phs = 0, phr = 1;
+    bool pending = false;
+    TT_DECL(6);
+    TT_START();
     for (int i = 0; i < nkb; ++i) {
-      const int s = i % NS, a = i % NA;
-      if (!mbar_wait(smem_u32(&bar_full[s]), (i / NS) & 1, abortp)) break;
-      const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZBytes + row] : p.zconst;
-      __half2 d[16];
+      if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp)) break;
+      TT_ADD(0);
+      const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qsel + row] : p.zconst;
+      __half2 d[32];
       StageDecode<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
-      uint32_t r[16];
+      uint32_t rr[32];
       if (!POST && has_s) {
-        const __half2 s2 = __half2half2(*reinterpret_cast<const __half*>(gbase + s_off + s * Cfg::kSBytes + row * 2));
+        const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(gbase + s_off + s * Cfg::kSSlot)[qsel + row]);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = as_u32(__hmul2(d[j], s2));
+        for (int j = 0; j < 32; ++j) rr[j] = as_u32(__hmul2(d[j], s2));
       } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) r[j] = as_u32(d[j]);
+        for (int j = 0; j < 32; ++j) rr[j] = as_u32(d[j]);
       }
-      if (!mbar_wait(smem_u32(&bar_aempty[a]), ((i / NA) & 1) ^ 1, abortp)) break;
+      // the packed stage is in registers: hand the shared-memory slot back to the producer
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
+      TT_ADD(1);
+      if (pending) {  // publish the previous stage: its tensor-memory stores have had a stage to land
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r_prev]));
+      }
+      TT_ADD(2);
+      // slot r was last read by the MMAs of stage i - R
+      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { pending = false; break; }
+      if (i >= R && warp == 4 && lane == 0) {  // ... whose activation tile is free as well: relay to its producer
+        mbar_arrive(smem_u32(&bar_xempty[xrel]));
+        if (++xrel == NX) xrel = 0;
+      }
+      TT_ADD(3);
       tc_fence_after();
-      tmem_st_x16(tmem_base + ((uint32_t)(q * 32) << 16) + a * 32 + h * 16, r);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + r * kAColsPerSlot + h * 32;
+      tmem_st_x16(taddr, reinterpret_cast<const uint32_t(&)[16]>(rr[0]));
+      tmem_st_x16(taddr + 16, reinterpret_cast<const uint32_t(&)[16]>(rr[16]));
+      pending = true;
+      r_prev = r;
+      if (++s == NS) { s = 0; phs ^= 1; }
+      if (++r == R) { r = 0; phr ^= 1; }
+      TT_ADD(4);
+    }
+    if (warp == 4 && lane == 0) { TT_DUMP(16, 6); }
+    if (pending) {
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_afull[a]));
+      if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r_prev]));
     }
+    if (NX < R && warp == 4 && lane == 0) {
+      // activation ring shallower than the slot ring: keep relaying the releases the loop
+      // above did not reach, as long as the producer still has tiles to load
+      for (int i = nkb; i < nkb + R && (i - R) + NX < nkb; ++i) {
+        if (i >= R) {
+          if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) break;
+          mbar_arrive(smem_u32(&bar_xempty[xrel]));
+          if (++xrel == NX) xrel = 0;
+        }
+        if (++r == R) { r = 0; phr ^= 1; }
+      }
+    }
+    __syncwarp();
   } else if (warp >= 12) {
     // ------------------------------ scale / epilogue warps --------------------
     const int q = warp & 3;
@@ -274,41 +403,65 @@ __global__ void __launch_bounds__(kTcThreads, (POST && NB <= 16) ? 2 : 1) qgemm_
       float acc[NB];
 #pragma unroll
       for (int j = 0; j < NB; ++j) acc[j] = 0.f;
-      int seg = 0;
+      const size_t sz_row = (size_t)tile * p.groups * kTileRows + row;
+      const int stages_per_group = p.halfstages_per_group >> 1;  // POST needs groups of whole stages
+      int r = 0;
+      uint32_t phr = 0;
+      TT_DECL(3);
+      TT_START();
+      // scales are fetched two stages ahead of their use
+      auto scale_of = [&](int i) -> __half {
+        if (!has_s || i >= nkb) return __ushort_as_half(0x3C00);
+        return p.qs[sz_row + (size_t)((kb0 + i) / stages_per_group) * kTileRows];
+      };
+      __half sc0 = scale_of(0), sc1 = scale_of(1);
       for (int i = 0; i < nkb; ++i) {
-        const int kb = kb0 + i;
-        const bool end_seg = (i == nkb - 1) || ((kb + 1) % p.kb_per_group == 0);
-        if (!end_seg) continue;
-        const int g = kb / p.kb_per_group;
-        const float sval = has_s ? __half2float(p.qs[((size_t)tile * p.groups + g) * kTileRows + row]) : 1.f;
-        const int d = seg & 1;
-        if (!mbar_wait(smem_u32(&bar_dfull[d]), (seg >> 1) & 1, abortp)) { ok = false; break; }
+        const float sval = __half2float(sc0);
+        sc0 = sc1;
+        sc1 = scale_of(i + 2);
+        TT_ADD(0);
+        if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { ok = false; break; }
+        TT_ADD(1);
         tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColsTotal + d * NB;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase + r * NB;
+        constexpr int CH = NB < 32 ? NB : 32;  // columns read back per wait
 #pragma unroll
-        for (int c = 0; c < NB; c += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(taddr + c, v);
+        for (int c0 = 0; c0 < NB; c0 += CH) {
+          uint32_t v[CH];
+#pragma unroll
+          for (int c = 0; c < CH; c += 16) tmem_ld_x16(taddr + c0 + c, reinterpret_cast<uint32_t(&)[16]>(v[c]));
           tmem_wait_ld();
+          if (c0 + CH == NB) {  // the accumulator is free as soon as its last chunk is in registers
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_dempty[r]));
+          }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[c + j] = fmaf(sval, __uint_as_float(v[j]), acc[c + j]);
+          for (int j = 0; j < CH; ++j) acc[c0 + j] = fmaf(sval, __uint_as_float(v[j]), acc[c0 + j]);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_dempty[d]));
-        ++seg;
+        if (++r == R) { r = 0; phr ^= 1; }
+        TT_ADD(2);
       }
+      if (warp == 12 && lane == 0) { TT_DUMP(24, 3); }
       if (ok) {
         grid_dependency_wait();  // y and the workspace may still be in use by the preceding kernel
 #pragma unroll
         for (int c = 0; c < NB; c += 16) store_chunk(c, &acc[c]);
       }
     } else {
-      ok = mbar_wait(smem_u32(&bar_dfull[0]), 0, abortp);
+      // follow the stage commits in order; the last one covers every MMA of this CTA
+      {
+        int r = 0;
+        uint32_t phr = 0;
+        for (int i = 0; i < nkb; ++i) {
+          if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { ok = false; break; }
+          if (++r == R) { r = 0; phr ^= 1; }
+        }
+      }
       if (ok) {
         tc_fence_after();
         grid_dependency_wait();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColsTotal;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase;
 #pragma unroll 1
         for (int c = 0; c < NB; c += 16) {
           uint32_t v[16];
@@ -323,25 +476,22 @@ __global__ void __launch_bounds__(kTcThreads, (POST && NB <= 16) ? 2 : 1) qgemm_
       }
     }
     if (ok && S > 1) {
-      // split-K: every epilogue warp publishes its 32 rows, the LAST warp to arrive (over all
-      // splits and all four row quarters) sums the partials of the whole tile in split order.
+      // split-K: every epilogue warp publishes its 32 rows; per row quarter, the LAST warp to
+      // arrive over all splits sums that quarter's partials in split order.
       __threadfence();
       __syncwarp();
       unsigned prev = 0;
-      unsigned* ctr = p.counters + (mtile * gridDim.x + tile);
+      unsigned* ctr = p.counters + ((mtile * gridDim.x + tile) * 4 + q);
       if (lane == 0) prev = atomicAdd(ctr, 1u);
       prev = __shfl_sync(0xffffffffu, prev, 0);
-      if (prev == (unsigned)(4 * S - 1)) {
+      if (prev == (unsigned)(S - 1)) {
         __threadfence();
-        for (int qq = 0; qq < 4; ++qq) {
-          const int nn = tile * kTileRows + qq * 32 + lane;
-          for (int j = 0; j < NB; ++j) {
-            const int m = m0 + j;
-            if (m >= p.m) break;
-            float sum = 0.f;
-            for (int sp = 0; sp < S; ++sp) sum += __ldcg(p.partial + ((size_t)sp * p.m + m) * p.npad + nn);
-            if (nn < p.n) p.y[(size_t)m * p.n + nn] = __float2half_rn(sum);
-          }
+        for (int j = 0; j < NB; ++j) {
+          const int m = m0 + j;
+          if (m >= p.m) break;
+          float sum = 0.f;
+          for (int sp = 0; sp < S; ++sp) sum += __ldcg(p.partial + ((size_t)sp * p.m + m) * p.npad + n);
+          if (n < p.n) p.y[(size_t)m * p.n + n] = __float2half_rn(sum);
         }
         if (lane == 0) *ctr = 0u;
       }
@@ -400,7 +550,6 @@ static cudaError_t launch_nb(const CUtensorMap& tm, const TcParams& p, int nb, b
     }
   }
   switch (nb) {
-    case 16: return launch_cfg<BITS, 16, false>(tm, p, grid, pdl, st);
     case 64: return launch_cfg<BITS, 64, false>(tm, p, grid, pdl, st);
     case 128: return launch_cfg<BITS, 128, false>(tm, p, grid, pdl, st);
     case 256: return launch_cfg<BITS, 256, false>(tm, p, grid, pdl, st);
@@ -412,20 +561,11 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bit
                            bool pdl, cudaStream_t st) {
   switch (bits) {
     case 2: return launch_nb<2>(tmap_x, p, nb, post, grid, pdl, st);
+    case 3: return launch_nb<3>(tmap_x, p, nb, post, grid, pdl, st);
     case 4: return launch_nb<4>(tmap_x, p, nb, post, grid, pdl, st);
     case 8: return launch_nb<8>(tmap_x, p, nb, post, grid, pdl, st);
     default: return cudaErrorInvalidValue;
   }
-}
-
-size_t gemm_tc_smem_bytes(int bits, int nb, bool post) {
-  auto stage = [&](int wb) { return wb + nb * 128 + 128 + 256; };
-  const int wb = 128 * 64 * bits / 8;
-  const int budget = nb <= 64 ? 100 * 1024 : 200 * 1024;
-  int ns = budget / stage(wb);
-  ns = ns > 12 ? 12 : (ns < 3 ? 3 : ns);
-  (void)post;
-  return 1024 + (size_t)ns * stage(wb);
 }
 
 }  // namespace qfb

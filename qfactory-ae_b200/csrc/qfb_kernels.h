@@ -35,16 +35,17 @@ struct TcParams {
   float* partial;        // [S, m, npad] split-K partial sums
   unsigned* counters;    // [m tiles, n tiles] arrival counters, zero between launches
   unsigned* status;      // set to 1 when a bounded wait ran out
+  long long* dbg;        // optional cycle counters (timing builds only)
   int m, n, k, npad;
   int groups;
-  int kblocks;           // K / 64
-  int kb_per_group;      // group_size / 64 (kblocks when group-less)
+  int kblocks;               // K / 128 pipeline stages
+  int steps_per_group;       // group_size / 16 MMA k-steps per quantisation group (K / 16 when group-less)
+  int halfstages_per_group;  // group_size / 64
   uint32_t zconst;
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
 cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, dim3 grid,
                            bool pdl, cudaStream_t st);
-size_t gemm_tc_smem_bytes(int bits, int nb, bool post);
 
 struct PackParams {
   const int32_t* codes;   // [k, n]
