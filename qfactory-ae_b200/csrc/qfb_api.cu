@@ -188,7 +188,11 @@ static int choose_kernel(const LayerView& v, int m, unsigned flags) {
   if (flags & QFB_FLAG_FORCE_SIMT) return 1;
   if (!tc_supported(v)) return 1;
   if (flags & QFB_FLAG_FORCE_TENSOR) return 2;
-  return m >= g_tc_min_m ? 2 : 1;
+  if (m >= g_tc_min_m) return 2;
+  // a single activation row: the CUDA-core kernel wins while the packed weight is small
+  // (measured cross-over near 64 MB); above that the tensor-core pipeline is ahead
+  const double wbytes = (double)v.npad * v.k * v.bits / 8.0;
+  return wbytes >= 64.0 * 1024 * 1024 ? 2 : 1;
 }
 
 struct GemvPlan { int split, kways, mb; size_t smem; };
@@ -333,6 +337,7 @@ int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags) {
   LayerView v = {};
   v.bits = bits;
   v.k = k;
+  v.npad = padded_rows(n);
   return choose_kernel(v, m, flags);
 }
 

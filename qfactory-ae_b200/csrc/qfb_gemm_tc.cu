@@ -230,6 +230,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(p.qw) + ((size_t)tile * p.kblocks + kb0) * Cfg::kWBytes;
       int s = 0;
       uint32_t ph = 1;  // first pass over the ring: parity 1 of a fresh barrier passes at once
+      // group of the stage's first 64 k, tracked without divisions in the loop
+      const int hpg = p.halfstages_per_group;
+      int g0 = (kb0 * 2) / hpg, gpos = (kb0 * 2) % hpg;
+      const uint32_t ng = hpg == 1 ? 2u : 1u;
+      const uint32_t zb = has_z ? ng * 128u : 0u, sb = (!POST && has_s) ? ng * 256u : 0u;
       TT_DECL(2);
       TT_START();
       for (int i = 0; i < nkb; ++i) {
@@ -237,13 +242,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         TT_ADD(0);
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
-        const int g0 = ((kb0 + i) * 2) / p.halfstages_per_group;
-        const uint32_t ng = p.halfstages_per_group == 1 ? 2u : 1u;
-        const uint32_t zb = has_z ? ng * 128u : 0u, sb = (!POST && has_s) ? ng * 256u : 0u;
         mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
         tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)i * Cfg::kWBytes, Cfg::kWBytes, bar);
         if (zb) tma_bulk_g2s(sbase + z_off + s * Cfg::kZSlot, p.qz + ((size_t)tile * p.groups + g0) * kTileRows, zb, bar);
         if (sb) tma_bulk_g2s(sbase + s_off + s * Cfg::kSSlot, p.qs + ((size_t)tile * p.groups + g0) * kTileRows, sb, bar);
+        gpos += 2;
+        if (hpg == 1) { g0 += 2; gpos = 0; } else if (gpos >= hpg) { gpos = 0; ++g0; }
         if (++s == NS) { s = 0; ph ^= 1; }
         TT_ADD(1);
       }
@@ -292,11 +296,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         const uint32_t d_tmem = tmem_base + Cfg::kDBase + (POST ? r * NB : 0);
         const uint32_t xsm = sbase + x_off + xs * Cfg::kXBytes;
         const uint64_t bd0 = smem_desc_k_sw128(xsm), bd1 = smem_desc_k_sw128(xsm + NB * 128);
-#pragma unroll
-        for (int j = 0; j < kStepsPerStage; ++j) {
-          const uint32_t accumulate = POST ? (j != 0) : (i != 0 || j != 0);
-          mma_f16_ts(d_tmem, a_tmem + 8 * j, (j < 4 ? bd0 : bd1) + (uint64_t)(2 * (j & 3)), idesc, accumulate);
-        }
+        mma_f16_ts_stage8(d_tmem, a_tmem, (uint32_t)bd0, (uint32_t)bd1, (uint32_t)(bd0 >> 32), idesc,
+                          POST ? 0u : (i != 0 ? 1u : 0u));
         mma_commit(smem_u32(&bar_done[r]));
         TT_ADD(2);
       }
@@ -310,9 +311,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     // with groups of 64 the two halves of a stage belong to different groups: half h reads
     // the second record of the stage's zero / scale slot
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
-    int s = 0, r = 0, r_prev = 0, xrel = 0;
+    int s = 0, r = 0, xrel = 0;
     uint32_t phs = 0, phr = 1;
-    bool pending = false;
     TT_DECL(6);
     TT_START();
     for (int i = 0; i < nkb; ++i) {
@@ -334,15 +334,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
       TT_ADD(1);
-      if (pending) {  // publish the previous stage: its tensor-memory stores have had a stage to land
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r_prev]));
-      }
-      TT_ADD(2);
       // slot r was last read by the MMAs of stage i - R
-      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { pending = false; break; }
+      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) break;
       if (i >= R && warp == 4 && lane == 0) {  // ... whose activation tile is free as well: relay to its producer
         mbar_arrive(smem_u32(&bar_xempty[xrel]));
         if (++xrel == NX) xrel = 0;
@@ -352,19 +345,17 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + r * kAColsPerSlot + h * 32;
       tmem_st_x16(taddr, reinterpret_cast<const uint32_t(&)[16]>(rr[0]));
       tmem_st_x16(taddr + 16, reinterpret_cast<const uint32_t(&)[16]>(rr[16]));
-      pending = true;
-      r_prev = r;
+      // publish at once: the MMAs of this stage start a whole decode earlier than with a deferred
+      // hand-off, which matters more than the store latency exposed here (measured)
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r]));
       if (++s == NS) { s = 0; phs ^= 1; }
       if (++r == R) { r = 0; phr ^= 1; }
       TT_ADD(4);
     }
     if (warp == 4 && lane == 0) { TT_DUMP(16, 6); }
-    if (pending) {
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r_prev]));
-    }
     if (NX < R && warp == 4 && lane == 0) {
       // activation ring shallower than the slot ring: keep relaying the releases the loop
       // above did not reach, as long as the producer still has tiles to load
@@ -410,15 +401,17 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       TT_DECL(3);
       TT_START();
       // scales are fetched two stages ahead of their use
-      auto scale_of = [&](int i) -> __half {
-        if (!has_s || i >= nkb) return __ushort_as_half(0x3C00);
-        return p.qs[sz_row + (size_t)((kb0 + i) / stages_per_group) * kTileRows];
+      // group of stage kb0 + j, advanced without divisions: (gq, gr) = divmod(kb0 + j, stages_per_group)
+      int gq = (kb0 + 2) / stages_per_group, gr = (kb0 + 2) % stages_per_group;
+      auto scale_at = [&](int j, int grp) -> __half {
+        return (has_s && j < nkb) ? p.qs[sz_row + (size_t)grp * kTileRows] : __ushort_as_half(0x3C00);
       };
-      __half sc0 = scale_of(0), sc1 = scale_of(1);
+      __half sc0 = scale_at(0, kb0 / stages_per_group), sc1 = scale_at(1, (kb0 + 1) / stages_per_group);
       for (int i = 0; i < nkb; ++i) {
         const float sval = __half2float(sc0);
         sc0 = sc1;
-        sc1 = scale_of(i + 2);
+        sc1 = scale_at(i + 2, gq);
+        if (++gr == stages_per_group) { gr = 0; ++gq; }
         TT_ADD(0);
         if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { ok = false; break; }
         TT_ADD(1);

@@ -118,6 +118,38 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The eight k16 steps of one 128-k stage in a single block: A advances 8 columns per step,
+// B walks two 128-byte-swizzled 64-k atoms (descriptor low words b0_lo / b1_lo, +32 bytes per
+// step).  `first_accumulates` = 0 makes step 0 overwrite D.
+__device__ __forceinline__ void mma_f16_ts_stage8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b0_lo, uint32_t b1_lo,
+                                                  uint32_t b_hi, uint32_t idesc, uint32_t first_accumulates) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p0, p1;\n\t"
+      ".reg .b64 bd;\n\t"
+      ".reg .b32 a, bl;\n\t"
+      "setp.ne.b32 p0, %6, 0;\n\t"
+      "setp.eq.b32 p1, 0, 0;\n\t"
+      "mov.b64 bd, {%2, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %5, p0;\n\t"
+      "add.u32 a, %1, 8;\n\t  add.u32 bl, %2, 2;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 16;\n\t add.u32 bl, %2, 4;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 24;\n\t add.u32 bl, %2, 6;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 32;\n\t mov.b64 bd, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 40;\n\t add.u32 bl, %3, 2;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 48;\n\t add.u32 bl, %3, 4;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "add.u32 a, %1, 56;\n\t add.u32 bl, %3, 6;\n\t  mov.b64 bd, {bl, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %5, p1;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b0_lo), "r"(b1_lo), "r"(b_hi), "r"(idesc), "r"(first_accumulates)
+      : "memory");
+}
 // arrive on an mbarrier once every tcgen05 operation issued so far by this thread is done
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -68,23 +68,31 @@ def test_dequantised_weight_bit_exact(bits, sym):
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
+KERNEL_FLAGS = {"simt": _native.FLAG_FORCE_SIMT, "tensor": _native.FLAG_FORCE_TENSOR, "auto": 0}
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tensor"])
 @pytest.mark.parametrize("bits", [2, 3, 4, 8])
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16, 17])
-def test_forward_small_shapes(bits, M):
+def test_forward_small_shapes(bits, M, kernel):
     N, K, GS = 328, 1024, 128
     layer, x, q, s, z = _layer(N, K, bits, GS, False, seed=100 * bits + M, M=M)
+    layer.flags = KERNEL_FLAGS[kernel]
     y = layer(x.cuda())
+    assert _native.last_launch()["kernel"] == (1 if kernel == "simt" else 2)
     assert y.shape == (M, N) and y.dtype == torch.float16
     _check_output(y, x, q, s, z, bits)
 
 
 @pytest.mark.parametrize("bits", [2, 3, 4, 8])
-@pytest.mark.parametrize("GS,sym", [(128, True), (64 if True else 0, False), (256, False), (-1, False)])
-def test_forward_modes(bits, GS, sym):
+@pytest.mark.parametrize("GS,sym", [(128, True), (64, False), (256, False), (-1, False)])
+@pytest.mark.parametrize("kernel", ["simt", "tensor"])
+def test_forward_modes(bits, GS, sym, kernel):
     if bits == 3 and GS == 64:
         GS = 128
     N, K = 256, 2048
     layer, x, q, s, z = _layer(N, K, bits, GS, sym, seed=bits * 7 + (GS % 97), M=2)
+    layer.flags = KERNEL_FLAGS[kernel]
     y = layer(x.cuda())
     _check_output(y, x, q, s, z, bits)
 
@@ -166,6 +174,7 @@ def test_full_size_properties_mlp70b():
 def test_split_k_settings_agree(split, kways):
     N, K, bits, GS = 384, 4096, 4, 128
     layer, x, q, s, z = _layer(N, K, bits, GS, False, seed=9, M=3)
+    layer.flags = _native.FLAG_FORCE_SIMT
     L = _native.lib()
     try:
         L.qfb_set_gemv_tuning(split, kways)
@@ -217,11 +226,12 @@ def test_pdl_flag_gives_identical_results():
 def test_status_codes_on_device():
     L = _native.lib()
     layer, x, q, s, z = _layer(128, 4096, 4, 128, False, seed=1, M=1)
+    layer.flags = _native.FLAG_FORCE_SIMT
     xs = x.cuda()
     y = layer(xs)
     d = layer._desc
     # split-K needs a workspace
-    st = L.qfb_linear_forward(ctypes.byref(d), xs.data_ptr(), 1, y.data_ptr(), None, 0, 0, None)
+    st = L.qfb_linear_forward(ctypes.byref(d), xs.data_ptr(), 1, y.data_ptr(), None, 0, _native.FLAG_FORCE_SIMT, None)
     assert st == 5
     torch.cuda.synchronize()
 
