@@ -111,6 +111,24 @@ int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, v
                             void* x_staging, void* y_staging, void* workspace,
                             size_t workspace_bytes, unsigned flags, void* stream);
 
+/*
+ * The split-K GEMV for callers that cannot allocate device memory (a process whose device
+ * pool is owned elsewhere, code between the steps of a fixed schedule, an allocator-free
+ * plugin sandbox).  It has no counterpart in the reference.  Same computation as
+ * qfb_linear_forward on the CUDA-core kernel, but the split-K scratch is a fixed device array
+ * inside the library (qfb_static_scratch_capacity() bytes, 8 MiB, held by every GPU that loads
+ * the library until the process exits) instead of a caller workspace; the caller still passes
+ * x and y.  It calls no allocator.  Shapes whose scratch need exceeds the capacity return
+ * QFB_ERR_TOO_LARGE.  The first call on each device looks up the array's device address (with
+ * that device current); make that first call before any stream capture.  All calls on a device
+ * share the one array, which keeps the previous call's contents (the part that must start at
+ * zero is cleared on `stream` by each call): calls that overlap on the GPU race and must be
+ * serialised by the caller.
+ */
+int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* y, unsigned flags,
+                            void* stream);
+size_t qfb_static_scratch_capacity(void);
+
 /* Which kernel qfb_linear_forward picks: 1 = SIMT split-K GEMV, 2 = tcgen05 GEMM, 0 = invalid. */
 int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags);
 

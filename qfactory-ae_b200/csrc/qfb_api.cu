@@ -263,6 +263,22 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
   return QFB_OK;
 }
 
+// Exact scratch need of the CUDA-core split-K kernel for `m` rows under the built-in plan
+// (0 for invalid shapes); used by the allocation-free entry point.
+size_t gemv_scratch_bytes(int m, int n, int k, int bits) {
+  if (m <= 0 || validate_shape(n, k, bits, -1) != QFB_OK) return 0;
+  LayerView v = {};
+  v.n = n;
+  v.k = k;
+  v.bits = bits;
+  v.npad = padded_rows(n);
+  v.tiles = v.npad / kTileRows;
+  v.units = k / unit_k(bits);
+  const int rows = std::min(m, kMaxSimtRows);
+  const GemvPlan pl = plan_gemv(v, rows);
+  return partial_offset(v.tiles) + (size_t)pl.split * rows * v.npad * sizeof(float);
+}
+
 }  // namespace qfb
 
 using namespace qfb;

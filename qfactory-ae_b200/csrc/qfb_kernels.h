@@ -27,6 +27,9 @@ struct GemvParams {
 cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int block, size_t smem, bool pdl,
                         cudaStream_t st);
 
+// exact scratch bytes the split-K GEMV needs for m rows (0 when the shape is invalid)
+size_t gemv_scratch_bytes(int m, int n, int k, int bits);
+
 struct TcParams {
   const uint4* qw;
   const __half* qs;      // null: group-less (no scaling)

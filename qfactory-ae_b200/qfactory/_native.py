@@ -25,6 +25,7 @@ EXPORTS = (
     "qfb_linear_forward", "qfb_linear_forward_host", "qfb_select_kernel",
     "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_read_status",
     "qfb_pack", "qfb_unpack_codes", "qfb_dequantize",
+    "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
 )
 
 
@@ -93,6 +94,9 @@ def lib() -> ctypes.CDLL:
     L.qfb_unpack_codes.argtypes = [LP, vp, vp]
     L.qfb_dequantize.restype = i32
     L.qfb_dequantize.argtypes = [LP, vp, vp]
+    L.qfb_gemv_forward_static.restype = i32
+    L.qfb_gemv_forward_static.argtypes = [LP, vp, i32, vp, u32, vp]
+    L.qfb_static_scratch_capacity.restype = sz
     _lib = L
     return L
 
