@@ -78,7 +78,7 @@ static size_t counters_bytes(int tiles) {
 static size_t partial_offset(int tiles) { return kHeaderBytes + counters_bytes(tiles); }
 
 // ---- tensor-core path planning --------------------------------------------------------
-struct TcPlan { int nb, mtiles, split; bool post; };
+struct TcPlan { int nb, mtiles, split, dg; bool post; };
 
 static bool tc_supported(const LayerView& v) { return v.k % 128 == 0; }
 
@@ -87,13 +87,14 @@ static TcPlan plan_tc(const LayerView& v, int m) {
   pl.split = 1;
   // per-stage accumulators need quantisation groups made of whole 128-k stages
   const bool post_ok = v.group_size == -1 || v.group_size % 128 == 0;
+  pl.dg = 1;
   if (m <= 64) {
     // HBM-bound regime: split K until the SMs are covered
-    pl.post = post_ok;
-    pl.nb = !post_ok ? 64 : m <= 16 ? 16 : m <= 32 ? 32 : 64;
+    pl.post = post_ok && m <= 32;
+    pl.nb = !pl.post ? 64 : m <= 16 ? 16 : 32;
     pl.mtiles = 1;
     const int kblocks = v.k / 128;
-    const int target = kNumSMs * ((pl.post && pl.nb <= 16) ? 2 : 1);
+    const int target = kNumSMs * ((pl.post && pl.nb <= 16 && pl.dg == 1) ? 2 : 1);
     int split = std::max(1, target / v.tiles);
     split = std::min(split, std::max(1, kblocks / 4));
     split = std::min(split, 32);
@@ -179,9 +180,9 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   tl_last_launch[0] = 2;
   tl_last_launch[1] = grid.x * grid.y;
   tl_last_launch[2] = grid.z;
-  tl_last_launch[3] = 512;
+  tl_last_launch[3] = 256 + 256 * pl.dg;
   tl_last_launch[4] = pl.nb;
-  return check_cuda(launch_gemm_tc(tm, p, v.bits, pl.nb, pl.post, grid, (flags & QFB_FLAG_PDL) != 0, st));
+  return check_cuda(launch_gemm_tc(tm, p, v.bits, pl.nb, pl.post, pl.dg, grid, (flags & QFB_FLAG_PDL) != 0, st));
 }
 
 static int choose_kernel(const LayerView& v, int m, unsigned flags) {
@@ -202,7 +203,7 @@ static GemvPlan plan_gemv(const LayerView& v, int m_rows) {
   pl.mb = m_rows <= 1 ? 1 : m_rows <= 2 ? 2 : m_rows <= 4 ? 4 : 8;
   const int uk = unit_k(v.bits);
   int kways = g_tune_kways > 0 ? g_tune_kways : 2;
-  kways = std::max(1, std::min(kways, 4));
+  kways = std::max(1, std::min(kways, 2));  // the kernel is built for at most 256 threads
   // one register batch of units per thread: 8 vectors of 16 bytes in flight
   const int batch = v.bits == 3 ? 2 : v.bits == 2 ? 4 : 8;
   int split = g_tune_split > 0 ? g_tune_split : (v.units + batch * kways - 1) / (batch * kways);
@@ -240,6 +241,7 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
     p.groups = v.groups;
     p.units_per_group = v.units_per_group;
     p.max_units_per_cta = (v.units + pl.split - 1) / pl.split;
+    p.units_per_kway = (p.max_units_per_cta + pl.kways - 1) / pl.kways;
     p.zconst = v.zconst;
     p.partial = nullptr;
     p.counters = nullptr;

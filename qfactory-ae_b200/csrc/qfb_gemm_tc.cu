@@ -10,7 +10,7 @@
 //                     activation tile (two 128-byte-swizzled tensor boxes) -> two independent
 //                     shared-memory rings; the weight ring is released by the decode warps as
 //                     soon as the codes are in registers, the activation ring by MMA completion
-//   decode (8 warps)  packed codes -> exact (q - z) fp16 pairs in registers (LOP3 / PRMT magic
+//   decode (8 or 16 warps)  packed codes -> exact (q - z) fp16 pairs in registers (LOP3 / PRMT magic
 //                     numbers) -> tcgen05.st into TENSOR MEMORY as the A operand.  The fp16
 //                     weights never touch shared memory, whose bandwidth could not carry the
 //                     4x-expanded stream at HBM rate.  Thread (row, half) owns 64 codes of a stage.
@@ -48,39 +48,40 @@ using namespace ptx;
 #define TT_DUMP(base, n)
 #endif
 
-constexpr int kTcThreads = 512;
 constexpr int kStageK = 128;              // k per pipeline stage
 constexpr int kStepsPerStage = kStageK / 16;
 constexpr int kAColsPerSlot = kStageK / 2;  // one 32-bit column holds two fp16 k
 constexpr int kDecodeWarps = 8;
 
-template <int BITS, int NB, bool POST>
+// DG = decode groups: 1 -> 8 decode warps (512 threads, two CTAs per SM for the smallest batch
+// tile), 2 -> two groups of 8 decode warps that take alternate stages (768 threads, one CTA per SM).
+template <int BITS, int NB, bool POST, int DG>
 struct TcCfg {
+  static constexpr int kThreads = 128 + 256 * DG + 128;
+  static constexpr int kScaleWarp0 = 4 + 8 * DG;
   static constexpr int kWBytes = 128 * kStageK * BITS / 8;
   static constexpr int kXBytes = NB * kStageK * 2;
   static constexpr int kZSlot = 256;   // effective zeros of a stage: 128 rows x up to 2 groups
   static constexpr int kSSlot = 512;   // fp16 scales of a stage (PRE mode only)
   static constexpr int kQBytes = kZSlot + (POST ? 0 : kSSlot);
-#ifdef QFB_EXP_ONE_CTA
-  static constexpr bool kTwoPerSM = false;
-#else
-  static constexpr bool kTwoPerSM = POST && NB <= 16;   // smallest batches: two CTAs share an SM
-#endif
+  static constexpr bool kTwoPerSM = POST && NB <= 16 && DG == 1;   // smallest batches: two CTAs share an SM
   static constexpr int kBudget = kTwoPerSM ? 98 * 1024 : 224 * 1024;
   static constexpr int kXStages = NB <= 16 ? 6 : NB <= 32 ? 8 : NB <= 64 ? 6 : NB <= 128 ? 4 : (BITS == 8 ? 2 : 3);
   static constexpr int kWStagesRaw = (kBudget - kXStages * kXBytes) / (kWBytes + kQBytes);
-  static constexpr int kWStages = kWStagesRaw > 10 ? 10 : kWStagesRaw;
+  static constexpr int kWStages = kWStagesRaw > 16 ? 16 : kWStagesRaw;
   static constexpr int kTmemCols = kTwoPerSM ? 256 : 512;
   // ring of R slots in tensor memory: A operand (64 columns) + in POST mode one accumulator each
   static constexpr int kSlotCols = kAColsPerSlot + (POST ? NB : 0);
-  static constexpr int kRingRaw = (kTmemCols - (POST ? 0 : NB)) / kSlotCols;
-  static constexpr int kRing = kRingRaw > 6 ? 6 : kRingRaw;
+  // PRE mode with skinny MMAs (N <= 128) is issue-bound too: two issuers, one accumulator each
+  static constexpr int kIssuers = POST ? 2 : (NB <= 128 ? 2 : 1);
+  static constexpr int kRingRaw = (kTmemCols - (POST ? 0 : kIssuers * NB)) / kSlotCols;
+  static constexpr int kRingCap = kXStages < 6 ? kXStages : 6;   // never deeper than the activation ring
+  static constexpr int kRing = kRingRaw > kRingCap ? kRingCap : kRingRaw;
   static constexpr int kDBase = kRing * kAColsPerSlot;
-  static constexpr int kIssuers = POST ? 2 : 1;
   static constexpr size_t kSmemBytes = 1024 + (size_t)kXStages * kXBytes + (size_t)kWStages * (kWBytes + kQBytes);
   static_assert(kWStages >= 2, "weight ring too shallow");
   static_assert(kRing >= 2, "need at least two tensor-memory slots");
-  static_assert(kDBase + (POST ? kRing * NB : NB) <= kTmemCols, "tensor memory over-subscribed");
+  static_assert(kDBase + (POST ? kRing * NB : kIssuers * NB) <= kTmemCols, "tensor memory over-subscribed");
 };
 
 // ---- decode of the 64 codes thread (row, h) owns in a 128-k stage -> 32 fp16 pairs ------
@@ -165,17 +166,17 @@ template <> struct StageDecode<3> {
   }
 };
 
-template <int BITS, int NB, bool POST>
-__global__ void __launch_bounds__(kTcThreads, (TcCfg<BITS, NB, POST>::kTwoPerSM ? 2 : 1))
+template <int BITS, int NB, bool POST, int DG>
+__global__ void __launch_bounds__(TcCfg<BITS, NB, POST, DG>::kThreads, (TcCfg<BITS, NB, POST, DG>::kTwoPerSM ? 2 : 1))
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
-  using Cfg = TcCfg<BITS, NB, POST>;
+  using Cfg = TcCfg<BITS, NB, POST, DG>;
   constexpr int NS = Cfg::kWStages;   // weight ring
   constexpr int NX = Cfg::kXStages;   // activation ring
   constexpr int R = Cfg::kRing;       // tensor-memory slot ring
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_wfull[NS], bar_wempty[NS], bar_xfull[NX], bar_xempty[NX];
-  __shared__ uint64_t bar_afull[R], bar_done[R], bar_dempty[R];
+  __shared__ uint64_t bar_afull[R], bar_done[R], bar_dempty[R], bar_final;
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -195,7 +196,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(smem_u32(&bar_wfull[i]), 1);
-      mbar_init(smem_u32(&bar_wempty[i]), kDecodeWarps);
+      mbar_init(smem_u32(&bar_wempty[i]), kDecodeWarps);  // the eight warps of the group that decodes the stage
     }
     for (int i = 0; i < NX; ++i) {
       mbar_init(smem_u32(&bar_xfull[i]), 1);
@@ -206,6 +207,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       mbar_init(smem_u32(&bar_done[i]), 1);
       mbar_init(smem_u32(&bar_dempty[i]), 4);
     }
+    mbar_init(smem_u32(&bar_final), Cfg::kIssuers);
     abort_flag = 0;
     fence_barrier_init();
   }
@@ -274,7 +276,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     __syncwarp();
   } else if (warp == 1 || (warp == 2 && Cfg::kIssuers == 2)) {
     // ------------------------------ MMA issuer(s) -----------------------------
-    // POST: issuer e takes stages e, e+2, ...; every stage has its own accumulator.
+    // Issuer e takes stages e, e + kIssuers, ...  POST: every stage has its own accumulator.
+    // PRE: every issuer has its own accumulator over all its stages; the epilogue adds them.
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_f16_m128(NB);
       const int e = (warp == 1) ? 0 : 1;
@@ -293,29 +296,32 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         }
         tc_fence_after();
         const uint32_t a_tmem = tmem_base + r * kAColsPerSlot;
-        const uint32_t d_tmem = tmem_base + Cfg::kDBase + (POST ? r * NB : 0);
+        const uint32_t d_tmem = tmem_base + Cfg::kDBase + (POST ? r * NB : e * NB);
         const uint32_t xsm = sbase + x_off + xs * Cfg::kXBytes;
         const uint64_t bd0 = smem_desc_k_sw128(xsm), bd1 = smem_desc_k_sw128(xsm + NB * 128);
         mma_f16_ts_stage8(d_tmem, a_tmem, (uint32_t)bd0, (uint32_t)bd1, (uint32_t)(bd0 >> 32), idesc,
-                          POST ? 0u : (i != 0 ? 1u : 0u));
+                          POST ? 0u : (i >= Cfg::kIssuers ? 1u : 0u));
         mma_commit(smem_u32(&bar_done[r]));
         TT_ADD(2);
       }
+      mma_commit(smem_u32(&bar_final));  // every MMA this thread issued is complete
       if (e == 0) { TT_DUMP(8, 5); }
     }
     __syncwarp();
-  } else if (warp >= 4 && warp < 4 + kDecodeWarps) {
+  } else if (warp >= 4 && warp < Cfg::kScaleWarp0) {
     // ------------------------------ decode warps ------------------------------
-    const int q = warp & 3, h = (warp - 4) >> 2;
+    // group `grp` takes stages grp, grp + DG, ...; inside a group thread (row, h) owns 64 codes
+    const int grp = (warp - 4) >> 3;
+    const int q = warp & 3, h = ((warp - 4) >> 2) & 1;
     const int row = q * 32 + lane;
     // with groups of 64 the two halves of a stage belong to different groups: half h reads
     // the second record of the stage's zero / scale slot
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
-    int s = 0, r = 0, xrel = 0;
-    uint32_t phs = 0, phr = 1;
     TT_DECL(6);
     TT_START();
-    for (int i = 0; i < nkb; ++i) {
+    for (int i = grp; i < nkb; i += DG) {
+      const int s = i % NS, r = i % R;
+      const uint32_t phs = (uint32_t)(i / NS) & 1u, phr = ((uint32_t)(i / R) & 1u) ^ 1u;
       if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp)) break;
       TT_ADD(0);
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qsel + row] : p.zconst;
@@ -336,40 +342,26 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       TT_ADD(1);
       // slot r was last read by the MMAs of stage i - R
       if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) break;
-      if (i >= R && warp == 4 && lane == 0) {  // ... whose activation tile is free as well: relay to its producer
-        mbar_arrive(smem_u32(&bar_xempty[xrel]));
-        if (++xrel == NX) xrel = 0;
-      }
+      // ... and the activation tile of that stage is free as well: tell its producer.  The
+      // decode warps cannot fall behind the commits (the MMAs need their stores), so this
+      // relay never misses a phase; R <= NX makes it reach every tile that is still needed.
+      if (i >= R && (warp & 7) == 4 && lane == 0) mbar_arrive(smem_u32(&bar_xempty[(i - R) % NX]));
       TT_ADD(3);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + r * kAColsPerSlot + h * 32;
       tmem_st_x16(taddr, reinterpret_cast<const uint32_t(&)[16]>(rr[0]));
       tmem_st_x16(taddr + 16, reinterpret_cast<const uint32_t(&)[16]>(rr[16]));
+      TT_ADD(4);
       // publish at once: the MMAs of this stage start a whole decode earlier than with a deferred
       // hand-off, which matters more than the store latency exposed here (measured)
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r]));
-      if (++s == NS) { s = 0; phs ^= 1; }
-      if (++r == R) { r = 0; phr ^= 1; }
-      TT_ADD(4);
+      TT_ADD(5);
     }
     if (warp == 4 && lane == 0) { TT_DUMP(16, 6); }
-    if (NX < R && warp == 4 && lane == 0) {
-      // activation ring shallower than the slot ring: keep relaying the releases the loop
-      // above did not reach, as long as the producer still has tiles to load
-      for (int i = nkb; i < nkb + R && (i - R) + NX < nkb; ++i) {
-        if (i >= R) {
-          if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) break;
-          mbar_arrive(smem_u32(&bar_xempty[xrel]));
-          if (++xrel == NX) xrel = 0;
-        }
-        if (++r == R) { r = 0; phr ^= 1; }
-      }
-    }
-    __syncwarp();
-  } else if (warp >= 12) {
+  } else if (warp >= Cfg::kScaleWarp0) {
     // ------------------------------ scale / epilogue warps --------------------
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -424,45 +416,41 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 #pragma unroll
           for (int c = 0; c < CH; c += 16) tmem_ld_x16(taddr + c0 + c, reinterpret_cast<uint32_t(&)[16]>(v[c]));
           tmem_wait_ld();
+          TT_ADD(2);
           if (c0 + CH == NB) {  // the accumulator is free as soon as its last chunk is in registers
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_dempty[r]));
           }
+          TT_ADD(3);
 #pragma unroll
           for (int j = 0; j < CH; ++j) acc[c0 + j] = fmaf(sval, __uint_as_float(v[j]), acc[c0 + j]);
         }
         if (++r == R) { r = 0; phr ^= 1; }
-        TT_ADD(2);
+        TT_ADD(4);
       }
-      if (warp == 12 && lane == 0) { TT_DUMP(24, 3); }
+      if (warp == Cfg::kScaleWarp0 && lane == 0) { TT_DUMP(24, 5); }
       if (ok) {
         grid_dependency_wait();  // y and the workspace may still be in use by the preceding kernel
 #pragma unroll
         for (int c = 0; c < NB; c += 16) store_chunk(c, &acc[c]);
       }
     } else {
-      // follow the stage commits in order; the last one covers every MMA of this CTA
-      {
-        int r = 0;
-        uint32_t phr = 0;
-        for (int i = 0; i < nkb; ++i) {
-          if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { ok = false; break; }
-          if (++r == R) { r = 0; phr ^= 1; }
-        }
-      }
+      ok = mbar_wait(smem_u32(&bar_final), 0, abortp);
       if (ok) {
         tc_fence_after();
         grid_dependency_wait();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase;
+        const bool two = Cfg::kIssuers == 2 && nkb >= 2;  // the second accumulator holds something
 #pragma unroll 1
         for (int c = 0; c < NB; c += 16) {
-          uint32_t v[16];
+          uint32_t v[16], v2[16];
           tmem_ld_x16(taddr + c, v);
+          if (two) tmem_ld_x16(taddr + NB + c, v2);
           tmem_wait_ld();
           float f[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]) + (two ? __uint_as_float(v2[j]) : 0.f);
           store_chunk(c, f);
         }
         tc_fence_before();
@@ -508,10 +496,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
-template <int BITS, int NB, bool POST>
+template <int BITS, int NB, bool POST, int DG>
 static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
-  using Cfg = TcCfg<BITS, NB, POST>;
-  auto kern = qgemm_tc_kernel<BITS, NB, POST>;
+  using Cfg = TcCfg<BITS, NB, POST, DG>;
+  auto kern = qgemm_tc_kernel<BITS, NB, POST, DG>;
   static bool configured = false;  // per instantiation
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
@@ -520,7 +508,7 @@ static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 gri
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kTcThreads);
+  cfg.blockDim = dim3(Cfg::kThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -531,34 +519,41 @@ static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 gri
   return cudaLaunchKernelEx(&cfg, kern, tm, p);
 }
 
-template <int BITS>
+template <int BITS, int DG>
 static cudaError_t launch_nb(const CUtensorMap& tm, const TcParams& p, int nb, bool post, dim3 grid, bool pdl,
                              cudaStream_t st) {
   if (post) {
     switch (nb) {
-      case 16: return launch_cfg<BITS, 16, true>(tm, p, grid, pdl, st);
-      case 32: return launch_cfg<BITS, 32, true>(tm, p, grid, pdl, st);
-      case 64: return launch_cfg<BITS, 64, true>(tm, p, grid, pdl, st);
+      case 16: return launch_cfg<BITS, 16, true, DG>(tm, p, grid, pdl, st);
+      case 32: return launch_cfg<BITS, 32, true, DG>(tm, p, grid, pdl, st);
       default: return cudaErrorInvalidValue;
     }
   }
   switch (nb) {
-    case 64: return launch_cfg<BITS, 64, false>(tm, p, grid, pdl, st);
-    case 128: return launch_cfg<BITS, 128, false>(tm, p, grid, pdl, st);
-    case 256: return launch_cfg<BITS, 256, false>(tm, p, grid, pdl, st);
+    case 64: return launch_cfg<BITS, 64, false, DG>(tm, p, grid, pdl, st);
+    case 128: return launch_cfg<BITS, 128, false, DG>(tm, p, grid, pdl, st);
+    case 256: return launch_cfg<BITS, 256, false, DG>(tm, p, grid, pdl, st);
     default: return cudaErrorInvalidValue;
   }
 }
 
-cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, dim3 grid,
-                           bool pdl, cudaStream_t st) {
+template <int DG>
+static cudaError_t launch_bits(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, dim3 grid,
+                               bool pdl, cudaStream_t st) {
   switch (bits) {
-    case 2: return launch_nb<2>(tmap_x, p, nb, post, grid, pdl, st);
-    case 3: return launch_nb<3>(tmap_x, p, nb, post, grid, pdl, st);
-    case 4: return launch_nb<4>(tmap_x, p, nb, post, grid, pdl, st);
-    case 8: return launch_nb<8>(tmap_x, p, nb, post, grid, pdl, st);
+    case 2: return launch_nb<2, DG>(tmap_x, p, nb, post, grid, pdl, st);
+    case 3: return launch_nb<3, DG>(tmap_x, p, nb, post, grid, pdl, st);
+    case 4: return launch_nb<4, DG>(tmap_x, p, nb, post, grid, pdl, st);
+    case 8: return launch_nb<8, DG>(tmap_x, p, nb, post, grid, pdl, st);
     default: return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,
+                           dim3 grid, bool pdl, cudaStream_t st) {
+  // two decode groups (768 threads, one CTA per SM) measured no faster than one: not instantiated
+  (void)decode_groups;
+  return launch_bits<1>(tmap_x, p, bits, nb, post, grid, pdl, st);
 }
 
 }  // namespace qfb

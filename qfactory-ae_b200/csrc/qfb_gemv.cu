@@ -12,9 +12,11 @@
 // workspace and are summed in split order by the last CTA of the tile to arrive
 // (deterministic, no atomics on data, counters reset themselves).
 //
-// Numerics.  (q - z) is exact in fp16, the scale multiply rounds once (bit-identical to the
-// reference dequantisation), products are accumulated in fp16x2 chains of at most 8 terms
-// which are flushed into fp32 accumulators.
+// Numerics.  (q - z) is exact in fp16; x * (q - z) is accumulated in fp16x2 chains of at most 8
+// terms, flushed into an fp32 sum per quantisation group, and the group sum is multiplied by the
+// scale once, in fp32 (the reference's "deferred decode", qfactory/include/utils.h:193-213, with
+// fp32 instead of fp16 group sums).  fp16x2 arithmetic issues at half rate on B200, so every
+// fp16 instruction removed from the inner loop counts double.
 //
 // Ordering under programmatic dependent launch: weight, scale and zero loads (which never
 // depend on the preceding kernel) are issued first; activations, the workspace and the
@@ -25,7 +27,7 @@
 namespace qfb {
 
 template <int BITS, int MB, int U>
-__global__ void __launch_bounds__(512) gemv_splitk_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(256, (MB <= 2 ? 3 : 2)) gemv_splitk_kernel(const GemvParams p) {
   using G = Geo<BITS>;
   using C = Codec<BITS>;
   constexpr int XV = G::kUnitK / 8;  // uint4 (8 halfs) of activations per unit
@@ -41,29 +43,43 @@ __global__ void __launch_bounds__(512) gemv_splitk_kernel(const GemvParams p) {
   const int split = blockIdx.x;
   const int S = gridDim.x;
 
-  const int ub = (int)(((long long)split * p.units) / S);
-  const int ue = (int)(((long long)(split + 1) * p.units) / S);
+  // unit range of the CTA and of this thread's k-way (no divisions: the host passes the strides)
+  const int ub = min(split * p.max_units_per_cta, p.units);
+  const int ue = min(ub + p.max_units_per_cta, p.units);
   const int ncta = ue - ub;
-  const int tb = ub + (kw * ncta) / KW;
-  const int te = ub + ((kw + 1) * ncta) / KW;
+  const int tb = min(ub + kw * p.units_per_kway, ue);
+  const int te = min(tb + p.units_per_kway, ue);
 
   const uint4* wrow = p.qw + ((size_t)tile * p.units * NV) * kTileRows + r;
-  const size_t sz_base = (size_t)tile * p.groups * kTileRows + r;
+  const __half* srow = p.qs + (size_t)tile * p.groups * kTileRows + r;
+  const uint8_t* zrow = p.qz + (size_t)tile * p.groups * kTileRows + r;
+
+  // position of unit `tb` inside its quantisation group (one division per thread)
+  int g_load = tb / p.units_per_group;
+  int gpos_load = tb - g_load * p.units_per_group;
 
   uint4 wv[U][NV];
   __half sc[U];
   uint32_t zr[U];
+  bool newg[U];
 
   auto load_batch = [&](int base) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int un = base + u;
+      newg[u] = false;
       if (un < te) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) wv[u][v] = ldg_stream_v4(wrow + ((size_t)un * NV + v) * kTileRows);
-        const int g = un / p.units_per_group;
-        sc[u] = p.qs ? p.qs[sz_base + (size_t)g * kTileRows] : __ushort_as_half(0x3C00);
-        zr[u] = p.qz ? (uint32_t)p.qz[sz_base + (size_t)g * kTileRows] : p.zconst;
+        newg[u] = (u == 0) || (gpos_load == 0);
+        if (newg[u]) {  // first unit of a group (or of the batch): fetch the group's scale and zero
+          sc[u] = p.qs ? srow[(size_t)g_load * kTileRows] : __ushort_as_half(0x3C00);
+          zr[u] = p.qz ? (uint32_t)zrow[(size_t)g_load * kTileRows] : p.zconst;
+        }
+        if (++gpos_load == p.units_per_group) {
+          gpos_load = 0;
+          ++g_load;
+        }
       }
     }
   };
@@ -89,38 +105,45 @@ __global__ void __launch_bounds__(512) gemv_splitk_kernel(const GemvParams p) {
   }
   __syncthreads();
 
-  float acc[MB];
+  // acc: fp32 results; gacc: fp32 sum of x * (q - z) over the current group, scaled once per group
+  float acc[MB], gacc[MB];
 #pragma unroll
-  for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+  for (int m = 0; m < MB; ++m) acc[m] = gacc[m] = 0.f;
+  float s_cur = 0.f;
+  typename C::ZM zm = C::zmagic(0);
 
   for (int base = tb; base < te; base += U) {
     if (base != tb) load_batch(base);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (base + u < te) {
-        const typename C::ZM zm = C::zmagic(zr[u]);
-        const __half2 s2 = __half2half2(sc[u]);
+        if (newg[u]) {
+#pragma unroll
+          for (int m = 0; m < MB; ++m) {
+            acc[m] = fmaf(s_cur, gacc[m], acc[m]);
+            gacc[m] = 0.f;
+          }
+          s_cur = __half2float(sc[u]);
+          zm = C::zmagic(zr[u]);
+        }
         const uint4* xs = smem + (base + u - ub) * XV;
         __half2 a0[MB], a1[MB];
 #pragma unroll
         for (int m = 0; m < MB; ++m) a0[m] = a1[m] = __half2half2(__ushort_as_half(0));
         C::unit(wv[u], zm, [&](int j8, __half2(&d)[4]) {
-          __half2 w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) w[i] = __hmul2(d[i], s2);
 #pragma unroll
           for (int m = 0; m < MB; ++m) {
             const uint4 xv = xs[m * xs_stride + j8];
-            a0[m] = __hfma2(w[0], as_h2(xv.x), a0[m]);
-            a1[m] = __hfma2(w[1], as_h2(xv.y), a1[m]);
-            a0[m] = __hfma2(w[2], as_h2(xv.z), a0[m]);
-            a1[m] = __hfma2(w[3], as_h2(xv.w), a1[m]);
+            a0[m] = __hfma2(d[0], as_h2(xv.x), a0[m]);
+            a1[m] = __hfma2(d[1], as_h2(xv.y), a1[m]);
+            a0[m] = __hfma2(d[2], as_h2(xv.z), a0[m]);
+            a1[m] = __hfma2(d[3], as_h2(xv.w), a1[m]);
           }
-          if ((j8 & 3) == 3 || j8 == XV - 1) {  // flush the fp16 chains (<= 8 terms each)
+          if ((j8 & 3) == 3 || j8 == XV - 1) {  // flush the fp16 chains (<= 8 terms each) into fp32
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
               const float2 f = __half22float2(__hadd2(a0[m], a1[m]));
-              acc[m] += f.x + f.y;
+              gacc[m] += f.x + f.y;
               a0[m] = a1[m] = __half2half2(__ushort_as_half(0));
             }
           }
@@ -128,6 +151,8 @@ __global__ void __launch_bounds__(512) gemv_splitk_kernel(const GemvParams p) {
       }
     }
   }
+#pragma unroll
+  for (int m = 0; m < MB; ++m) acc[m] = fmaf(s_cur, gacc[m], acc[m]);
 
   // combine the k-ways of this CTA
   __syncthreads();  // everyone is done reading the activation stage

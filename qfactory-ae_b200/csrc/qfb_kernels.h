@@ -20,7 +20,8 @@ struct GemvParams {
   int units;             // K / unit_k(bits)
   int groups;            // K / group_size (1 when group-less)
   int units_per_group;
-  int max_units_per_cta; // ceil(units / S)
+  int max_units_per_cta; // ceil(units / S): unit stride between K splits
+  int units_per_kway;    // ceil(max_units_per_cta / k-ways): unit stride between the k-ways of a CTA
   uint32_t zconst;
 };
 
@@ -47,8 +48,8 @@ struct TcParams {
   uint32_t zconst;
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
-cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, dim3 grid,
-                           bool pdl, cudaStream_t st);
+cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,
+                           dim3 grid, bool pdl, cudaStream_t st);
 
 struct PackParams {
   const int32_t* codes;   // [k, n]

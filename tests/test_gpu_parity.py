@@ -170,7 +170,7 @@ def test_full_size_properties_mlp70b():
     assert np.abs(got - want).max() <= TOL * float(scale)
 
 
-@pytest.mark.parametrize("split,kways", [(1, 1), (2, 2), (5, 1), (16, 2), (64, 4), (1000, 2)])
+@pytest.mark.parametrize("split,kways", [(1, 1), (2, 2), (5, 1), (16, 2), (64, 1), (1000, 2)])
 def test_split_k_settings_agree(split, kways):
     N, K, bits, GS = 384, 4096, 4, 128
     layer, x, q, s, z = _layer(N, K, bits, GS, False, seed=9, M=3)
