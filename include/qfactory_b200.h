@@ -141,6 +141,8 @@ int qfb_read_status(const void* workspace, void* stream, unsigned* status_out);
 /* Debug / tuning override of the split-K heuristic of the SIMT kernel: split_k <= 0 and
  * k_ways <= 0 restore the built-in choice.  Process-wide, not thread-safe. */
 void qfb_set_gemv_tuning(int split_k, int k_ways);
+/* Tuning override of the tensor-core kernel's split-K factor for batches <= 64 (0 = built-in). */
+void qfb_set_tensor_split(int split_k);
 /* The configuration the last qfb_linear_forward of this thread used (for reports). */
 void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes);
 

@@ -16,6 +16,7 @@ static thread_local int tl_last_cuda_error = 0;
 static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
 static int g_tune_split = 0, g_tune_kways = 0;
 static int g_tc_min_m = 2;  // smallest batch routed to the tensor-core kernel
+static int g_tc_split = 0;  // tuning override of the tensor-core split-K factor (0 = built-in)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -98,6 +99,12 @@ static TcPlan plan_tc(const LayerView& v, int m) {
     int split = std::max(1, target / v.tiles);
     split = std::min(split, std::max(1, kblocks / 4));
     split = std::min(split, 32);
+    // measured: the wider the batch tile, the dearer a split (partials, reduce, per-CTA fill);
+    // beyond 8 rows it only pays while the tiles alone leave most SMs idle or K is very long
+    if (pl.nb == 16 && m > 8 && v.tiles >= 90) split = 1;
+    if (pl.nb == 32 && kblocks < 80) split = 1;
+    if (pl.nb == 64 && kblocks < 160) split = 1;
+    if (g_tc_split > 0) split = std::min(g_tc_split, std::max(1, kblocks));
     if (v.tiles > 512) split = 1;  // the counter array holds 512 tiles x 4 row quarters
     pl.split = split;
   } else {
@@ -375,6 +382,8 @@ void qfb_set_gemv_tuning(int split_k, int k_ways) {
   g_tune_split = split_k;
   g_tune_kways = k_ways;
 }
+
+void qfb_set_tensor_split(int split_k) { g_tc_split = split_k > 0 ? split_k : 0; }
 
 void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes) {
   if (kernel) *kernel = tl_last_launch[0];

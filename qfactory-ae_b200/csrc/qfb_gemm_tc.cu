@@ -467,11 +467,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       prev = __shfl_sync(0xffffffffu, prev, 0);
       if (prev == (unsigned)(S - 1)) {
         __threadfence();
+        // eight independent loads in flight per step; the additions stay in split order
+        const size_t sstride = (size_t)p.m * p.npad;
         for (int j = 0; j < NB; ++j) {
           const int m = m0 + j;
           if (m >= p.m) break;
+          const float* base = p.partial + (size_t)m * p.npad + n;
           float sum = 0.f;
-          for (int sp = 0; sp < S; ++sp) sum += __ldcg(p.partial + ((size_t)sp * p.m + m) * p.npad + n);
+          int sp = 0;
+          for (; sp + 8 <= S; sp += 8) {
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = __ldcg(base + (size_t)(sp + u) * sstride);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) sum += t[u];
+          }
+          for (; sp < S; ++sp) sum += __ldcg(base + (size_t)sp * sstride);
           if (n < p.n) p.y[(size_t)m * p.n + n] = __float2half_rn(sum);
         }
         if (lane == 0) *ctr = 0u;

@@ -200,8 +200,19 @@ __global__ void __launch_bounds__(256, (MB <= 2 ? 3 : 2)) gemv_splitk_kernel(con
 #pragma unroll
     for (int m = 0; m < MB; ++m) {
       if (m < p.m) {
+        // eight independent loads in flight per step; the additions stay in split order
+        const float* base = p.partial + (size_t)m * p.npad + n;
+        const size_t sstride = (size_t)p.m * p.npad;
         float s = 0.f;
-        for (int sp = 0; sp < S; ++sp) s += __ldcg(p.partial + ((size_t)sp * p.m + m) * p.npad + n);
+        int sp = 0;
+        for (; sp + 8 <= S; sp += 8) {
+          float t[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) t[u] = __ldcg(base + (size_t)(sp + u) * sstride);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) s += t[u];
+        }
+        for (; sp < S; ++sp) s += __ldcg(base + (size_t)sp * sstride);
         if (n < p.n) p.y[(size_t)m * p.n + n] = __float2half_rn(s);
       }
     }
