@@ -181,6 +181,9 @@ def main():
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("QFB_BENCH_PDL", "0")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-shape", type=int, default=1)
+    ap.add_argument("--decode", type=int, default=int(os.environ.get("QFB_BENCH_DECODE", "1")),
+                    help="also report decode tok/s of the Llama-2-70B-architecture decoder, tensor-parallel over the ranks")
+    ap.add_argument("--decode-batch", type=int, default=1)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -336,6 +339,33 @@ def main():
                 per_shape.append({"layer": name, "N": N, "K": K, "M": M, "us": round(med * 1e3, 2),
                                   "GBps": round(nb / (med * 1e-3) / 1e9, 1), "launch": _native.last_launch()})
 
+    # free the sweep's device memory before the decoder is built
+    case_meta = [(M, layer.out_features, layer.in_features) for _, M, layer, *_ in cases[0]]
+    del graphs, sub_graphs, cases
+    torch.cuda.empty_cache()
+
+    # secondary figure: decode tokens/s of the random-init Llama-2-70B-architecture decoder,
+    # all linears W4A16 g128, prompt 128 then 256 greedy steps, tensor-parallel over the ranks
+    decode = None
+    if args.decode and 8 % world == 0:
+        try:
+            from qfactory.decoder import DecoderConfig, QuantDecoder, run_decode
+
+            cfg = DecoderConfig()
+            model = QuantDecoder(cfg, world=world, rank=rank, device=dev, batch=args.decode_batch)
+            sec, _ = run_decode(model, prompt_len=128, steps=256)
+            dt = torch.tensor([sec], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            sec = float(dt[0])
+            decode = {"model": "llama2-70b-architecture random init, W4A16 g128", "tp": world, "batch": args.decode_batch,
+                      "prompt": 128, "steps": 256, "tok_per_s": 256 * args.decode_batch / sec,
+                      "ms_per_step": sec / 256 * 1e3, "collective": "nccl all_reduce after O and down" if world > 1 else "none"}
+            del model
+            torch.cuda.empty_cache()
+        except Exception as e:  # the headline line must not depend on the secondary figure
+            decode = {"error": str(e)[:200]}
+
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -352,7 +382,7 @@ def main():
         shares = {}
         for kid, kms in kernel_ms.items():
             idx = [ci for ci in range(n_cases) if kern_of[ci] == kid]
-            kb = sum(algorithmic_bytes(cases[0][ci][1], cases[0][ci][2].out_features, cases[0][ci][2].in_features) for ci in idx)
+            kb = sum(algorithmic_bytes(*case_meta[ci]) for ci in idx)
             shares[kid] = {"kernel": names.get(kid, str(kid)), "launches_per_step": len(idx), "ms_per_step": kms,
                            "bytes_per_step": kb, "GBps": kb / (kms * 1e-3) / 1e9}
         dom = max(shares, key=lambda k: shares[k]["ms_per_step"])
@@ -376,6 +406,7 @@ def main():
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "avg_launch_us": per_launch_s * 1e6, "traffic": None},
             "per_shape": per_shape,
+            "decode": decode,
         }
         out["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
         if world == 1 and not args.no_cpu_baseline:
