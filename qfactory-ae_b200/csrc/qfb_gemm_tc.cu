@@ -52,6 +52,15 @@ constexpr int kStageK = 128;              // k per pipeline stage
 constexpr int kStepsPerStage = kStageK / 16;
 constexpr int kAColsPerSlot = kStageK / 2;  // one 32-bit column holds two fp16 k
 constexpr int kDecodeWarps = 8;
+// sleep between polls of a barrier that is not ready yet, per role (ns)
+#ifndef QFB_SLEEP_SCALE
+#define QFB_SLEEP_SCALE 100
+#define QFB_SLEEP_PRODUCER 100
+#define QFB_SLEEP_MMA 20
+#define QFB_SLEEP_DECODE 20
+#endif
+constexpr unsigned kSleepScale = QFB_SLEEP_SCALE, kSleepProducer = QFB_SLEEP_PRODUCER, kSleepMma = QFB_SLEEP_MMA,
+                   kSleepDecode = QFB_SLEEP_DECODE;
 
 // DG = decode groups: 1 -> 8 decode warps (512 threads, two CTAs per SM for the smallest batch
 // tile), 2 -> two groups of 8 decode warps that take alternate stages (768 threads, one CTA per SM).
@@ -240,7 +249,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       TT_DECL(2);
       TT_START();
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp)) break;
+        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp, kSleepProducer)) break;
         TT_ADD(0);
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
@@ -264,7 +273,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       int s = 0;
       uint32_t ph = 1;
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(smem_u32(&bar_xempty[s]), ph, abortp)) break;
+        if (!mbar_wait(smem_u32(&bar_xempty[s]), ph, abortp, kSleepProducer)) break;
         const uint32_t bar = smem_u32(&bar_xfull[s]);
         const uint32_t dst = sbase + x_off + s * Cfg::kXBytes;
         mbar_arrive_expect_tx(bar, Cfg::kXBytes);
@@ -286,12 +295,12 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       for (int i = e; i < nkb; i += Cfg::kIssuers) {
         const int xs = i % NX, r = i % R;
         const uint32_t phx = (uint32_t)(i / NX) & 1u, phr = (uint32_t)(i / R) & 1u;
-        if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp)) break;
+        if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp, kSleepMma)) break;
         TT_ADD(0);
-        if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp)) break;
+        if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp, kSleepMma)) break;
         TT_ADD(1);
         if (POST) {
-          if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp)) break;
+          if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp, kSleepMma)) break;
           TT_ADD(3);
         }
         tc_fence_after();
@@ -319,10 +328,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
     TT_DECL(6);
     TT_START();
+    static_assert(DG == 1, "ring positions below advance by one stage per iteration");
+    int s = 0, r = 0, xrel = 0;
+    uint32_t phs = 0, phr = 1;  // no divisions in the loop: every integer op here competes with the decode
     for (int i = grp; i < nkb; i += DG) {
-      const int s = i % NS, r = i % R;
-      const uint32_t phs = (uint32_t)(i / NS) & 1u, phr = ((uint32_t)(i / R) & 1u) ^ 1u;
-      if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp)) break;
+      if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode)) break;
       TT_ADD(0);
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qsel + row] : p.zconst;
       __half2 d[32];
@@ -341,11 +351,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
       TT_ADD(1);
       // slot r was last read by the MMAs of stage i - R
-      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) break;
+      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepDecode)) break;
       // ... and the activation tile of that stage is free as well: tell its producer.  The
       // decode warps cannot fall behind the commits (the MMAs need their stores), so this
       // relay never misses a phase; R <= NX makes it reach every tile that is still needed.
-      if (i >= R && (warp & 7) == 4 && lane == 0) mbar_arrive(smem_u32(&bar_xempty[(i - R) % NX]));
+      if (i >= R && (warp & 7) == 4 && lane == 0) {
+        mbar_arrive(smem_u32(&bar_xempty[xrel]));
+        if (++xrel == NX) xrel = 0;
+      }
       TT_ADD(3);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + r * kAColsPerSlot + h * 32;
@@ -358,6 +371,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r]));
+      if (++s == NS) { s = 0; phs ^= 1u; }
+      if (++r == R) { r = 0; phr ^= 1u; }
       TT_ADD(5);
     }
     if (warp == 4 && lane == 0) { TT_DUMP(16, 6); }
@@ -405,7 +420,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         sc1 = scale_at(i + 2, gq);
         if (++gr == stages_per_group) { gr = 0; ++gq; }
         TT_ADD(0);
-        if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepScale)) { ok = false; break; }
         TT_ADD(1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase + r * NB;
@@ -436,7 +451,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         for (int c = 0; c < NB; c += 16) store_chunk(c, &acc[c]);
       }
     } else {
-      ok = mbar_wait(smem_u32(&bar_final), 0, abortp);
+      ok = mbar_wait(smem_u32(&bar_final), 0, abortp, 500);
       if (ok) {
         tc_fence_after();
         grid_dependency_wait();

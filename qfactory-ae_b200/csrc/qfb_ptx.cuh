@@ -42,11 +42,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after ~1 s of polling (or as soon as another thread of the CTA
 // has given up), raising *abort_flag so every role of the CTA drains and exits.
 constexpr long long kWaitLimitCycles = 2000000000LL;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// `backoff_ns` > 0 puts the warp to sleep between attempts: a polling warp otherwise spends
+// issue slots and ALU-pipe cycles that the decode warps of the same SM need (measured: idle
+// roles polled away more instructions than the decode itself executed).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((++it & 15) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
