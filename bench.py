@@ -178,12 +178,17 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--pdl", type=int, default=int(os.environ.get("QFB_BENCH_PDL", "0")))
+    ap.add_argument("--pdl", type=int, default=int(os.environ.get("QFB_BENCH_PDL", "1")),
+                    help="launch with programmatic stream serialisation (weights prefetch under the previous kernel's tail)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-shape", type=int, default=1)
     ap.add_argument("--decode", type=int, default=int(os.environ.get("QFB_BENCH_DECODE", "1")),
                     help="also report decode tok/s of the Llama-2-70B-architecture decoder, tensor-parallel over the ranks")
     ap.add_argument("--decode-batch", type=int, default=1)
+    ap.add_argument("--case", default="", help="profiling aid: run ONE layer NxKxM a few times (4 weight replicas in "
+                    "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
+    ap.add_argument("--reps", type=int, default=8)
+    ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -200,6 +205,8 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     _native.lib()  # fail loudly if the native library is missing
+    if os.environ.get("QFB_TC_MIN_M"):  # tuning experiments only
+        _native.lib().qfb_set_tensor_min_batch(int(os.environ["QFB_TC_MIN_M"]))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -208,6 +215,27 @@ def main():
     REPL = 2
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     flags = _native.FLAG_PDL if args.pdl else 0
+    if args.force:
+        flags |= _native.FLAG_FORCE_SIMT if args.force == "simt" else _native.FLAG_FORCE_TENSOR
+
+    if args.case:
+        N, K, M = (int(v) for v in args.case.lower().split("x"))
+        layers = []
+        for _ in range(4):
+            L = QLinear.empty(max(M, 16), K, N, BITS, GS, sym=False, device=dev)
+            L.w.random_(-128, 127)
+            L.s.uniform_(0.002, 0.02)
+            L.z.random_(0, 15)
+            L.flags = flags
+            layers.append(L)
+        x = torch.randn(M, K, device=dev).half()
+        y = torch.empty(M, N, dtype=torch.float16, device=dev)
+        for i in range(args.reps):
+            layers[i % 4](x, out=y)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": args.case, "reps": args.reps, "launch": _native.last_launch(),
+                          "algorithmic_bytes": algorithmic_bytes(M, N, K)}))
+        return
 
     def make_layer(N, K):
         L = QLinear.empty(16, K, N, BITS, GS, sym=False, device=dev)

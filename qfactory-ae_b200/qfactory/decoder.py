@@ -18,6 +18,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from . import _native
 from .parallel import all_reduce_sum
 from .qlinear import QLinear
 
@@ -46,6 +47,8 @@ def _random_layer(K, N, bits, gs, device, gen):
     # small scales keep the residual stream of a random-weight network finite
     L.s.copy_((torch.rand(L.s.shape, generator=gen, device=device) * 2e-4 + 1e-4).half())
     L.z.copy_(torch.randint(7, 10, L.z.shape, generator=gen, dtype=torch.int8, device=device))
+    # programmatic dependent launch: the layer's weight prefetch overlaps the tail of whatever ran before
+    L.flags = _native.FLAG_PDL
     return L
 
 
