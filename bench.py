@@ -37,9 +37,11 @@ BATCHES = [1, 4, 16]
 BITS, GS = 4, 128
 METRIC = "w4a16_g128_gemv_achieved_hbm_bandwidth"
 UNIT = "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, averaged over
-# the sweep, from the ncu capture summarised under profiles/ (None until one has been taken)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (qgemm_tc_kernel):
+# the ncu capture of the (22016,4096) M=4 case moved 1.00592 x its algorithmic bytes; traffic
+# grows with the weight bytes, so the sweep's average launch (26,614,016 algorithmic bytes)
+# is scaled by the same factor
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 26771537
 WORKLOAD = "llama7b_layer_sweep_w4a16_g128_asym: (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)} x M in {1,4,16}"
 
 
