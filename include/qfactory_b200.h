@@ -23,6 +23,14 @@
  * Inside a 32-bit word the 2/4-bit fields are pair-interleaved (even elements in the low
  * half-word, odd ones in the high half-word) so that one LOP3 yields an fp16x2 pair.
  *
+ * Second packed layout ("fragment", QFB_LAYOUT_FRAGMENT, 4-bit layers with K % 128 == 0):
+ * the same bytes permuted so that one 32-bit word is the A fragment one thread feeds to the
+ * warp-level tensor-core instruction (rows g and g+8 of a 16-row block, four k each):
+ *   qweight  u32 [Npad/128][2 x 64 rows][K/16][32 lanes][4 row blocks]
+ *   scales / zeros  [Npad/128][K/group][128] in fragment row order
+ * It is the layout of choice for layers that mostly see batches of at most 16 rows (decode);
+ * larger batches on such a layer are processed 16 rows at a time.
+ *
  * Zero-point semantics follow the reference packer and kernel: the stored, effective
  * zero is min(z + 1, 2^bits - 1) for GPTQ-convention zeros z
  * (reference: qfactory/convert.py:76, qfactory/include/utils.h:53-60); symmetric layers
@@ -58,6 +66,10 @@ typedef enum qfb_status {
 #define QFB_FLAG_FORCE_SIMT 2u   /* always use the CUDA-core split-K kernel */
 #define QFB_FLAG_FORCE_TENSOR 4u /* always use the tcgen05 kernel (if the shape allows) */
 
+/* packed layouts */
+#define QFB_LAYOUT_TILE 0      /* tile-128 interleaved: every bit width, every batch size */
+#define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: 4-bit, K % 128 == 0, small batches */
+
 /* One packed layer.  Plain data; the caller owns the device buffers. */
 typedef struct qfb_layer {
   const void* qweight;   /* packed codes, 16-byte aligned */
@@ -67,6 +79,7 @@ typedef struct qfb_layer {
   int32_t k;             /* in_features */
   int32_t bits;          /* 2, 3, 4 or 8 */
   int32_t group_size;    /* multiple of 64 dividing k, or -1 for group-less */
+  int32_t layout;        /* QFB_LAYOUT_TILE or QFB_LAYOUT_FRAGMENT */
 } qfb_layer;
 
 /* Library / layout version (major*100 + minor). */
@@ -129,7 +142,8 @@ int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* 
                             void* stream);
 size_t qfb_static_scratch_capacity(void);
 
-/* Which kernel qfb_linear_forward picks: 1 = SIMT split-K GEMV, 2 = tcgen05 GEMM, 0 = invalid. */
+/* Which kernel qfb_linear_forward picks for a tile-layout layer: 1 = SIMT split-K GEMV,
+ * 2 = tcgen05 GEMM, 0 = invalid.  Fragment-layout layers always run kernel 3 (mma.sync GEMV). */
 int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags);
 
 /* Smallest batch that is routed to the tensor-core kernel (default 2).  Process-wide. */
@@ -157,6 +171,12 @@ void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int*
 int qfb_pack(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k,
              int bits, int group_size, void* qweight_out, void* scales_out, void* zeros_out,
              void* stream);
+
+/* qfb_pack into the given layout; 1 when the layout can hold the shape, else 0. */
+int qfb_pack_layout(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k,
+                    int bits, int group_size, int layout, void* qweight_out, void* scales_out,
+                    void* zeros_out, void* stream);
+int qfb_layout_supported(int layout, int n, int k, int bits, int group_size);
 
 /* Inverse of the code packing through the kernels' own bit-extraction path:
  * writes i32 codes [k, n].  Used by the bit-exactness tests. */

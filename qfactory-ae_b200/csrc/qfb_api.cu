@@ -11,6 +11,7 @@ namespace qfb {
 constexpr int kNumSMs = 148;
 constexpr size_t kCounterAlign = 256;
 constexpr int kMaxSimtRows = 8;  // activation rows one SIMT launch handles
+constexpr int kMaxMmaRows = 16;  // activation rows one mma.sync GEMV launch handles
 
 static thread_local int tl_last_cuda_error = 0;
 static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
@@ -39,10 +40,21 @@ static int validate_shape(int n, int k, int bits, int group_size) {
   return QFB_OK;
 }
 
+static int validate_layout(int layout, int k, int bits, int group_size) {
+  if (layout == QFB_LAYOUT_TILE) return QFB_OK;
+  if (layout != QFB_LAYOUT_FRAGMENT) return QFB_ERR_UNSUPPORTED;
+  if (bits != 4) return QFB_ERR_UNSUPPORTED;
+  if (group_size != -1 && group_size != 64 && group_size % 128 != 0) return QFB_ERR_BAD_SHAPE;
+  return k % 128 == 0 ? QFB_OK : QFB_ERR_BAD_SHAPE;
+}
+
 static int make_view(const qfb_layer* L, LayerView* v) {
   if (!L || !L->qweight) return QFB_ERR_NULL_POINTER;
   int st = validate_shape(L->n, L->k, L->bits, L->group_size);
   if (st != QFB_OK) return st;
+  st = validate_layout(L->layout, L->k, L->bits, L->group_size);
+  if (st != QFB_OK) return st;
+  v->layout = L->layout;
   if (L->group_size == -1 && (L->scales || L->zeros)) return QFB_ERR_BAD_SHAPE;
   if (L->group_size != -1 && !L->scales) return QFB_ERR_NULL_POINTER;
   if (!aligned16(L->qweight) || !aligned16(L->scales) || !aligned16(L->zeros)) return QFB_ERR_MISALIGNED;
@@ -272,6 +284,99 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
   return QFB_OK;
 }
 
+// ---- mma.sync GEMV over the fragment layout ---------------------------------------------
+struct MmaPlan { int nt, split, kways; size_t smem; };
+
+static int mma_split_cap(int tiles, int batches) {
+  return std::max(1, std::min(batches, (kNumSMs * 4 + tiles - 1) / tiles));
+}
+
+static size_t mma_smem(int rows, int nt, int bpc, int kways) {
+  const size_t stage = (size_t)rows * (bpc * 128 + 16) * 2 + (size_t)bpc * 2 * 8 * nt * sizeof(float);
+  const size_t red = (size_t)kways * rows * 132 * sizeof(float);
+  return std::max(stage, red);
+}
+
+// Split-K factor and k-ways of the mma.sync GEMV.  Model fitted to measurements: the CTAs of a
+// launch should be resident at once (a second wave costs a full CTA time), a CTA costs its longest
+// k-way plus a fixed part worth ~1.5 batches, and SMs hold 16 warps of this kernel.
+static MmaPlan plan_mma(int tiles, int k, int rows) {
+  MmaPlan pl;
+  pl.nt = rows <= 8 ? 1 : 2;
+  const int batches = k / 128;
+  const int wpk = pl.nt == 1 ? 2 : 4;       // warps per k-way: 2 x 64 rows (m <= 8) or 4 x 32 rows
+  const int kways_max = pl.nt == 1 ? 4 : 2;  // at most 256 threads
+  const int cap = mma_split_cap(tiles, batches);
+  const size_t smem_max = 100 * 1024;
+  int best_s = cap, best_kw = 1;
+  double best_cost = 1e30;
+  for (int kw = kways_max; kw >= 1; kw >>= 1) {
+    if (g_tune_kways > 0 && kw != std::min(g_tune_kways, kways_max)) continue;
+    for (int s = 1; s <= cap; ++s) {
+      if (g_tune_split > 0 && s != std::min(g_tune_split, cap)) continue;
+      const int bpc = (batches + s - 1) / s;
+      const size_t smem = mma_smem(rows, pl.nt, bpc, kw);
+      if (smem > smem_max && s < cap) continue;
+      // CTAs resident per SM: 16 warps of 128 registers per thread, and the shared memory
+      const int resident = std::max(1, std::min(16 / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
+      const int slots = kNumSMs * resident;
+      const int per_kway = (bpc + kw - 1) / kw;
+      const int waves = (tiles * s + slots - 1) / slots;
+      const double cost = (double)waves * (per_kway + 1.5) + 0.05 * s + 0.01 * (kways_max - kw);
+      if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; }
+    }
+  }
+  pl.split = best_s;
+  const int bpc = (batches + best_s - 1) / best_s;
+  pl.kways = std::max(1, std::min(best_kw, batches / best_s > 0 ? batches / best_s : 1));
+  pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
+  return pl;
+}
+
+static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
+                   unsigned flags, cudaStream_t st) {
+  for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
+    const int rows = std::min(kMaxMmaRows, m - m0);
+    const MmaPlan pl = plan_mma(v.tiles, v.k, rows);
+    if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
+    MmaParams p;
+    p.qw = v.qw;
+    p.qs = v.qs;
+    p.qz = v.qz;
+    p.x = x + (size_t)m0 * v.k;
+    p.y = y + (size_t)m0 * v.n;
+    p.m = rows;
+    p.n = v.n;
+    p.k = v.k;
+    p.npad = v.npad;
+    p.ksteps = v.k / 16;
+    p.groups = v.groups;
+    p.chunks_per_group = (v.group_size == -1 ? v.k : v.group_size) / 64;
+    p.batches = v.k / 128;
+    p.batches_per_cta = (p.batches + pl.split - 1) / pl.split;
+    p.zconst = v.zconst;
+    p.partial = nullptr;
+    p.counters = nullptr;
+    if (pl.split > 1) {
+      const size_t off = partial_offset(v.tiles);
+      const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);
+      if (!workspace || ws_bytes < need) return QFB_ERR_WORKSPACE;
+      p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
+      p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
+    }
+    const dim3 grid(pl.split, v.tiles);
+    const int block = (pl.nt == 1 ? 64 : 128) * pl.kways;
+    tl_last_launch[0] = 3;
+    tl_last_launch[1] = grid.x;
+    tl_last_launch[2] = grid.y;
+    tl_last_launch[3] = block;
+    tl_last_launch[4] = (int)pl.smem;
+    int stt = check_cuda(launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st));
+    if (stt != QFB_OK) return stt;
+  }
+  return QFB_OK;
+}
+
 // Exact scratch need of the CUDA-core split-K kernel for `m` rows under the built-in plan
 // (0 for invalid shapes); used by the allocation-free entry point.
 size_t gemv_scratch_bytes(int m, int n, int k, int bits) {
@@ -347,6 +452,10 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
       }
     }
   }
+  if (bits == 4 && k % 128 == 0) {  // fragment-layout layers: the mma.sync GEMV's split bound
+    const size_t rows_mma = (size_t)std::min(m_max, kMaxMmaRows);
+    partial = std::max(partial, (size_t)mma_split_cap(tiles, k / 128) * rows_mma * npad * sizeof(float));
+  }
   return partial_offset(tiles) + partial;
 }
 
@@ -402,6 +511,9 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
   if (m == 0) return QFB_OK;
   if (!x || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  if (v.layout == QFB_LAYOUT_FRAGMENT)
+    return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                   static_cast<cudaStream_t>(stream));
   if (choose_kernel(v, m, flags) == 2)
     return run_tc(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                   static_cast<cudaStream_t>(stream));
@@ -424,9 +536,22 @@ int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, v
   return check_cuda(cudaStreamSynchronize(st));
 }
 
+int qfb_layout_supported(int layout, int n, int k, int bits, int group_size) {
+  return validate_shape(n, k, bits, group_size) == QFB_OK && validate_layout(layout, k, bits, group_size) == QFB_OK;
+}
+
 int qfb_pack(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k, int bits,
              int group_size, void* qweight_out, void* scales_out, void* zeros_out, void* stream) {
+  return qfb_pack_layout(codes, scales, zeros, n, k, bits, group_size, QFB_LAYOUT_TILE, qweight_out, scales_out,
+                         zeros_out, stream);
+}
+
+int qfb_pack_layout(const int32_t* codes, const void* scales, const int32_t* zeros, int n, int k, int bits,
+                    int group_size, int layout, void* qweight_out, void* scales_out, void* zeros_out,
+                    void* stream) {
   int st = validate_shape(n, k, bits, group_size);
+  if (st != QFB_OK) return st;
+  st = validate_layout(layout, k, bits, group_size);
   if (st != QFB_OK) return st;
   if (!codes || !qweight_out) return QFB_ERR_NULL_POINTER;
   if (group_size != -1 && (!scales || !scales_out)) return QFB_ERR_NULL_POINTER;
@@ -448,6 +573,7 @@ int qfb_pack(const int32_t* codes, const void* scales, const int32_t* zeros, int
   p.tiles = p.npad / kTileRows;
   p.units = k / unit_k(bits);
   p.groups = group_size == -1 ? 1 : k / group_size;
+  p.layout = layout;
   return check_cuda(launch_pack(p, static_cast<cudaStream_t>(stream)));
 }
 
@@ -470,6 +596,7 @@ static int run_unpack(const qfb_layer* layer, int32_t* codes_out, void* w_out, v
   p.groups = v.groups;
   p.units_per_group = v.units_per_group;
   p.zconst = v.zconst;
+  p.layout = v.layout;
   return check_cuda(launch_unpack(p, static_cast<cudaStream_t>(stream)));
 }
 

@@ -184,6 +184,30 @@ template <> struct Codec<3> {
   }
 };
 
+// ---------------------------------------------------------------------------
+// Fragment layout (4-bit).  One 32-bit word is the A fragment one thread feeds to
+// mma.sync.m16n8k16 (weights on the M side): for lane (g = lane / 4, t = lane % 4) of a
+// 16-row block it holds rows g and g + 8 at k = 4t .. 4t+3 of a 16-k step:
+//   nibble 0: (g, 4t)    nibble 4: (g, 4t+1)    nibble 2: (g, 4t+2)    nibble 6: (g, 4t+3)
+//   nibble 1: (g+8, 4t)  nibble 5: (g+8, 4t+1)  nibble 3: (g+8, 4t+2)  nibble 7: (g+8, 4t+3)
+// so four ANDs (and one shift) yield the four fragment registers.  A masked nibble is the
+// fp16 subnormal q * 2^-24 (bits 0-3 of a half: rows g) or q * 2^-20 (bits 4-7: rows g + 8).
+//   qweight  u32 [N/128][2 halves of 64 rows][K/16 steps][32 lanes][4 row blocks]
+//   scales   f16 [N/128][K/group][128]   position wt*64 + g*8 + rb*2 + h  <->  row wt*64 + rb*16 + h*8 + g
+//   zeros    u8  the same order
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void frag4_fields(uint32_t w, uint32_t (&a)[4]) {
+  const uint32_t hi = w >> 8;
+  a[0] = w & 0x000f000fu;
+  a[1] = w & 0x00f000f0u;
+  a[2] = hi & 0x000f000fu;
+  a[3] = hi & 0x00f000f0u;
+}
+// row inside the 128-row tile held at position `pos` of the fragment-ordered scale / zero arrays
+__host__ __device__ inline int frag_row_of_pos(int pos) {
+  return (pos >> 6) * 64 + ((pos >> 1) & 3) * 16 + (pos & 1) * 8 + ((pos >> 3) & 7);
+}
+
 // Host-visible description of a validated layer (filled by the API layer).
 struct LayerView {
   const uint4* qw;
@@ -192,6 +216,7 @@ struct LayerView {
   int n, k, bits, group_size;
   int npad, tiles, units, groups, units_per_group;
   uint32_t zconst;      // zero used when qz == null
+  int layout;           // QFB_LAYOUT_TILE / QFB_LAYOUT_FRAGMENT
 };
 
 }  // namespace qfb

@@ -1,0 +1,376 @@
+// Split-K GEMV / skinny GEMM for batches of at most 16 activation rows on the warp-level
+// tensor-core instruction (mma.sync m16n8k16), reading the "fragment" packed layout.
+//
+// Replaces the reference's kernel_gptq / kernel_gemv templates
+// (qfactory/include/gptq_gemv.h:14-154, qfactory/include/gemv.h:12-94) for 4-bit layers.
+//
+// Why a third kernel.  On B200 the fp16x2 CUDA-core instructions and the integer/logic pipe both
+// issue at half rate, so a CUDA-core GEMV that spends LOP3 + HSUB2 + HFMA2 per code pair is
+// bound by instruction issue at about a third of the HBM rate.  Here the dot product moves to
+// the tensor core and the zero-point subtraction moves out of the inner loop:
+//
+//   * the 16 weight rows of a row block are the M side of the MMA, the (at most 8) activation
+//     rows its N side, so one 32-bit word of eight 4-bit codes is exactly one thread's A
+//     fragment (rows g and g+8, four k each) and costs one shift and four AND instructions;
+//   * a masked nibble is used AS IT IS as an fp16 bit pattern: the subnormal q * 2^-24 (nibble at
+//     bits 0-3 of a half) or q * 2^-20 (bits 4-7).  The tensor core multiplies subnormals
+//     exactly and accumulates in fp32; the two powers of two belong to different ROWS (g and
+//     g+8), so they are folded into the row's scale;
+//   * per quantisation group  sum_k x_k (q_k - z) s = s * sum_k x_k q_k - s z * sum_k x_k :
+//     the first sum is the MMA accumulator, sum_k x_k is computed once per CTA by MMAs whose
+//     A fragment is all ones, and both products are applied in fp32 once per group.
+//
+// Mapping.  A CTA owns one 128-row tile and a range of 128-k batches; warp (wt, kw) owns the
+// 64-row half wt and the k-way kw of that range.  One 128-bit load per thread brings the words
+// of four row blocks for one 16-k step, so consecutive steps of a warp are consecutive 512-byte
+// runs.  Partial sums of the k-ways are combined in shared memory, those of the K splits
+// through the fp32 workspace by the last CTA of the tile to arrive, in split order
+// (deterministic; the counters reset themselves).
+//
+// Ordering under programmatic dependent launch: weight, scale and zero loads are issued before
+// griddepcontrol.wait; activations, workspace and output are only touched after it.
+#include "qfb_common.cuh"
+#include "qfb_kernels.h"
+
+namespace qfb {
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+constexpr int kRedStride = 132;  // floats per (k-way, batch row) line of the k-way reduction
+
+// first MMA of a segment: the accumulator starts from zero
+__device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// the RB words (row blocks) of one lane and k-step: RB = 4 reads the lane's whole 16 bytes,
+// RB = 2 its lower or upper 8 bytes
+template <int RB> struct Words;
+template <> struct Words<4> {
+  uint32_t v[4];
+  __device__ __forceinline__ void load(const void* p) {
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(p));
+  }
+};
+template <> struct Words<2> {
+  uint32_t v[2];
+  __device__ __forceinline__ void load(const void* p) {
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "l"(p));
+  }
+};
+
+// raw scales (one half2 = rows g, g+8 per row block) and zeros (one byte per row) of a thread's rows
+template <int RB> struct ScaleZero {
+  uint32_t s[RB];
+  uint32_t z[RB / 2];
+  __device__ __forceinline__ void load(const __half* qs, const uint8_t* qz, size_t o) {
+    if (RB == 4) {
+      if (qs) { const uint4 v = ldg_v4(qs + o); s[0] = v.x; s[1] = v.y; s[RB - 2] = v.z; s[RB - 1] = v.w; }
+      if (qz) { const uint2 v = ldg_v2(qz + o); z[0] = v.x; z[RB / 2 - 1] = v.y; }
+    } else {
+      if (qs) { const uint2 v = ldg_v2(qs + o); s[0] = v.x; s[1] = v.y; }
+      if (qz) z[0] = __ldg(reinterpret_cast<const unsigned*>(qz + o));
+    }
+  }
+};
+
+// NT    = number of 8-column batch tiles (m <= 8 * NT)
+// RB    = 16-row blocks per warp: 4 (a warp owns 64 rows) or 2 (32 rows, two batches in flight)
+// SEG64 = quantisation groups of 64 (a segment = 4 k-steps) instead of >= 128 (8 k-steps)
+// A segment is the run of k-steps whose MMA accumulator is folded into the results at once
+// with one scale and zero per row: min(group, 128) k.
+template <int NT, int RB, bool SEG64>
+__global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
+  constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
+  constexpr int NSEG = SEG64 ? 2 : 1;  // segments per 128-k batch
+  constexpr int NSLOT = 4 / RB;        // register buffers of one batch each
+  constexpr int WPK = 8 / RB;          // warps per k-way: 128 rows / (16 * RB)
+  extern __shared__ uint4 smem[];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int wt = warp & 1;                    // 64-row half of the tile
+  const int sub = (warp >> 1) & (WPK / 2 - 1);  // which RB row blocks of that half (RB = 2 only)
+  const int kw = warp / WPK;
+  const int KW = (blockDim.x >> 5) / WPK;
+  const int tile = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+
+  // balanced ranges of 128-k batches: CTA [bb, be), this warp's k-way [wb, we)
+  const int bb = (int)(((long long)split * p.batches) / S);
+  const int be = (int)(((long long)(split + 1) * p.batches) / S);
+  const int ncta = be - bb;
+  const int wb = bb + (kw * ncta) / KW;
+  const int we = bb + ((kw + 1) * ncta) / KW;
+
+  // 16 bytes per lane and k-step; this warp reads bytes [sub * 8, sub * 8 + 4 * RB) of them
+  const char* wp = reinterpret_cast<const char*>(p.qw) +
+                   (((size_t)(tile * 2 + wt) * p.ksteps + (size_t)wb * 8) * 32 + lane) * 16 + sub * 8;
+  constexpr int kStepBytes = 32 * 16, kBatchBytes = 8 * kStepBytes;
+
+  // quantisation group of the warp's first segment, and the position inside it
+  const int segs_per_group = SEG64 ? p.chunks_per_group : (p.chunks_per_group >> 1);
+  int grp = (wb * NSEG) / segs_per_group;
+  int gpos = wb * NSEG - grp * segs_per_group;
+  const int grp_last = (we * NSEG - 1) / segs_per_group;  // last group this warp touches
+
+  ScaleZero<RB> sz_cur, sz_nxt;
+#pragma unroll
+  for (int i = 0; i < RB; ++i) sz_cur.s[i] = sz_nxt.s[i] = 0;
+#pragma unroll
+  for (int i = 0; i < RB / 2; ++i) sz_cur.z[i] = sz_nxt.z[i] = 0;
+  auto sz_offset = [&](int gi) { return (((size_t)tile * p.groups + gi) * 2 + wt) * 64 + g * 8 + sub * 4; };
+
+  Words<RB> w[NSLOT][8];
+#pragma unroll
+  for (int sl = 0; sl < NSLOT; ++sl)
+    if (wb + sl < we) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[sl][i].load(wp + sl * kBatchBytes + i * kStepBytes);
+    }
+  wp += NSLOT * kBatchBytes;  // from here on: the batch NSLOT ahead of the one being processed
+  if (wb < we) {
+    sz_cur.load(p.qs, p.qz, sz_offset(grp));
+    if (grp < grp_last) sz_nxt.load(p.qs, p.qz, sz_offset(grp + 1));
+  }
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  // ---- stage the CTA's activation slice (plain 16-byte asynchronous copies) -----------------
+  const int xstride = p.batches_per_cta * 128 + 16;  // halfs; +16 keeps the fragment loads conflict-free
+  __half* x_s = reinterpret_cast<__half*>(smem);
+  {
+    const int nvec_row = ncta * 16;
+    for (int m = 0; m < p.m; ++m) {
+      const __half* src = p.x + (size_t)m * p.k + (size_t)bb * 128;
+      __half* dst = x_s + (size_t)m * xstride;
+      for (int j = tid; j < nvec_row; j += blockDim.x) cp_async_16(dst + j * 8, src + j * 8);
+    }
+    cp_async_commit_wait_all();
+  }
+  __syncthreads();
+
+  // activation row each batch tile of this thread reads (rows >= m repeat the last valid row;
+  // their output columns are never stored)
+  const __half* xrow[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) xrow[nt] = x_s + (size_t)min(g + 8 * nt, p.m - 1) * xstride + 4 * t;
+
+  // ---- sum of the activations over every segment of the slice: an MMA whose A fragment is all
+  // ones yields, in every row, the column sums of the B fragment.  The warps share the segments.
+  float* xsum_s = reinterpret_cast<float*>(x_s + (size_t)p.m * xstride);  // [segments][8 * NT]
+  {
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};  // fp16 1.0
+    const int nwarps = blockDim.x >> 5;
+    for (int sg = warp; sg < ncta * NSEG; sg += nwarps) {
+      float dx[NT][4];
+#pragma unroll
+      for (int k4 = 0; k4 < KS; ++k4) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint2 v = *reinterpret_cast<const uint2*>(xrow[nt] + (sg * KS + k4) * 16);
+          if (k4 == 0) mma_m16n8k16_zero(dx[nt], ones, v.x, v.y);
+          else mma_m16n8k16(dx[nt], ones, v.x, v.y);
+        }
+      }
+      if (g == 0) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          *reinterpret_cast<float2*>(xsum_s + sg * (8 * NT) + nt * 8 + 2 * t) = make_float2(dx[nt][0], dx[nt][1]);
+      }
+    }
+  }
+  __syncthreads();
+
+  float acc[RB][NT][4];
+#pragma unroll
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[rb][nt][i] = 0.f;
+
+  const float zc = (float)p.zconst;
+
+  for (int b0 = wb; b0 < we; b0 += NSLOT) {
+#pragma unroll
+    for (int sl = 0; sl < NSLOT; ++sl) {
+      const int b = b0 + sl;
+      if (b >= we) break;
+      const int lb = b - bb;
+      const bool more = b + NSLOT < we;
+#pragma unroll
+      for (int seg = 0; seg < NSEG; ++seg) {
+        float d[RB][NT][4];
+#pragma unroll
+        for (int k4 = 0; k4 < KS; ++k4) {
+          const int ks = seg * KS + k4;
+          uint32_t bf[NT][2];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint2 v = *reinterpret_cast<const uint2*>(xrow[nt] + lb * 128 + ks * 16);
+            bf[nt][0] = v.x;
+            bf[nt][1] = v.y;
+          }
+#pragma unroll
+          for (int rb = 0; rb < RB; ++rb) {
+            uint32_t a[4];
+            frag4_fields(w[sl][ks].v[rb], a);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              if (k4 == 0) mma_m16n8k16_zero(d[rb][nt], a, bf[nt][0], bf[nt][1]);
+              else mma_m16n8k16(d[rb][nt], a, bf[nt][0], bf[nt][1]);
+            }
+          }
+          // the words of this k-step are consumed: fetch the same step of a later batch into them
+          if (more) w[sl][ks].load(wp + ks * kStepBytes);
+        }
+        // fold the segment's accumulators into the results: s * 2^24 * D - s * z * sum(x)
+        float dx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const float2 v = *reinterpret_cast<const float2*>(xsum_s + (lb * NSEG + seg) * (8 * NT) + nt * 8 + 2 * t);
+          dx[nt][0] = v.x;
+          dx[nt][1] = v.y;
+        }
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+          float2 sf = make_float2(1.f, 1.f);
+          if (p.qs) sf = __half22float2(as_h2(sz_cur.s[rb]));
+          float z0 = zc, z1 = zc;
+          if (p.qz) {
+            const uint32_t zb = sz_cur.z[rb >> 1] >> ((rb & 1) * 16);
+            z0 = (float)(zb & 0xffu);
+            z1 = (float)((zb >> 8) & 0xffu);
+          }
+          const float a0 = sf.x * 16777216.f, a1 = sf.y * 1048576.f;  // undo 2^-24 (row g) and 2^-20 (row g+8)
+          const float b0 = -sf.x * z0, b1 = -sf.y * z1;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            acc[rb][nt][0] = fmaf(b0, dx[nt][0], fmaf(a0, d[rb][nt][0], acc[rb][nt][0]));
+            acc[rb][nt][1] = fmaf(b0, dx[nt][1], fmaf(a0, d[rb][nt][1], acc[rb][nt][1]));
+            acc[rb][nt][2] = fmaf(b1, dx[nt][0], fmaf(a1, d[rb][nt][2], acc[rb][nt][2]));
+            acc[rb][nt][3] = fmaf(b1, dx[nt][1], fmaf(a1, d[rb][nt][3], acc[rb][nt][3]));
+          }
+        }
+        if (++gpos == segs_per_group) {  // the next segment starts a new group
+          gpos = 0;
+          ++grp;
+          sz_cur = sz_nxt;
+          if (grp < grp_last) sz_nxt.load(p.qs, p.qz, sz_offset(grp + 1));
+        }
+      }
+      wp += kBatchBytes;
+    }
+  }
+
+  // ---- combine the k-ways of the CTA ----------------------------------------------------
+  __syncthreads();  // everyone is done reading the staged activations
+  float* red = reinterpret_cast<float*>(smem);
+#pragma unroll
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int mm = nt * 8 + 2 * t + (i & 1);
+        const int r = wt * 64 + (sub * RB + rb) * 16 + (i >> 1) * 8 + g;
+        if (mm < p.m) red[(kw * p.m + mm) * kRedStride + r] = acc[rb][nt][i];
+      }
+  __syncthreads();
+
+  const int nout = p.m * kTileRows;
+  if (S == 1) {
+    for (int i = tid; i < nout; i += blockDim.x) {
+      const int mm = i >> 7, r = i & 127;
+      float s = 0.f;
+      for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
+      const int n = tile * kTileRows + r;
+      if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+    }
+    return;
+  }
+
+  // split-K: publish this CTA's partial, the last CTA of the tile sums them in split order
+  for (int i = tid; i < nout; i += blockDim.x) {
+    const int mm = i >> 7, r = i & 127;
+    float s = 0.f;
+    for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
+    p.partial[((size_t)split * p.m + mm) * p.npad + tile * kTileRows + r] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  __shared__ int is_last;
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(p.counters + tile, 1u);
+    is_last = (prev == (unsigned)(S - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const size_t sstride = (size_t)p.m * p.npad;
+  for (int i = tid; i < nout; i += blockDim.x) {
+    const int mm = i >> 7, r = i & 127;
+    const int n = tile * kTileRows + r;
+    const float* base = p.partial + (size_t)mm * p.npad + n;
+    float s = 0.f;
+    int sp = 0;
+    for (; sp + 8 <= S; sp += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(base + (size_t)(sp + u) * sstride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; sp < S; ++sp) s += __ldcg(base + (size_t)sp * sstride);
+    if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+  }
+  if (tid == 0) p.counters[tile] = 0u;
+}
+
+template <int NT, int RB, bool SEG64>
+static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
+  auto kern = gemv_mma_kernel<NT, RB, SEG64>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+cudaError_t launch_gemv_mma(const MmaParams& p, int nt, dim3 grid, int block, size_t smem, bool pdl,
+                            cudaStream_t st) {
+  const bool seg64 = p.chunks_per_group == 1;
+  if (nt == 1) return seg64 ? launch_cfg<1, 4, true>(p, grid, block, smem, pdl, st) : launch_cfg<1, 4, false>(p, grid, block, smem, pdl, st);
+  if (nt == 2) return seg64 ? launch_cfg<2, 2, true>(p, grid, block, smem, pdl, st) : launch_cfg<2, 2, false>(p, grid, block, smem, pdl, st);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace qfb

@@ -31,6 +31,26 @@ cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int bl
 // exact scratch bytes the split-K GEMV needs for m rows (0 when the shape is invalid)
 size_t gemv_scratch_bytes(int m, int n, int k, int bits);
 
+// mma.sync split-K kernel over the fragment layout (4-bit, m <= 16 per launch)
+struct MmaParams {
+  const uint4* qw;
+  const __half* qs;      // null: scale 1 (group-less)
+  const uint8_t* qz;     // null: zconst
+  const __half* x;       // [m, k]
+  __half* y;             // [m, n]
+  float* partial;        // [S, m, npad] split-K partial sums
+  unsigned* counters;    // [tiles] arrival counters, zero between launches
+  int m, n, k, npad;
+  int ksteps;            // K / 16
+  int groups;            // K / group_size (1 when group-less)
+  int chunks_per_group;  // group_size / 64 (K / 64 when group-less)
+  int batches;           // K / 128
+  int batches_per_cta;   // ceil(batches / S): sizes the staged activation slice
+  uint32_t zconst;
+};
+cudaError_t launch_gemv_mma(const MmaParams& p, int nt, dim3 grid, int block, size_t smem, bool pdl,
+                            cudaStream_t st);
+
 struct TcParams {
   const uint4* qw;
   const __half* qs;      // null: group-less (no scaling)
@@ -59,6 +79,7 @@ struct PackParams {
   __half* qs;
   uint8_t* qz;
   int n, k, bits, group_size, npad, tiles, units, groups;
+  int layout;             // QFB_LAYOUT_TILE or QFB_LAYOUT_FRAGMENT
 };
 cudaError_t launch_pack(const PackParams& p, cudaStream_t st);
 
@@ -70,6 +91,7 @@ struct UnpackParams {
   __half* w_out;        // [k, n] or null
   int n, k, bits, npad, tiles, units, groups, units_per_group;
   uint32_t zconst;
+  int layout;
 };
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st);
 

@@ -83,7 +83,103 @@ __global__ void pack_scale_zero_kernel(const PackParams p) {
   }
 }
 
+// ---- fragment layout (4-bit): one thread per packed word / per scale position -----------
+// nibble i of a fragment word holds (row0 + 8 * (i & 1), k0 + kFragNibbleK[i])
+__device__ __forceinline__ int frag_nibble_k(int i) { return (i >> 2) + 2 * ((i >> 1) & 1); }
+
+__global__ void pack_weight_frag_kernel(const PackParams p) {
+  const int ksteps = p.k / 16;
+  const long long total = (long long)p.tiles * 2 * ksteps * 32 * 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int rb = (int)(idx & 3);
+  const int lane = (int)((idx >> 2) & 31);
+  long long t = idx >> 7;
+  const int ks = (int)(t % ksteps); t /= ksteps;
+  const int wt = (int)(t & 1);
+  const int tile = (int)(t >> 1);
+  const int row0 = tile * kTileRows + wt * 64 + rb * 16 + (lane >> 2);
+  const int k0 = ks * 16 + 4 * (lane & 3);
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int n = row0 + 8 * (i & 1);
+    if (n < p.n) {
+      const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + frag_nibble_k(i)) * p.n + n];
+      word |= (q & 15u) << (4 * i);
+    }
+  }
+  p.qw[idx] = word;
+}
+
+__global__ void pack_scale_zero_frag_kernel(const PackParams p) {
+  const long long total = (long long)p.tiles * p.groups * kTileRows;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int pos = (int)(idx % kTileRows);
+  const int g = (int)((idx / kTileRows) % p.groups);
+  const int tile = (int)(idx / ((long long)kTileRows * p.groups));
+  const int n = tile * kTileRows + frag_row_of_pos(pos);
+  if (p.qs) p.qs[idx] = (n < p.n) ? p.scales[(size_t)g * p.n + n] : __ushort_as_half(0);
+  if (p.qz) {
+    int z = 0;
+    if (n < p.n) {
+      z = p.zeros[(size_t)g * p.n + n] + 1;  // same "zero - 1" convention and clamp as the tile layout
+      const int zmax = (1 << p.bits) - 1;
+      z = z > zmax ? zmax : z;
+    }
+    p.qz[idx] = (uint8_t)z;
+  }
+}
+
+// inverse through frag4_fields, the extraction the mma kernel itself runs
+__global__ void unpack_frag_kernel(const UnpackParams p) {
+  const int ksteps = p.k / 16;
+  const long long total = (long long)p.tiles * 2 * ksteps * 32 * 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int rb = (int)(idx & 3);
+  const int lane = (int)((idx >> 2) & 31);
+  long long t = idx >> 7;
+  const int ks = (int)(t % ksteps); t /= ksteps;
+  const int wt = (int)(t & 1);
+  const int tile = (int)(t >> 1);
+  const int g = lane >> 2;
+  const int k0 = ks * 16 + 4 * (lane & 3);
+  uint32_t a[4];
+  frag4_fields(reinterpret_cast<const uint32_t*>(p.qw)[idx], a);
+  const int grp = k0 / (p.k / p.groups);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {  // h = 0: row g (fields a[0], a[2]); h = 1: row g + 8 (a[1], a[3], shifted by 4)
+    const int n = tile * kTileRows + wt * 64 + rb * 16 + h * 8 + g;
+    if (n >= p.n) continue;
+    const uint32_t lo = a[h] >> (4 * h), hi = a[2 + h] >> (4 * h);
+    const int q[4] = {(int)(lo & 15u), (int)((lo >> 16) & 15u), (int)(hi & 15u), (int)((hi >> 16) & 15u)};
+    const size_t sz = ((size_t)tile * p.groups + grp) * kTileRows + wt * 64 + g * 8 + rb * 2 + h;
+    const __half sc = p.qs ? p.qs[sz] : __ushort_as_half(0x3C00);
+    const int z = p.qz ? (int)p.qz[sz] : (int)p.zconst;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (p.codes_out) p.codes_out[(size_t)(k0 + i) * p.n + n] = q[i];
+      if (p.w_out) p.w_out[(size_t)(k0 + i) * p.n + n] = __hmul(__int2half_rn(q[i] - z), sc);
+    }
+  }
+}
+
 cudaError_t launch_pack(const PackParams& p, cudaStream_t st) {
+  if (p.layout == QFB_LAYOUT_FRAGMENT) {
+    const int block = 256;
+    const long long total = (long long)p.tiles * 2 * (p.k / 16) * 32 * 4;
+    pack_weight_frag_kernel<<<(unsigned)((total + block - 1) / block), block, 0, st>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (p.qs || p.qz) {
+      const long long t2 = (long long)p.tiles * p.groups * kTileRows;
+      pack_scale_zero_frag_kernel<<<(unsigned)((t2 + block - 1) / block), block, 0, st>>>(p);
+      e = cudaGetLastError();
+    }
+    return e;
+  }
   const int nv = unit_vecs(p.bits);
   const long long total = (long long)p.tiles * p.units * nv * 4 * kTileRows;
   const int block = 256;
@@ -143,6 +239,12 @@ __global__ void unpack_kernel(const UnpackParams p) {
 }
 
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st) {
+  if (p.layout == QFB_LAYOUT_FRAGMENT) {
+    const int block = 256;
+    const long long tf = (long long)p.tiles * 2 * (p.k / 16) * 32 * 4;
+    unpack_frag_kernel<<<(unsigned)((tf + block - 1) / block), block, 0, st>>>(p);
+    return cudaGetLastError();
+  }
   const long long total = (long long)p.tiles * p.units * kTileRows;
   const int block = 128;
   const unsigned grid = (unsigned)((total + block - 1) / block);

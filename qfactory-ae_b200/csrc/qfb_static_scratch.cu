@@ -49,6 +49,7 @@ int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* 
   if (!layer) return QFB_ERR_NULL_POINTER;
   if (m < 0) return QFB_ERR_BAD_SHAPE;
   if (m == 0) return QFB_OK;
+  if (layer->layout != QFB_LAYOUT_TILE) return QFB_ERR_UNSUPPORTED;  // the CUDA-core kernel reads the tile layout
   // the split-K kernel handles 8 rows per pass and reuses the scratch between passes
   const size_t need = qfb::gemv_scratch_bytes(m, layer->n, layer->k, layer->bits);
   if (need == 0) return QFB_ERR_BAD_SHAPE;

@@ -24,7 +24,7 @@ EXPORTS = (
     "qfb_workspace_bytes", "qfb_workspace_init",
     "qfb_linear_forward", "qfb_linear_forward_host", "qfb_select_kernel",
     "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_read_status",
-    "qfb_pack", "qfb_unpack_codes", "qfb_dequantize",
+    "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
 )
 
@@ -40,6 +40,7 @@ class QfbLayer(ctypes.Structure):
         ("k", ctypes.c_int32),
         ("bits", ctypes.c_int32),
         ("group_size", ctypes.c_int32),
+        ("layout", ctypes.c_int32),
     ]
 
 
@@ -92,6 +93,10 @@ def lib() -> ctypes.CDLL:
     L.qfb_get_last_launch.argtypes = [ctypes.POINTER(i32)] * 5
     L.qfb_pack.restype = i32
     L.qfb_pack.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.qfb_pack_layout.restype = i32
+    L.qfb_pack_layout.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+    L.qfb_layout_supported.restype = i32
+    L.qfb_layout_supported.argtypes = [i32, i32, i32, i32, i32]
     L.qfb_unpack_codes.restype = i32
     L.qfb_unpack_codes.argtypes = [LP, vp, vp]
     L.qfb_dequantize.restype = i32

@@ -36,7 +36,7 @@ def _check_zero(K, N, GS, zero, nbits):
     assert lo >= 0 and hi < 2 ** nbits, "zero-points out of range"
 
 
-def _pack_native(K, N, nbits, GS, weight, scale, zero):
+def _pack_native(K, N, nbits, GS, weight, scale, zero, lay=layout.LAYOUT_TILE):
     from . import _native
 
     L = _native.lib()
@@ -52,11 +52,11 @@ def _pack_native(K, N, nbits, GS, weight, scale, zero):
     scale_c = scale.contiguous() if scale is not None else None
     zero_c = zero.contiguous() if zero is not None else None
     with torch.cuda.device(dev):
-        st = L.qfb_pack(
+        st = L.qfb_pack_layout(
             weight.data_ptr(),
             scale_c.data_ptr() if scale_c is not None else None,
             zero_c.data_ptr() if zero_c is not None else None,
-            N, K, nbits, GS,
+            N, K, nbits, GS, lay,
             w.data_ptr(),
             s.data_ptr() if s is not None else None,
             z.data_ptr() if z is not None else None,
@@ -70,8 +70,11 @@ def convert_params(args, params):
     """Pack one layer.  Returns `w` (group-less) or `(w, s, z)`:
         w  int8 [Npad, K*NBITS/8]   s  fp16 [Npad, K/GS]   z  int8 [Npad, K/GS] or None
     with Npad = N rounded up to 128.  The stored zero is min(zero+1, 2^NBITS-1), as in the
-    reference packer (reference: qfactory/convert.py:76)."""
+    reference packer (reference: qfactory/convert.py:76).  The optional key LAYOUT ('tile', the
+    default, or 'fragment') selects the packed layout (layout.py)."""
     K, N, NBITS = args["K"], args["N"], args["NBITS"]
+    lay = layout.resolve_layout(args.get("LAYOUT", "tile"), N, K, NBITS, args.get("GS", -1))
+    frag = lay == layout.LAYOUT_FRAGMENT
     if "GS" not in args:
         if len(params) != 1:
             raise ValueError("gemv requires 1 parameters")
@@ -79,8 +82,8 @@ def convert_params(args, params):
         layout.check_shape(N, K, NBITS, -1)
         _check_weight(K, N, weight, NBITS)
         if weight.is_cuda:
-            return _pack_native(K, N, NBITS, -1, weight, None, None)[0]
-        return layout.pack_weight(weight, NBITS)
+            return _pack_native(K, N, NBITS, -1, weight, None, None, lay)[0]
+        return layout.pack_weight_fragment(weight) if frag else layout.pack_weight(weight, NBITS)
     if len(params) != 3:
         raise ValueError("gptq_gemv requires 3 parameters")
     weight, scale, zero = params
@@ -91,7 +94,10 @@ def convert_params(args, params):
     if zero is not None:
         _check_zero(K, N, GS, zero, NBITS)
     if weight.is_cuda:
-        return _pack_native(K, N, NBITS, GS, weight, scale, zero)
+        return _pack_native(K, N, NBITS, GS, weight, scale, zero, lay)
+    if frag:
+        return (layout.pack_weight_fragment(weight), layout.pack_scale_fragment(scale),
+                layout.pack_zero_fragment(zero, NBITS) if zero is not None else None)
     w = layout.pack_weight(weight, NBITS)
     s = layout.pack_scale(scale)
     z = layout.pack_zero(zero, NBITS) if zero is not None else None
@@ -102,10 +108,14 @@ def unpack_params(args, packed):
     """Inverse of convert_params: returns codes int32 [K,N] (group-less) or
     (codes, scales fp16 [K/GS,N], effective zeros int32 [K/GS,N] or None)."""
     K, N, NBITS = args["K"], args["N"], args["NBITS"]
+    frag = layout.resolve_layout(args.get("LAYOUT", "tile"), N, K, NBITS, args.get("GS", -1)) == layout.LAYOUT_FRAGMENT
     if "GS" not in args:
         w = packed[0] if isinstance(packed, (tuple, list)) else packed
-        return layout.unpack_weight(w, N, K, NBITS)
+        return layout.unpack_weight_fragment(w, N, K) if frag else layout.unpack_weight(w, N, K, NBITS)
     w, s, z = packed
+    if frag:
+        return (layout.unpack_weight_fragment(w, N, K), layout.unpack_scale_fragment(s, N),
+                layout.unpack_zero_fragment(z, N) if z is not None else None)
     return (
         layout.unpack_weight(w, N, K, NBITS),
         layout.unpack_scale(s, N),

@@ -41,8 +41,9 @@ class DecoderConfig:
         return self.d_model // self.n_heads
 
 
-def _random_layer(K, N, bits, gs, device, gen):
-    L = QLinear.empty(32, K, N, bits, gs, sym=False, device=device)
+def _random_layer(K, N, bits, gs, device, gen, batch=1):
+    # the batch the decoder is built for picks the packed layout (fragment up to 16 rows)
+    L = QLinear.empty(batch, K, N, bits, gs, sym=False, device=device)
     L.w.copy_(torch.randint(-128, 128, L.w.shape, generator=gen, dtype=torch.int8, device=device))
     # small scales keep the residual stream of a random-weight network finite
     L.s.copy_((torch.rand(L.s.shape, generator=gen, device=device) * 2e-4 + 1e-4).half())
@@ -53,14 +54,14 @@ def _random_layer(K, N, bits, gs, device, gen):
 
 
 class DecoderLayer(torch.nn.Module):
-    def __init__(self, cfg: DecoderConfig, world: int, device, gen):
+    def __init__(self, cfg: DecoderConfig, world: int, device, gen, batch: int = 1):
         super().__init__()
         d, hd = cfg.d_model, cfg.head_dim
         self.hq, self.hkv, self.hd = cfg.n_heads // world, cfg.n_kv_heads // world, hd
-        self.qkv = _random_layer(d, (self.hq + 2 * self.hkv) * hd, cfg.bits, cfg.group_size, device, gen)   # column parallel
-        self.o = _random_layer(self.hq * hd, d, cfg.bits, cfg.group_size, device, gen)                       # row parallel
-        self.gate_up = _random_layer(d, 2 * cfg.d_ff // world, cfg.bits, cfg.group_size, device, gen)        # column parallel
-        self.down = _random_layer(cfg.d_ff // world, d, cfg.bits, cfg.group_size, device, gen)               # row parallel
+        self.qkv = _random_layer(d, (self.hq + 2 * self.hkv) * hd, cfg.bits, cfg.group_size, device, gen, batch)   # column parallel
+        self.o = _random_layer(self.hq * hd, d, cfg.bits, cfg.group_size, device, gen, batch)                       # row parallel
+        self.gate_up = _random_layer(d, 2 * cfg.d_ff // world, cfg.bits, cfg.group_size, device, gen, batch)        # column parallel
+        self.down = _random_layer(cfg.d_ff // world, d, cfg.bits, cfg.group_size, device, gen, batch)               # row parallel
         self.norm1 = torch.nn.Parameter(torch.ones(d, dtype=torch.float16, device=device), requires_grad=False)
         self.norm2 = torch.nn.Parameter(torch.ones(d, dtype=torch.float16, device=device), requires_grad=False)
 
@@ -71,7 +72,7 @@ class QuantDecoder(torch.nn.Module):
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
-        self.blocks = torch.nn.ModuleList([DecoderLayer(cfg, world, device, gen) for _ in range(cfg.layers)])
+        self.blocks = torch.nn.ModuleList([DecoderLayer(cfg, world, device, gen, batch) for _ in range(cfg.layers)])
         g0 = torch.Generator(device=device).manual_seed(seed)  # replicated tensors: same on every rank
         self.embed = (torch.randn(cfg.vocab, cfg.d_model, generator=g0, device=device) * 0.02).half()
         self.lm_head = (torch.randn(cfg.d_model, cfg.vocab, generator=g0, device=device) * 0.02).half()

@@ -18,6 +18,7 @@ from __future__ import annotations
 import torch
 
 TILE = 128
+LAYOUT_TILE, LAYOUT_FRAGMENT = 0, 1  # QFB_LAYOUT_* of the C ABI
 
 
 def unit_k(bits: int) -> int:
@@ -176,3 +177,88 @@ def unpack_zero(z: torch.Tensor, N: int) -> torch.Tensor:
     Np, G = z.shape
     zz = z.contiguous().view(torch.uint8).view(Np // TILE, G, TILE).permute(1, 0, 2).reshape(G, Np)
     return zz[:, :N].to(torch.int32).contiguous()
+
+
+# ---------------------------------------------------------------------------------------
+# Fragment layout (4-bit, K % 128 == 0): the same codes permuted so that one 32-bit word is
+# the A fragment a thread feeds to mma.sync.m16n8k16 (include/qfactory_b200.h).  For lane
+# (g = lane // 4, t = lane % 4) of row block rb in the 64-row half wt of a tile, nibble i of
+# the word at 16-k step ks holds row wt*64 + rb*16 + 8*(i & 1) + g, k = 16*ks + 4*t + NIBBLE_K[i].
+#     qweight  u32 [tiles][2][K/16][32 lanes][4 row blocks]
+#     scales / zeros  [tiles][K/group][128], position wt*64 + g*8 + rb*2 + h <-> row wt*64 + rb*16 + h*8 + g
+# ---------------------------------------------------------------------------------------
+NIBBLE_K = [(i >> 2) + 2 * ((i >> 1) & 1) for i in range(8)]
+
+
+def fragment_supported(N: int, K: int, bits: int, GS: int) -> bool:
+    return bits == 4 and K % 128 == 0 and (GS in (-1, 64) or GS % 128 == 0)
+
+
+def resolve_layout(layout, N: int, K: int, bits: int, GS: int, batch_size: int = 1) -> int:
+    """'tile' | 'fragment' | 'auto' | 0 | 1 | None -> LAYOUT_*.  'auto' (and None) picks the fragment
+    layout for 4-bit layers that are built for batches of at most 16 rows."""
+    if layout in (LAYOUT_TILE, "tile"):
+        return LAYOUT_TILE
+    if layout in (LAYOUT_FRAGMENT, "fragment"):
+        assert fragment_supported(N, K, bits, GS), "the fragment layout needs 4-bit codes and K % 128 == 0"
+        return LAYOUT_FRAGMENT
+    assert layout in (None, "auto"), f"unknown layout {layout!r}"
+    return LAYOUT_FRAGMENT if (fragment_supported(N, K, bits, GS) and batch_size <= 16) else LAYOUT_TILE
+
+
+def frag_row_of_pos(device=None) -> torch.Tensor:
+    pos = torch.arange(TILE, device=device)
+    return (pos >> 6) * 64 + ((pos >> 1) & 3) * 16 + (pos & 1) * 8 + ((pos >> 3) & 7)
+
+
+def pack_weight_fragment(q: torch.Tensor) -> torch.Tensor:
+    """int32 codes [K, N] (4-bit) -> int8 [Npad, K/2] in fragment order."""
+    K, N = q.shape
+    Np = padded_rows(N)
+    T = Np // TILE
+    blk = torch.zeros(Np, K, dtype=torch.int64, device=q.device)
+    blk[:N] = q.t()
+    v = blk.view(T, 2, 4, 2, 8, K // 16, 4, 4)            # [tile, wt, rb, h, g, ks, t, kk]
+    words = torch.zeros(T, 2, K // 16, 8, 4, 4, dtype=torch.int64, device=q.device)  # [tile, wt, ks, g, t, rb]
+    for i in range(8):
+        words += v[:, :, :, i & 1, :, :, :, NIBBLE_K[i]].permute(0, 1, 4, 3, 5, 2) << (4 * i)
+    return _words_to_bytes(words).reshape(Np, K // 2).view(torch.int8)
+
+
+def unpack_weight_fragment(w: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    Np = padded_rows(N)
+    T = Np // TILE
+    words = _bytes_to_words(w.contiguous().view(torch.uint8).view(T, 2, K // 16, 8, 4, 4, 4))  # [tile, wt, ks, g, t, rb]
+    v = torch.empty(T, 2, 4, 2, 8, K // 16, 4, 4, dtype=torch.int64, device=w.device)
+    for i in range(8):
+        v[:, :, :, i & 1, :, :, :, NIBBLE_K[i]] = ((words >> (4 * i)) & 15).permute(0, 1, 5, 3, 2, 4)
+    return v.reshape(Np, K)[:N].t().contiguous().to(torch.int32)
+
+
+def _to_fragment_rows(a: torch.Tensor) -> torch.Tensor:
+    """[Npad, G] flat tile-major -> the same with the 128 rows of every tile in fragment order."""
+    Np, G = a.shape
+    return a.contiguous().view(Np // TILE, G, TILE)[:, :, frag_row_of_pos(a.device)].contiguous().view(Np, G)
+
+
+def _from_fragment_rows(a: torch.Tensor) -> torch.Tensor:
+    Np, G = a.shape
+    out = torch.empty_like(a.contiguous().view(Np // TILE, G, TILE))
+    out[:, :, frag_row_of_pos(a.device)] = a.contiguous().view(Np // TILE, G, TILE)
+    return out.view(Np, G)
+
+
+def pack_scale_fragment(s: torch.Tensor) -> torch.Tensor:
+    return _to_fragment_rows(pack_scale(s))
+
+
+def pack_zero_fragment(z: torch.Tensor, bits: int) -> torch.Tensor:
+    return _to_fragment_rows(pack_zero(z, bits))
+
+
+def unpack_scale_fragment(s: torch.Tensor, N: int) -> torch.Tensor:
+    return unpack_scale(_from_fragment_rows(s), N)
+
+
+def unpack_zero_fragment(z: torch.Tensor, N: int) -> torch.Tensor:
+    return unpack_zero(_from_fragment_rows(z), N)

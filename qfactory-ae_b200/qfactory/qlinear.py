@@ -3,7 +3,9 @@
 
 Same names, arguments and error behaviour as the reference (reference:
 qfactory/qlinear.py:5-145).  Differences, all on purpose:
-  * the packed tensors `.w/.s/.z` use the tile-128 layout of `convert.py`;
+  * the packed tensors `.w/.s/.z` use the layouts of `convert.py`: `layout='tile'` (every bit
+    width and batch size), `layout='fragment'` (4-bit, made for batches of at most 16 rows) or
+    `layout='auto'` (the default: fragment when the layer is built for `batch_size <= 16`);
   * the batch size is a run-time property of `forward`, not a compile-time constant, and
     `x` may have any number of leading dimensions;
   * kernel selection is a static heuristic inside the native library, so `compile_flags`
@@ -26,8 +28,10 @@ class _PackedLinear(torch.nn.Module):
     """Shared implementation: owns the packed buffers, the split-K workspace and the
     `qfb_layer` descriptor handed to the C ABI."""
 
-    def __init__(self, in_features, out_features, n_bits, group_size, w, s, z, max_batch=16):
+    def __init__(self, in_features, out_features, n_bits, group_size, w, s, z, max_batch=16,
+                 packed_layout=layout.LAYOUT_TILE):
         super().__init__()
+        self.packed_layout = packed_layout
         self.in_features, self.out_features = in_features, out_features
         self.n_bits, self.group_size = n_bits, group_size
         # buffers: they follow .to()/.cuda() and are saved by state_dict()
@@ -51,6 +55,7 @@ class _PackedLinear(torch.nn.Module):
         d.scales = self.s.data_ptr() if self.s is not None else None
         d.zeros = self.z.data_ptr() if self.z is not None else None
         d.n, d.k, d.bits, d.group_size = self.out_features, self.in_features, self.n_bits, self.group_size
+        d.layout = self.packed_layout
         nbytes = L.qfb_workspace_bytes(self._max_batch, self.out_features, self.in_features, self.n_bits)
         self._ws = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.w.device)
         self._ws_bytes = nbytes
@@ -110,6 +115,18 @@ class _PackedLinear(torch.nn.Module):
             _native.check(st, "qfb_linear_forward_host")
         return y_host
 
+    def unpack_torch(self):
+        """(codes int32 [K,N], scales fp16 [K/GS,N] or None, effective zeros int32 [K/GS,N] or None)
+        recovered from the packed buffers in torch, on whatever device they live on."""
+        N, K = self.out_features, self.in_features
+        if self.packed_layout == layout.LAYOUT_FRAGMENT:
+            return (layout.unpack_weight_fragment(self.w, N, K),
+                    layout.unpack_scale_fragment(self.s, N) if self.s is not None else None,
+                    layout.unpack_zero_fragment(self.z, N) if self.z is not None else None)
+        return (layout.unpack_weight(self.w, N, K, self.n_bits),
+                layout.unpack_scale(self.s, N) if self.s is not None else None,
+                layout.unpack_zero(self.z, N) if self.z is not None else None)
+
     # -- test / debug helpers through the kernels' own decode path ----------
     def unpack_codes(self) -> torch.Tensor:
         if self._desc is None:
@@ -129,21 +146,24 @@ class _PackedLinear(torch.nn.Module):
 
     def extra_repr(self):
         return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.n_bits}, "
-                f"group_size={self.group_size}, symmetric={self.z is None and self.s is not None}")
+                f"group_size={self.group_size}, symmetric={self.z is None and self.s is not None}, "
+                f"layout={'fragment' if self.packed_layout else 'tile'}")
 
 
 class GPTQLinear(_PackedLinear):
     """Group-quantized layer (reference: qfactory/qlinear.py:5-58)."""
 
     def __init__(self, in_features, out_features, n_bits, weight, group_size, scale, zero, bias,
-                 compile_flags=None, skip_convert=False, batch_size=1, base_impl=False):
+                 compile_flags=None, skip_convert=False, batch_size=1, base_impl=False, layout_kind="auto"):
         if bias:
             raise NotImplementedError("Bias is not supported")
+        lay = layout.resolve_layout(layout_kind, out_features, in_features, n_bits, group_size, batch_size)
         if skip_convert:
             w, s, z = weight, scale, zero
         else:
             w, s, z = convert_params(
-                {"K": in_features, "N": out_features, "NBITS": n_bits, "GS": group_size}, (weight, scale, zero))
+                {"K": in_features, "N": out_features, "NBITS": n_bits, "GS": group_size, "LAYOUT": lay},
+                (weight, scale, zero))
         npad = layout.padded_rows(out_features)
         layout.check_shape(out_features, in_features, n_bits, group_size)
         assert w.dtype == torch.int8 and w.dim() == 2
@@ -151,22 +171,26 @@ class GPTQLinear(_PackedLinear):
         assert s.dtype == torch.float16 and s.shape == (npad, in_features // group_size)
         if z is not None:
             assert z.dtype == torch.int8 and z.shape == (npad, in_features // group_size)
-        super().__init__(in_features, out_features, n_bits, group_size, w, s, z, max_batch=max(16, batch_size))
+        super().__init__(in_features, out_features, n_bits, group_size, w, s, z, max_batch=max(16, batch_size),
+                         packed_layout=lay)
 
 
 class GEMVLinear(_PackedLinear):
     """Group-less layer on raw unsigned codes: y = x @ codes^T, no scale or zero
     (reference: qfactory/qlinear.py:60-97, kernel qfactory/include/gemv.h:12-94)."""
 
-    def __init__(self, in_features, out_features, n_bits, weight, bias, compile_flags=None, skip_convert=False):
+    def __init__(self, in_features, out_features, n_bits, weight, bias, compile_flags=None, skip_convert=False,
+                 batch_size=1, layout_kind="auto"):
         if bias:
             raise NotImplementedError("Bias is not supported")
+        lay = layout.resolve_layout(layout_kind, out_features, in_features, n_bits, -1, batch_size)
         w = weight if skip_convert else convert_params(
-            {"K": in_features, "N": out_features, "NBITS": n_bits}, (weight,))
+            {"K": in_features, "N": out_features, "NBITS": n_bits, "LAYOUT": lay}, (weight,))
         layout.check_shape(out_features, in_features, n_bits, -1)
         assert w.dtype == torch.int8 and w.dim() == 2
         assert w.numel() == layout.padded_rows(out_features) * in_features * n_bits // 8
-        super().__init__(in_features, out_features, n_bits, -1, w, None, None)
+        super().__init__(in_features, out_features, n_bits, -1, w, None, None, max_batch=max(16, batch_size),
+                         packed_layout=lay)
 
 
 class QLinear:
@@ -174,28 +198,30 @@ class QLinear:
 
     @staticmethod
     def init(batch_size, in_features, out_features, n_bits, weight, group_size=-1, scale=None, zero=None,
-             bias=False, compile_flags={}):
+             bias=False, compile_flags={}, layout="auto"):
         if group_size == -1:
-            return GEMVLinear(in_features, out_features, n_bits, weight, bias, compile_flags, skip_convert=False)
+            return GEMVLinear(in_features, out_features, n_bits, weight, bias, compile_flags, skip_convert=False,
+                              batch_size=batch_size, layout_kind=layout)
         return GPTQLinear(in_features, out_features, n_bits, weight, group_size, scale, zero, bias, compile_flags,
-                          skip_convert=False, batch_size=batch_size)
+                          skip_convert=False, batch_size=batch_size, layout_kind=layout)
 
     @staticmethod
-    def empty(M, K, N, NBITS, GS, sym, compile_flags={}, base_impl=False, device="cuda"):
+    def empty(M, K, N, NBITS, GS, sym, compile_flags={}, base_impl=False, device="cuda", layout="auto"):
         """Uninitialised packed buffers of the right shapes (benchmarks, the vLLM hook)."""
-        npad = layout.padded_rows(N)
+        from . import layout as _layout
+        npad = _layout.padded_rows(N)
         w = torch.empty(npad, K * NBITS // 8, dtype=torch.int8, device=device)
         if GS == -1:
-            return GEMVLinear(K, N, NBITS, w, False, compile_flags, skip_convert=True)
+            return GEMVLinear(K, N, NBITS, w, False, compile_flags, skip_convert=True, batch_size=M, layout_kind=layout)
         s = torch.empty(npad, K // GS, dtype=torch.float16, device=device)
         z = None if sym else torch.empty(npad, K // GS, dtype=torch.int8, device=device)
         return GPTQLinear(K, N, NBITS, w, GS, s, z, False, compile_flags, skip_convert=True, batch_size=M,
-                          base_impl=base_impl)
+                          base_impl=base_impl, layout_kind=layout)
 
     @staticmethod
-    def from_float(weight: torch.Tensor, n_bits: int, group_size: int = 128, batch_size: int = 1):
+    def from_float(weight: torch.Tensor, n_bits: int, group_size: int = 128, batch_size: int = 1, layout="auto"):
         """Quantize an fp16 weight [K, N] group-wise (asymmetric, as the reference's
         tests/acc_gptq.py:10-29 does) and pack it."""
         K, N = weight.shape
         q, s, z = asymmetric_quant(weight, group_size, n_bits)
-        return QLinear.init(batch_size, K, N, n_bits, q, group_size, s, z)
+        return QLinear.init(batch_size, K, N, n_bits, q, group_size, s, z, layout=layout)

@@ -30,9 +30,10 @@ def test_layer_from_gptq_holds_the_same_codes_scales_and_effective_zeros():
     x, q, s, z = O.make_case(1, N, K, bits, GS, False, seed=4)
     layer = gptq.layer_from_gptq(gptq.pack_qweight(q, bits), gptq.pack_qzeros(z, bits), s, bits, GS,
                                  g_idx=torch.arange(K, dtype=torch.int32) // GS)
-    assert torch.equal(layout.unpack_weight(layer.w, N, K, bits), q)
-    assert np.array_equal(layout.unpack_zero(layer.z, N).numpy(), O.effective_zero(z.numpy(), bits))
-    assert torch.equal(layout.unpack_scale(layer.s, N).view(torch.int16), s.view(torch.int16))
+    q2, s2, z2 = layer.unpack_torch()  # whatever layout the factory picked
+    assert torch.equal(q2, q)
+    assert np.array_equal(z2.numpy(), O.effective_zero(z.numpy(), bits))
+    assert torch.equal(s2.view(torch.int16), s.view(torch.int16))
 
 
 def test_activation_reordered_checkpoints_are_rejected():
@@ -52,7 +53,7 @@ def test_repack_of_a_loaded_row_parallel_shard():
                                  scales=P(s), g_idx=P(torch.arange(K, dtype=torch.int32) // GS + 6))
     layer = vllm_hook.repack_loaded_layer(fake, bits, GS)
     assert layer.in_features == K and layer.out_features == N
-    assert torch.equal(layout.unpack_weight(layer.w, N, K, bits), q)
+    assert torch.equal(layer.unpack_torch()[0], q)
 
 
 def test_hook_classes_build_against_the_installed_vllm():

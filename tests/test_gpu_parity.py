@@ -18,12 +18,12 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-2  # max-abs error allowed, as a fraction of ||y||_inf
 
 
-def _layer(N, K, bits, GS, sym, seed=0, M=1):
+def _layer(N, K, bits, GS, sym, seed=0, M=1, layout_kind="tile"):
     x, q, s, z = O.make_case(M, N, K, bits, GS, sym, seed)
     if GS == -1:
-        layer = QLinear.init(M, K, N, bits, q.cuda())
+        layer = QLinear.init(M, K, N, bits, q.cuda(), layout=layout_kind)
     else:
-        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), None if z is None else z.cuda())
+        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), None if z is None else z.cuda(), layout=layout_kind)
     return layer, x, q, s, z
 
 
@@ -102,13 +102,13 @@ def test_forward_on_golden_fixture(golden_dir, bits):
     f = np.load(os.path.join(golden_dir, f"dequant_b{bits}.npz"))
     K, N, GS, M = int(f["K"]), int(f["N"]), int(f["GS"]), int(f["M"])
     q, s, z = torch.from_numpy(f["q"]), torch.from_numpy(f["s"]), torch.from_numpy(f["z"])
-    layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda())
+    layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda(), layout="tile")
     y = layer(torch.from_numpy(f["x"]).cuda()).float().cpu().numpy()
     ref = f["y"].astype(np.float32)  # produced by the reference's own dequant + fp16 matmul
     assert np.abs(y - ref).max() <= TOL * np.abs(ref).max()
     # the dequantised weight equals the reference helper's output bit for bit (no clamp in play here)
     assert np.array_equal(layer.dequantize().cpu().numpy().view(np.uint16), f["wdq"].view(np.uint16))
-    g = QLinear.init(M, K, N, bits, q.cuda())
+    g = QLinear.init(M, K, N, bits, q.cuda(), layout="tile")
     yg = g(torch.from_numpy(f["x"]).cuda()).float().cpu().numpy()
     refg = f["y_groupless"].astype(np.float32)
     assert np.abs(yg - refg).max() <= TOL * np.abs(refg).max()
@@ -119,7 +119,7 @@ def test_clamped_top_zero_follows_packer_semantics():
     bits, N, K, GS = 4, 128, 256, 128
     x, q, s, z = O.make_case(1, N, K, bits, GS, False, seed=3)
     z[:] = 15
-    layer = QLinear.init(1, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda())
+    layer = QLinear.init(1, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda(), layout="tile")
     want = O.dequant_effective(q, s, np.full((K // GS, N), 15, dtype=np.int32))
     assert torch.equal(layer.dequantize().cpu().view(torch.int16), want.view(torch.int16))
 
@@ -149,7 +149,7 @@ def test_full_size_properties_mlp70b():
     # (28672, 8192) W4 g128: linearity in x, determinism, and a sampled oracle check
     N, K, bits, GS = 28672, 8192, 4, 128
     g = torch.Generator().manual_seed(0)
-    layer = QLinear.empty(1, K, N, bits, GS, sym=False)
+    layer = QLinear.empty(1, K, N, bits, GS, sym=False, layout="tile")
     layer.w.copy_(torch.randint(-128, 128, layer.w.shape, generator=g, dtype=torch.int8))
     layer.s.copy_((torch.rand(layer.s.shape, generator=g) * 0.018 + 0.002).half())
     layer.z.copy_(torch.randint(0, 16, layer.z.shape, generator=g, dtype=torch.int8))
@@ -239,7 +239,7 @@ def test_status_codes_on_device():
 def test_state_dict_round_trip():
     layer, x, q, s, z = _layer(256, 512, 4, 128, False, seed=8, M=1)
     sd = {k: v.cpu() for k, v in layer.state_dict().items()}
-    other = QLinear.empty(1, 512, 256, 4, 128, sym=False)
+    other = QLinear.empty(1, 512, 256, 4, 128, sym=False, layout="tile")
     other.load_state_dict(sd)
     assert torch.equal(other(x.cuda()), layer(x.cuda()))
 
@@ -248,7 +248,7 @@ def test_from_float_front_end():
     g = torch.Generator().manual_seed(12)
     w = torch.randn(512, 256, generator=g).half()
     x = torch.randn(2, 512, generator=g).half()
-    layer = QLinear.from_float(w.cuda(), 4, 128)
+    layer = QLinear.from_float(w.cuda(), 4, 128, layout="tile")
     q, s, z = O.asymmetric_quant(w, 128, 4)
     _check_output(layer(x.cuda()), x, q, s, z, 4)
     # the reference's own criterion (tests/acc_gptq.py:61-62): MSE against dequantize-then-matmul < 0.1

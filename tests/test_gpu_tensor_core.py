@@ -18,9 +18,9 @@ TOL = 1e-2
 def _run(M, N, K, bits, GS, sym, seed, flags=_native.FLAG_FORCE_TENSOR):
     x, q, s, z = O.make_case(M, N, K, bits, GS, sym, seed)
     if GS == -1:
-        layer = QLinear.init(M, K, N, bits, q.cuda())
+        layer = QLinear.init(M, K, N, bits, q.cuda(), layout="tile")
     else:
-        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), None if z is None else z.cuda())
+        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), None if z is None else z.cuda(), layout="tile")
     layer.flags = flags
     y = layer(x.cuda())
     torch.cuda.synchronize()
@@ -71,7 +71,7 @@ def test_k_extents_and_split_k(K):
 def test_tensor_kernel_falls_back_when_k_is_not_a_stage_multiple():
     # K = 192 is a multiple of 64 but not of 128: the tensor path does not apply
     x, q, s, z = O.make_case(4, 128, 192, 4, 64, False, 3)
-    layer = QLinear.init(4, 192, 128, 4, q.cuda(), 64, s.cuda(), z.cuda())
+    layer = QLinear.init(4, 192, 128, 4, q.cuda(), 64, s.cuda(), z.cuda(), layout="tile")
     layer.flags = _native.FLAG_FORCE_TENSOR
     y = layer(x.cuda())
     assert _native.last_launch()["kernel"] == 1
@@ -100,7 +100,7 @@ def test_pdl_launches_give_identical_results():
 
 def test_simt_and_tensor_kernels_agree():
     x, q, s, z = O.make_case(6, 640, 2048, 4, 128, False, 5)
-    layer = QLinear.init(6, 2048, 640, 4, q.cuda(), 128, s.cuda(), z.cuda())
+    layer = QLinear.init(6, 2048, 640, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="tile")
     layer.flags = _native.FLAG_FORCE_SIMT
     a = layer(x.cuda()).float()
     layer.flags = _native.FLAG_FORCE_TENSOR
@@ -113,7 +113,7 @@ def test_llama70b_mlp_shape_sampled_rows(M):
     # (28672, 8192) W4 g128 at full size: sampled output rows against the oracle
     N, K, bits, GS = 28672, 8192, 4, 128
     g = torch.Generator().manual_seed(M)
-    layer = QLinear.empty(M, K, N, bits, GS, sym=False)
+    layer = QLinear.empty(M, K, N, bits, GS, sym=False, layout="tile")
     layer.w.copy_(torch.randint(-128, 128, layer.w.shape, generator=g, dtype=torch.int8))
     layer.s.copy_((torch.rand(layer.s.shape, generator=g) * 0.018 + 0.002).half())
     layer.z.copy_(torch.randint(0, 16, layer.z.shape, generator=g, dtype=torch.int8))

@@ -20,7 +20,7 @@ TOL = 1e-2  # max-abs error as a fraction of ||y||_inf, the bar of the other par
 def test_static_scratch_entry_matches_regular_entry(M, N, K):
     L = _native.lib()
     x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=31 + M)
-    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda())
+    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="tile")
     xs = x.cuda()
     want = layer(xs).float()  # regular entry point, caller-provided workspace
     stream = torch.cuda.current_stream().cuda_stream
