@@ -37,11 +37,10 @@ BATCHES = [1, 4, 16]
 BITS, GS = 4, 128
 METRIC = "w4a16_g128_gemv_achieved_hbm_bandwidth"
 UNIT = "GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (qgemm_tc_kernel):
-# the ncu capture of the (22016,4096) M=4 case moved 1.00592 x its algorithmic bytes; traffic
-# grows with the weight bytes, so the sweep's average launch (26,614,016 algorithmic bytes)
-# is scaled by the same factor
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 26771537
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch, from the ncu
+# captures of the (22016,4096) case summarised under profiles/; traffic grows with the weight
+# bytes, so the average launch of the sweep is scaled by the same factor
+NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": None}
 WORKLOAD = "llama7b_layer_sweep_w4a16_g128_asym: (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)} x M in {1,4,16}"
 
 
@@ -191,6 +190,8 @@ def main():
                     "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
+    ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
+                    help="packed layout of the benchmark layers (auto: fragment for these batch sizes)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -224,7 +225,7 @@ def main():
         N, K, M = (int(v) for v in args.case.lower().split("x"))
         layers = []
         for _ in range(4):
-            L = QLinear.empty(max(M, 16), K, N, BITS, GS, sym=False, device=dev)
+            L = QLinear.empty(max(M, 16), K, N, BITS, GS, sym=False, device=dev, layout=args.layout)
             L.w.random_(-128, 127)
             L.s.uniform_(0.002, 0.02)
             L.z.random_(0, 15)
@@ -240,7 +241,7 @@ def main():
         return
 
     def make_layer(N, K):
-        L = QLinear.empty(16, K, N, BITS, GS, sym=False, device=dev)
+        L = QLinear.empty(16, K, N, BITS, GS, sym=False, device=dev, layout=args.layout)
         L.w.copy_(torch.randint(-128, 128, L.w.shape, generator=g, dtype=torch.int8, device=dev))
         L.s.copy_((torch.rand(L.s.shape, generator=g, device=dev) * 0.018 + 0.002).half())
         L.z.copy_(torch.randint(0, 16, L.z.shape, generator=g, dtype=torch.int8, device=dev))
@@ -288,7 +289,8 @@ def main():
         # own time can be measured with events in this same run
         kern_of = []
         for _, M, layer, *_ in cases[0]:
-            kern_of.append(_native.lib().qfb_select_kernel(M, layer.out_features, layer.in_features, BITS, flags))
+            kern_of.append(3 if layer.packed_layout else
+                           _native.lib().qfb_select_kernel(M, layer.out_features, layer.in_features, BITS, flags))
         sub_graphs = {}
         for kid in sorted(set(kern_of)):
             gl = []
@@ -408,7 +410,7 @@ def main():
         e2e_val = sb * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
         launches = n_cases * args.steps
         # dominant kernel = the one with the larger share of the step's device time
-        names = {1: "gemv_splitk_kernel", 2: "qgemm_tc_kernel"}
+        names = {1: "gemv_splitk_kernel", 2: "qgemm_tc_kernel", 3: "gemv_mma_kernel"}
         shares = {}
         for kid, kms in kernel_ms.items():
             idx = [ci for ci in range(n_cases) if kern_of[ci] == kid]
@@ -438,7 +440,9 @@ def main():
             "per_shape": per_shape,
             "decode": decode,
         }
-        out["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
+        ratio = NCU_TRAFFIC_RATIO.get(shares[dom]["kernel"])
+        if ratio:
+            out["roofline"]["traffic"] = int(ratio * shares[dom]["bytes_per_step"] / shares[dom]["launches_per_step"])
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(out))
