@@ -157,6 +157,10 @@ int qfb_read_status(const void* workspace, void* stream, unsigned* status_out);
 void qfb_set_gemv_tuning(int split_k, int k_ways);
 /* Tuning override of the tensor-core kernel's split-K factor for batches <= 64 (0 = built-in). */
 void qfb_set_tensor_split(int split_k);
+/* mma.sync GEMV (fragment layout), how K splits are reduced: 1 (default) lets the cost model
+ * choose between a thread-block cluster (distributed shared memory, at most 8 splits) and the
+ * workspace; 0 always uses the workspace; 2 uses a cluster whenever there are 2..8 splits. */
+void qfb_set_cluster_reduce(int mode);
 /* The configuration the last qfb_linear_forward of this thread used (for reports). */
 void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes);
 

@@ -18,6 +18,7 @@ static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
 static int g_tune_split = 0, g_tune_kways = 0;
 static int g_tc_min_m = 2;  // smallest batch routed to the tensor-core kernel
 static int g_tc_split = 0;  // tuning override of the tensor-core split-K factor (0 = built-in)
+static int g_mma_cluster = 1;  // mma.sync GEMV: reduce up to 8 K splits inside a thread-block cluster
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -285,7 +286,7 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
 }
 
 // ---- mma.sync GEMV over the fragment layout ---------------------------------------------
-struct MmaPlan { int nt, split, kways; size_t smem; };
+struct MmaPlan { int nt, split, kways, cluster; size_t smem; };
 
 static int mma_split_cap(int tiles, int batches) {
   return std::max(1, std::min(batches, (kNumSMs * 4 + tiles - 1) / tiles));
@@ -293,14 +294,19 @@ static int mma_split_cap(int tiles, int batches) {
 
 static size_t mma_smem(int rows, int nt, int bpc, int kways) {
   const size_t stage = (size_t)rows * (bpc * 128 + 16) * 2 + (size_t)bpc * 2 * 8 * nt * sizeof(float);
-  const size_t red = (size_t)kways * rows * 132 * sizeof(float);
+  // k-way reduction lines plus the CTA's own partial for the in-cluster split-K reduction
+  const size_t red = (size_t)kways * rows * 132 * sizeof(float) + (size_t)rows * 128 * sizeof(float);
   return std::max(stage, red);
 }
 
-// Split-K factor and k-ways of the mma.sync GEMV.  Model fitted to measurements: the CTAs of a
-// launch should be resident at once (a second wave costs a full CTA time), a CTA costs its longest
-// k-way plus a fixed part worth ~1.5 batches, and SMs hold 16 warps of this kernel.
-static MmaPlan plan_mma(int tiles, int k, int rows) {
+// Split-K factor, k-ways and reduction mode of the mma.sync GEMV.  Cost model fitted to sweeps
+// on B200, in units of one 128-k batch of one warp (~0.25 us): the CTAs of a launch should be
+// resident at once (a second wave costs a full CTA time); a CTA costs its longest k-way plus a
+// fixed part worth ~1.5 batches; reducing the splits inside a thread-block cluster costs a part
+// that grows with rows x splits, reducing them through the workspace a fixed fence / atomic /
+// re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
+// inside one GPC, so a grid that fits by CTA count may still need a second wave).
+static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
@@ -308,25 +314,37 @@ static MmaPlan plan_mma(int tiles, int k, int rows) {
   const int kways_max = pl.nt == 1 ? 4 : 2;  // at most 256 threads
   const int cap = mma_split_cap(tiles, batches);
   const size_t smem_max = 100 * 1024;
-  int best_s = cap, best_kw = 1;
+  int best_s = cap, best_kw = 1, best_cl = 0;
   double best_cost = 1e30;
   for (int kw = kways_max; kw >= 1; kw >>= 1) {
     if (g_tune_kways > 0 && kw != std::min(g_tune_kways, kways_max)) continue;
+    const int block = 32 * wpk * kw;
     for (int s = 1; s <= cap; ++s) {
       if (g_tune_split > 0 && s != std::min(g_tune_split, cap)) continue;
       const int bpc = (batches + s - 1) / s;
       const size_t smem = mma_smem(rows, pl.nt, bpc, kw);
       if (smem > smem_max && s < cap) continue;
-      // CTAs resident per SM: 16 warps of 128 registers per thread, and the shared memory
-      const int resident = std::max(1, std::min(16 / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
-      const int slots = kNumSMs * resident;
       const int per_kway = (bpc + kw - 1) / kw;
-      const int waves = (tiles * s + slots - 1) / slots;
-      const double cost = (double)waves * (per_kway + 1.5) + 0.05 * s + 0.01 * (kways_max - kw);
-      if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; }
+      const double base = 0.05 * s + 0.01 * (kways_max - kw);
+      // through the workspace: 16 warps of 128 registers per thread and the shared memory bound the residency
+      if (!(g_mma_cluster == 2 && s > 1 && s <= 8)) {
+        const int resident = std::max(1, std::min(16 / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
+        const int waves = (tiles * s + kNumSMs * resident - 1) / (kNumSMs * resident);
+        const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
+        if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 0; }
+      }
+      if (s > 1 && s <= 8 && g_mma_cluster && (pl.nt == 1 || s <= 4 || g_mma_cluster == 2)) {
+        const int fit = mma_max_active_clusters(pl.nt, seg64, block, smem, s);
+        if (fit > 0) {
+          const int waves = (tiles + fit - 1) / fit;
+          const double cost = (double)waves * (per_kway + 1.5) + base + 0.09 * rows * s;
+          if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 1; }
+        }
+      }
     }
   }
   pl.split = best_s;
+  pl.cluster = best_cl;
   const int bpc = (batches + best_s - 1) / best_s;
   pl.kways = std::max(1, std::min(best_kw, batches / best_s > 0 ? batches / best_s : 1));
   pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
@@ -337,7 +355,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
                    unsigned flags, cudaStream_t st) {
   for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
     const int rows = std::min(kMaxMmaRows, m - m0);
-    const MmaPlan pl = plan_mma(v.tiles, v.k, rows);
+    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
     MmaParams p;
     p.qw = v.qw;
@@ -357,7 +375,9 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.zconst = v.zconst;
     p.partial = nullptr;
     p.counters = nullptr;
-    if (pl.split > 1) {
+    // up to 8 splits reduce inside a thread-block cluster; more go through the workspace
+    p.cluster = pl.cluster;
+    if (pl.split > 1 && !p.cluster) {
       const size_t off = partial_offset(v.tiles);
       const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);
       if (!workspace || ws_bytes < need) return QFB_ERR_WORKSPACE;
@@ -493,6 +513,8 @@ void qfb_set_gemv_tuning(int split_k, int k_ways) {
 }
 
 void qfb_set_tensor_split(int split_k) { g_tc_split = split_k > 0 ? split_k : 0; }
+
+void qfb_set_cluster_reduce(int mode) { g_mma_cluster = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
 void qfb_get_last_launch(int* kernel, int* grid_x, int* grid_y, int* block, int* smem_bytes) {
   if (kernel) *kernel = tl_last_launch[0];

@@ -29,6 +29,9 @@
 //
 // Ordering under programmatic dependent launch: weight, scale and zero loads are issued before
 // griddepcontrol.wait; activations, workspace and output are only touched after it.
+#include <map>
+#include <mutex>
+
 #include "qfb_common.cuh"
 #include "qfb_kernels.h"
 
@@ -48,6 +51,19 @@ __device__ __forceinline__ uint4 ldg_v4(const void* p) {
 __device__ __forceinline__ uint2 ldg_v2(const void* p) {
   uint2 v;
   asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+// thread-block-cluster helpers: barrier across the CTAs of a cluster, load from the shared memory
+// of CTA `rank` of the cluster at the offset that `addr` has in this CTA
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
   return v;
 }
 
@@ -308,7 +324,36 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
     return;
   }
 
-  // split-K: publish this CTA's partial, the last CTA of the tile sums them in split order
+  if (p.cluster) {
+    // split-K inside a thread-block cluster (the S splits of a tile are one cluster): every CTA
+    // leaves its k-way-reduced partial in its own shared memory; after a cluster barrier CTA r
+    // sums, in split order, the outputs i = r (mod S) from all CTAs' shared memory.
+    float* cpart = red + KW * p.m * kRedStride;
+    for (int i = tid; i < nout; i += blockDim.x) {
+      const int mm = i >> 7, r = i & 127;
+      float s = 0.f;
+      for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
+      cpart[i] = s;
+    }
+    cluster_barrier();
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(cpart));
+    // outputs of this CTA: i = split + j * S; the S partials of an output are fetched together
+    for (int i = split + tid * S; i < nout; i += blockDim.x * S) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (u < S) ? ld_cluster_f32(base + i * 4, u) : 0.f;
+      float s = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+      const int mm = i >> 7, n = tile * kTileRows + (i & 127);
+      if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+    }
+    cluster_barrier();  // nobody leaves while its shared memory may still be read
+    return;
+  }
+
+  // split-K through the workspace: publish this CTA's partial, the last CTA of the tile to
+  // arrive sums them in split order
   for (int i = tid; i < nout; i += blockDim.x) {
     const int mm = i >> 7, r = i & 127;
     float s = 0.f;
@@ -326,21 +371,70 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   if (!is_last) return;
   __threadfence();
   const size_t sstride = (size_t)p.m * p.npad;
-  for (int i = tid; i < nout; i += blockDim.x) {
-    const int mm = i >> 7, r = i & 127;
-    const int n = tile * kTileRows + r;
-    const float* base = p.partial + (size_t)mm * p.npad + n;
-    float s = 0.f;
-    int sp = 0;
-    for (; sp + 8 <= S; sp += 8) {
-      float v[8];
+  // every thread sums its (at most 16) outputs in split order, with either the loads of one split
+  // for all its outputs or those of eight splits for two outputs in flight together, whichever
+  // makes the shorter chain of round trips
+  constexpr int kMaxOut = 16;  // 16 rows x 128 outputs over at least 128 threads, 8 x 128 over at least 64
+  const int J = (nout + blockDim.x - 1) / blockDim.x;
+  float s[kMaxOut];
+  const float* src[kMaxOut];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(base + (size_t)(sp + u) * sstride);
+  for (int j = 0; j < kMaxOut; ++j) {
+    const int i = min(tid + j * (int)blockDim.x, nout - 1);
+    src[j] = p.partial + (size_t)(i >> 7) * p.npad + tile * kTileRows + (i & 127);
+    s[j] = 0.f;
+  }
+  if (2 * S > J) {  // few outputs per thread: two outputs at a time, eight splits in flight each
+    for (int j0 = 0; j0 < J; j0 += 2) {
+      const float* a0 = src[0];
+      const float* a1 = src[0];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) s += v[u];
+      for (int j = 0; j < kMaxOut; j += 2)
+        if (j == j0) {
+          a0 = src[j];
+          a1 = src[j + 1];
+        }
+      float s0 = 0.f, s1 = 0.f;
+      int sp = 0;
+      for (; sp + 8 <= S; sp += 8) {
+        float v0[8], v1[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          v0[u] = __ldcg(a0 + (size_t)(sp + u) * sstride);
+          v1[u] = __ldcg(a1 + (size_t)(sp + u) * sstride);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          s0 += v0[u];
+          s1 += v1[u];
+        }
+      }
+      for (; sp < S; ++sp) {
+        const float v0 = __ldcg(a0 + (size_t)sp * sstride), v1 = __ldcg(a1 + (size_t)sp * sstride);
+        s0 += v0;
+        s1 += v1;
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxOut; j += 2)
+        if (j == j0) {
+          s[j] = s0;
+          s[j + 1] = s1;
+        }
     }
-    for (; sp < S; ++sp) s += __ldcg(base + (size_t)sp * sstride);
-    if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+  } else {
+    for (int sp = 0; sp < S; ++sp) {
+      float v[kMaxOut];
+#pragma unroll
+      for (int j = 0; j < kMaxOut; ++j) v[j] = (j < J) ? __ldcg(src[j] + (size_t)sp * sstride) : 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxOut; ++j) s[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxOut; ++j) {
+    const int i = tid + j * (int)blockDim.x;
+    const int n = tile * kTileRows + (i & 127);
+    if (j < J && i < nout && n < p.n) p.y[(size_t)(i >> 7) * p.n + n] = __float2half_rn(s[j]);
   }
   if (tid == 0) p.counters[tile] = 0u;
 }
@@ -353,16 +447,74 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
   cfg.blockDim = dim3(block);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.cluster) {  // the K splits of one tile form a cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = grid.x;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = na;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// How many clusters of `cluster` CTAs (block threads, smem bytes of dynamic shared memory each)
+// the current device holds at once; cached per configuration.  0 when the query fails.
+template <int NT, int RB, bool SEG64>
+static int query_clusters(int block, size_t smem, int cluster) {
+  auto kern = gemv_mma_kernel<NT, RB, SEG64>;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster, 1024);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int mma_max_active_clusters(int nt, bool seg64, int block, size_t smem, int cluster) {
+  static std::mutex mu;
+  static std::map<unsigned long long, int> cache;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  const size_t smem_kb = (smem + 1023) / 1024;  // the answer only changes with the shared-memory footprint
+  const unsigned long long key = ((unsigned long long)dev << 48) | ((unsigned long long)nt << 44) |
+                                 ((unsigned long long)seg64 << 43) | ((unsigned long long)block << 28) |
+                                 ((unsigned long long)smem_kb << 8) | (unsigned long long)cluster;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  const size_t sm = smem_kb * 1024;
+  int n;
+  if (nt == 1) n = seg64 ? query_clusters<1, 4, true>(block, sm, cluster) : query_clusters<1, 4, false>(block, sm, cluster);
+  else n = seg64 ? query_clusters<2, 2, true>(block, sm, cluster) : query_clusters<2, 2, false>(block, sm, cluster);
+  cache[key] = n;
+  return n;
 }
 
 cudaError_t launch_gemv_mma(const MmaParams& p, int nt, dim3 grid, int block, size_t smem, bool pdl,

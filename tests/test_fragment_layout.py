@@ -163,12 +163,34 @@ def test_fragment_forward_every_split_and_kway_agrees():
     layer, x, q, s, z = _frag_layer(3, 256, 4096, 128, False, seed=77)
     xs = x.cuda()
     try:
-        for kw in (1, 2, 4):
-            for sp in (1, 2, 3, 5, 8, 32):
-                L.qfb_set_gemv_tuning(sp, kw)
-                _check(layer(xs), x, q, s, z)
+        for mode in (0, 2):  # K splits reduced through the workspace / inside a thread-block cluster
+            L.qfb_set_cluster_reduce(mode)
+            for kw in (1, 2, 4):
+                for sp in (1, 2, 3, 5, 8, 32):
+                    L.qfb_set_gemv_tuning(sp, kw)
+                    _check(layer(xs), x, q, s, z)
     finally:
         L.qfb_set_gemv_tuning(0, 0)
+        L.qfb_set_cluster_reduce(1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 8, 16])
+def test_cluster_and_workspace_reductions_agree(M):
+    L = _native.lib()
+    layer, x, q, s, z = _frag_layer(M, 640, 4096, 128, False, seed=5 + M)
+    xs = x.cuda()
+    outs = []
+    try:
+        for mode in (0, 2):
+            L.qfb_set_cluster_reduce(mode)
+            L.qfb_set_gemv_tuning(4, 2)
+            outs.append(layer(xs).clone())
+    finally:
+        L.qfb_set_gemv_tuning(0, 0)
+        L.qfb_set_cluster_reduce(1)
+    _check(outs[0], x, q, s, z)
+    assert torch.equal(outs[0], outs[1])  # same partials, same summation order
 
 
 @pytest.mark.gpu
