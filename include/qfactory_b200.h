@@ -65,6 +65,8 @@ typedef enum qfb_status {
                                     prefetches weights before it waits for the preceding kernel */
 #define QFB_FLAG_FORCE_SIMT 2u   /* always use the CUDA-core split-K kernel */
 #define QFB_FLAG_FORCE_TENSOR 4u /* always use the tcgen05 kernel (if the shape allows) */
+#define QFB_FLAG_NO_SYNC 8u      /* qfb_linear_forward_host only: do not synchronise the stream; the
+                                    caller queues several layers and synchronises once */
 
 /* packed layouts */
 #define QFB_LAYOUT_TILE 0      /* tile-128 interleaved: every bit width, every batch size */
@@ -117,7 +119,8 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y,
 /*
  * Same computation for callers that hold HOST buffers: copies x_host (pinned or pageable)
  * into x_staging, runs the layer, copies the result into y_host and synchronises `stream`
- * before returning.  x_staging / y_staging are caller-owned device buffers of m*k and m*n
+ * before returning (unless QFB_FLAG_NO_SYNC is set: then y_host is valid once the caller has
+ * synchronised the stream, and the staging buffers must not be reused before that).  x_staging / y_staging are caller-owned device buffers of m*k and m*n
  * fp16 elements.  No counterpart in the reference (its callers hold device tensors).
  */
 int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host,

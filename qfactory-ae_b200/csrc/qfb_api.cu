@@ -555,6 +555,7 @@ int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, v
   if (s != QFB_OK) return s;
   s = check_cuda(cudaMemcpyAsync(y_host, y_staging, (size_t)m * layer->n * 2, cudaMemcpyDeviceToHost, st));
   if (s != QFB_OK) return s;
+  if (flags & QFB_FLAG_NO_SYNC) return QFB_OK;
   return check_cuda(cudaStreamSynchronize(st));
 }
 

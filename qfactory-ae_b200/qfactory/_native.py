@@ -17,6 +17,7 @@ QFB_OK = 0
 FLAG_PDL = 1
 FLAG_FORCE_SIMT = 2
 FLAG_FORCE_TENSOR = 4
+FLAG_NO_SYNC = 8
 
 EXPORTS = (
     "qfb_version", "qfb_status_string", "qfb_last_cuda_error",

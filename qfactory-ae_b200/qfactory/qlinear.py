@@ -91,9 +91,11 @@ class _PackedLinear(torch.nn.Module):
             _native.check(st, "qfb_linear_forward")
         return out.view(*lead, self.out_features)
 
-    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, sync: bool = True) -> torch.Tensor:
         """Host-buffer entry: `x_host` (CPU fp16, ideally pinned) is copied in, the result is
-        copied back into `y_host` (CPU fp16) and the stream is synchronised."""
+        copied back into `y_host` (CPU fp16) and the stream is synchronised.  With `sync=False` the
+        call only queues the work: `y_host` is valid after the caller has synchronised the stream
+        (several layers can be queued and waited for once)."""
         if self._desc is None:
             self._prepare()
         x2 = x_host.reshape(-1, self.in_features)
@@ -108,7 +110,7 @@ class _PackedLinear(torch.nn.Module):
         xs, ys = self._host
         st = self._lib.qfb_linear_forward_host(
             ctypes.byref(self._desc), x2.data_ptr(), M, y_host.data_ptr(), xs.data_ptr(), ys.data_ptr(),
-            self._ws.data_ptr(), self._ws_bytes, self.flags,
+            self._ws.data_ptr(), self._ws_bytes, self.flags | (0 if sync else _native.FLAG_NO_SYNC),
             torch.cuda.current_stream(self.w.device).cuda_stream,
         )
         if st != 0:

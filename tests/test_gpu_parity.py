@@ -210,6 +210,11 @@ def test_host_buffer_entry_matches_device_entry():
     yh = torch.empty(4, 640, dtype=torch.float16).pin_memory()
     layer.forward_host(xh, yh)
     assert torch.equal(yh, layer(x.cuda()).cpu())
+    # queued form: nothing is waited for until the caller synchronises the stream
+    yq = torch.zeros(4, 640, dtype=torch.float16).pin_memory()
+    layer.forward_host(xh, yq, sync=False)
+    torch.cuda.current_stream().synchronize()
+    assert torch.equal(yq, yh)
 
 
 def test_pdl_flag_gives_identical_results():
