@@ -40,7 +40,7 @@ UNIT = "GB/s"
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch, from the ncu
 # captures of the (22016,4096) case summarised under profiles/; traffic grows with the weight
 # bytes, so the average launch of the sweep is scaled by the same factor
-NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": None}
+NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": 1.00795}
 WORKLOAD = "llama7b_layer_sweep_w4a16_g128_asym: (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)} x M in {1,4,16}"
 
 
@@ -349,30 +349,38 @@ def main():
         e2e_ms = f0.elapsed_time(f1)
         clocks = sampler.stop() if rank == 0 else None
 
-        # per-case breakdown: single launches timed with events, a 256 MB write between
-        # launches flushes L2 so the weights come from HBM every time
+        # per-case breakdown: each case as a CUDA graph over enough weight replicas (>= 400 MB) that
+        # every launch streams its weights from HBM; time per launch from events around the replays
         per_shape = []
         if args.per_shape and rank == 0:
-            flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
             for ci in range(n_cases):
-                name, M, layer0, *_ = cases[0][ci]
+                name, M, layer0, x, y, _, _ = cases[0][ci]
                 N, K = layer0.out_features, layer0.in_features
-                reps = 40
-                evs = []
-                for i in range(reps):
-                    flush.fill_(i & 0xFF)
-                    _, _, layer, x, y, _, _ = cases[i % REPL][ci]
+                R = max(2, min(48, (400 << 20) // (N * K * BITS // 8) + 1))
+                reps_l = [make_layer(N, K) for _ in range(R)]
+                st = torch.cuda.Stream(device=dev)
+                with torch.cuda.stream(st):
+                    reps_l[0](x, out=y)
+                    torch.cuda.synchronize()
+                    launch = _native.last_launch()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr, stream=st):
+                        for l in reps_l:
+                            l(x, out=y)
+                    for _ in range(3):
+                        gr.replay()
+                    torch.cuda.synchronize()
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     a.record()
-                    layer(x, out=y)
+                    for _ in range(10):
+                        gr.replay()
                     b.record()
-                    evs.append((a, b))
-                torch.cuda.synchronize()
-                ts = sorted(a.elapsed_time(b) for a, b in evs[5:])
-                med = ts[len(ts) // 2]
+                    torch.cuda.synchronize()
+                med = a.elapsed_time(b) / (10 * R)
+                del gr, reps_l
                 nb = algorithmic_bytes(M, N, K)
                 per_shape.append({"layer": name, "N": N, "K": K, "M": M, "us": round(med * 1e3, 2),
-                                  "GBps": round(nb / (med * 1e-3) / 1e9, 1), "launch": _native.last_launch()})
+                                  "GBps": round(nb / (med * 1e-3) / 1e9, 1), "launch": launch})
 
     # free the sweep's device memory before the decoder is built
     case_meta = [(M, layer.out_features, layer.in_features) for _, M, layer, *_ in cases[0]]
