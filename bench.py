@@ -116,6 +116,17 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def use_all_host_threads(torch):
+    """The CPU arm uses every host core this process may run on (torchrun exports
+    OMP_NUM_THREADS=1 to its workers, which would otherwise leave it on one thread)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    if n > torch.get_num_threads():
+        torch.set_num_threads(n)
+
+
 def run_reference(args, rank, world):
     """The reference's own CPU path for this workload (dequantize, then fp16 matmul, in torch
     on the host cores), restated in oracle/qf_oracle.py.  Each step is a bounded sample of
@@ -125,6 +136,7 @@ def run_reference(args, rank, world):
     import torch
     from oracle import qf_oracle as O
 
+    use_all_host_threads(torch)
     cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
     nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
 
@@ -160,6 +172,7 @@ def cpu_baseline_sample(budget_s=12.0):
     import torch
     from oracle import qf_oracle as O
 
+    use_all_host_threads(torch)
     cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
     nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
     best, t_start, passes = float("inf"), time.perf_counter(), 0
