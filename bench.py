@@ -204,7 +204,7 @@ def main():
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
-                    help="packed layout of the benchmark layers (auto: fragment for these batch sizes)")
+                    help="packed layout of the benchmark layers (auto: fragment for these 4-bit shapes)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

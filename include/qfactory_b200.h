@@ -28,8 +28,8 @@
  * warp-level tensor-core instruction (rows g and g+8 of a 16-row block, four k each):
  *   qweight  u32 [Npad/128][2 x 64 rows][K/16][32 lanes][4 row blocks]
  *   scales / zeros  [Npad/128][K/group][128] in fragment row order
- * It is the layout of choice for layers that mostly see batches of at most 16 rows (decode);
- * larger batches on such a layer are processed 16 rows at a time.
+ * Batches of at most 16 rows run the mma.sync GEMV on it, larger ones the tcgen05 kernel, which
+ * reads the same words; it is the layout of choice whenever the shape allows it.
  *
  * Zero-point semantics follow the reference packer and kernel: the stored, effective
  * zero is min(z + 1, 2^bits - 1) for GPTQ-convention zeros z
@@ -70,7 +70,7 @@ typedef enum qfb_status {
 
 /* packed layouts */
 #define QFB_LAYOUT_TILE 0      /* tile-128 interleaved: every bit width, every batch size */
-#define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: 4-bit, K % 128 == 0, small batches */
+#define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: 4-bit, K % 128 == 0, group 64 / n*128 / none */
 
 /* One packed layer.  Plain data; the caller owns the device buffers. */
 typedef struct qfb_layer {
@@ -146,7 +146,8 @@ int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* 
 size_t qfb_static_scratch_capacity(void);
 
 /* Which kernel qfb_linear_forward picks for a tile-layout layer: 1 = SIMT split-K GEMV,
- * 2 = tcgen05 GEMM, 0 = invalid.  Fragment-layout layers always run kernel 3 (mma.sync GEMV). */
+ * 2 = tcgen05 GEMM, 0 = invalid.  Fragment-layout layers run kernel 3 (mma.sync GEMV) up to 16
+ * rows and kernel 2 above. */
 int qfb_select_kernel(int m, int n, int k, int bits, unsigned flags);
 
 /* Smallest batch that is routed to the tensor-core kernel (default 2).  Process-wide. */

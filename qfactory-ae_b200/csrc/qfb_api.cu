@@ -181,6 +181,7 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   p.steps_per_group = gs / 16;
   p.halfstages_per_group = gs / 64;
   p.zconst = v.zconst;
+  p.layout = v.layout;
   p.partial = nullptr;
   p.counters = nullptr;
   p.status = nullptr;
@@ -533,10 +534,11 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
   if (m == 0) return QFB_OK;
   if (!x || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
-  if (v.layout == QFB_LAYOUT_FRAGMENT)
+  // fragment-layout layers: the mma.sync GEMV up to 16 rows, the tcgen05 kernel above
+  if (v.layout == QFB_LAYOUT_FRAGMENT && (m <= kMaxMmaRows || (flags & QFB_FLAG_FORCE_SIMT)))
     return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                    static_cast<cudaStream_t>(stream));
-  if (choose_kernel(v, m, flags) == 2)
+  if (v.layout == QFB_LAYOUT_FRAGMENT || choose_kernel(v, m, flags) == 2)
     return run_tc(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                   static_cast<cudaStream_t>(stream));
   return run_gemv(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,

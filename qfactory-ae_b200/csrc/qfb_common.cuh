@@ -208,6 +208,11 @@ __host__ __device__ inline int frag_row_of_pos(int pos) {
   return (pos >> 6) * 64 + ((pos >> 1) & 3) * 16 + (pos & 1) * 8 + ((pos >> 3) & 7);
 }
 
+// inverse of frag_row_of_pos: where row `r` of a tile sits in the fragment-ordered arrays
+__host__ __device__ inline int frag_pos_of_row(int r) {
+  return (r >> 6) * 64 + (r & 7) * 8 + ((r >> 4) & 3) * 2 + ((r >> 3) & 1);
+}
+
 // Host-visible description of a validated layer (filled by the API layer).
 struct LayerView {
   const uint4* qw;

@@ -113,6 +113,27 @@ template <> struct StageDecode<4> {
     }
   }
 };
+// Fragment layout (4-bit): stage = [2 halves of 64 rows][8 k-steps][32 lanes][4 row blocks x 4 B].
+// Row wt*64 + rb*16 + hh*8 + g owns, in the word of (k-step, lane g*4+t, row block rb), nibbles
+// 0,4,2,6 (hh = 0) or 1,5,3,7 (hh = 1) = k 4t..4t+3 of the step: two LOP3 per word with the
+// row's mask / magic give two exact fp16 pairs in k order.
+struct StageDecodeFragment4 {
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const Codec<4>::ZM zm = Codec<4>::zmagic(z);
+    const int wt = row >> 6, rb = (row >> 4) & 3, hh = (row >> 3) & 1, g = row & 7;
+    const uint32_t mask = hh ? 0x00f000f0u : 0x000f000fu, magic = hh ? 0x54005400u : 0x64006400u;
+    const __half2 zs = as_h2(hh ? zm.hi : zm.lo);
+    const uint8_t* base = w + wt * 4096 + (4 * h) * 512 + g * 64 + rb * 4;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(base + ks * 512 + t * 16);
+        d[ks * 8 + t * 2] = __hsub2(as_h2(lop3_and_or(word, mask, magic)), zs);
+        d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(lop3_and_or(word >> 8, mask, magic)), zs);
+      }
+  }
+};
 template <> struct StageDecode<8> {
   // stage = [8 units][128 rows][16 B]; thread owns units 4h .. 4h+3
   __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
@@ -254,7 +275,16 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
         mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
-        tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)i * Cfg::kWBytes, Cfg::kWBytes, bar);
+        if (BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT) {
+          // the stage is two runs of 4 KiB: 8 k-steps of the upper and of the lower 64 rows
+          const uint8_t* f0 = reinterpret_cast<const uint8_t*>(p.qw) +
+                              (((size_t)tile * 2) * (size_t)(p.kblocks * 8) + (size_t)(kb0 + i) * 8) * 512;
+          tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, f0, Cfg::kWBytes / 2, bar);
+          tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes + Cfg::kWBytes / 2, f0 + (size_t)p.kblocks * 8 * 512,
+                       Cfg::kWBytes / 2, bar);
+        } else {
+          tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)i * Cfg::kWBytes, Cfg::kWBytes, bar);
+        }
         if (zb) tma_bulk_g2s(sbase + z_off + s * Cfg::kZSlot, p.qz + ((size_t)tile * p.groups + g0) * kTileRows, zb, bar);
         if (sb) tma_bulk_g2s(sbase + s_off + s * Cfg::kSSlot, p.qs + ((size_t)tile * p.groups + g0) * kTileRows, sb, bar);
         gpos += 2;
@@ -326,6 +356,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     // with groups of 64 the two halves of a stage belong to different groups: half h reads
     // the second record of the stage's zero / scale slot
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
+    const bool frag = BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT;
+    // position of the row's scale / zero inside the tile's 128 (fragment layers keep them in fragment order)
+    const int qrow = qsel + (frag ? frag_pos_of_row(row) : row);
     TT_DECL(6);
     TT_START();
     static_assert(DG == 1, "ring positions below advance by one stage per iteration");
@@ -334,12 +367,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     for (int i = grp; i < nkb; i += DG) {
       if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode)) break;
       TT_ADD(0);
-      const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qsel + row] : p.zconst;
+      const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qrow] : p.zconst;
       __half2 d[32];
-      StageDecode<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
+      if (BITS == 4 && frag) StageDecodeFragment4::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
+      else StageDecode<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
       uint32_t rr[32];
       if (!POST && has_s) {
-        const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(gbase + s_off + s * Cfg::kSSlot)[qsel + row]);
+        const __half2 s2 = __half2half2(reinterpret_cast<const __half*>(gbase + s_off + s * Cfg::kSSlot)[qrow]);
 #pragma unroll
         for (int j = 0; j < 32; ++j) rr[j] = as_u32(__hmul2(d[j], s2));
       } else {
@@ -401,7 +435,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       float acc[NB];
 #pragma unroll
       for (int j = 0; j < NB; ++j) acc[j] = 0.f;
-      const size_t sz_row = (size_t)tile * p.groups * kTileRows + row;
+      const size_t sz_row = (size_t)tile * p.groups * kTileRows +
+                            ((BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT) ? frag_pos_of_row(row) : row);
       const int stages_per_group = p.halfstages_per_group >> 1;  // POST needs groups of whole stages
       int r = 0;
       uint32_t phr = 0;

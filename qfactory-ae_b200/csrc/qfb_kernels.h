@@ -69,6 +69,7 @@ struct TcParams {
   int steps_per_group;       // group_size / 16 MMA k-steps per quantisation group (K / 16 when group-less)
   int halfstages_per_group;  // group_size / 64
   uint32_t zconst;
+  int layout;                // QFB_LAYOUT_TILE, or QFB_LAYOUT_FRAGMENT (4-bit only)
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
 cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,

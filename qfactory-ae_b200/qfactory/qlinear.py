@@ -4,8 +4,8 @@
 Same names, arguments and error behaviour as the reference (reference:
 qfactory/qlinear.py:5-145).  Differences, all on purpose:
   * the packed tensors `.w/.s/.z` use the layouts of `convert.py`: `layout='tile'` (every bit
-    width and batch size), `layout='fragment'` (4-bit, made for batches of at most 16 rows) or
-    `layout='auto'` (the default: fragment when the layer is built for `batch_size <= 16`);
+    width), `layout='fragment'` (4-bit, K % 128 == 0: the tensor-core fragment order) or
+    `layout='auto'` (the default: fragment whenever the shape allows it);
   * the batch size is a run-time property of `forward`, not a compile-time constant, and
     `x` may have any number of leading dimensions;
   * kernel selection is a static heuristic inside the native library, so `compile_flags`

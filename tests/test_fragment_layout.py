@@ -4,6 +4,7 @@ CPU part: the torch packer against the documented nibble positions, round trips,
 GPU part (marked): device packer == torch packer byte for byte, unpack / dequantise bit-exact
 through the kernel's own field extraction, and the forward pass against the oracle with the same
 bar as the other parity tests (max-abs <= 1e-2 * ||y||_inf)."""
+import ctypes
 import random
 
 import numpy as np
@@ -84,7 +85,7 @@ def test_layout_choice():
     R = layout.resolve_layout
     assert R("auto", 4096, 4096, 4, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
     assert R(None, 4096, 4096, 4, 128, batch_size=16) == layout.LAYOUT_FRAGMENT
-    assert R("auto", 4096, 4096, 4, 128, batch_size=17) == layout.LAYOUT_TILE
+    assert R("auto", 4096, 4096, 4, 128, batch_size=512) == layout.LAYOUT_FRAGMENT   # any batch size
     assert R("auto", 4096, 4096, 8, 128, batch_size=1) == layout.LAYOUT_TILE      # 4-bit only
     assert R("auto", 4096, 4160, 4, 64, batch_size=1) == layout.LAYOUT_TILE       # K % 128 != 0
     assert R("auto", 4096, 4224, 4, 192, batch_size=1) == layout.LAYOUT_TILE      # group neither 64 nor k*128
@@ -141,9 +142,33 @@ def test_fragment_forward_against_oracle(M, GS, sym):
     N, K = 328, 1024
     layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=1000 + 17 * M + (GS % 91))
     y = layer(x.cuda())
-    assert _native.last_launch()["kernel"] == 3
+    # up to 16 rows: the mma.sync GEMV; above: the tcgen05 kernel reading the same fragment layout
+    assert _native.last_launch()["kernel"] == (3 if M <= 16 else 2)
     assert y.shape == (M, N) and y.dtype == torch.float16
     _check(y, x, q, s, z)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [17, 33, 64, 65, 130, 256, 300])
+@pytest.mark.parametrize("GS,sym", [(128, False), (64, False), (256, True), (-1, False)])
+def test_fragment_layer_large_batches_on_the_tcgen05_kernel(M, GS, sym):
+    N, K = 384, 2048
+    layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=2000 + M + (GS % 89))
+    y = layer(x.cuda())
+    assert _native.last_launch()["kernel"] == 2
+    _check(y, x, q, s, z)
+    st = ctypes.c_uint(0)
+    assert _native.lib().qfb_read_status(layer._ws.data_ptr(), None, ctypes.byref(st)) == 0 and st.value == 0
+
+
+@pytest.mark.gpu
+def test_fragment_and_tile_layers_agree_on_a_large_batch():
+    x, q, s, z = O.make_case(200, 640, 4096, 4, 128, False, seed=12)
+    a = QLinear.init(1, 4096, 640, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="fragment")
+    b = QLinear.init(1, 4096, 640, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="tile")
+    ya, yb = a(x.cuda()), b(x.cuda())
+    # same decode arithmetic ((q - z) exact, one fp16 rounding of the scale product), same MMA order
+    assert torch.equal(ya, yb)
 
 
 @pytest.mark.gpu
@@ -213,8 +238,8 @@ def test_fragment_forward_pdl_graph_and_default_layout():
     g.replay()
     torch.cuda.synchronize()
     _check(y, x, q, s, z)
-    big = QLinear.init(64, 2048, 512, 4, q.cuda(), 128, s.cuda(), z.cuda())  # built for large batches: tile layout
-    assert big.packed_layout == layout.LAYOUT_TILE
+    other = QLinear.init(64, 2048, 512, 8, q.cuda(), 128, s.cuda(), z.cuda())  # 8-bit: tile layout
+    assert other.packed_layout == layout.LAYOUT_TILE
 
 
 @pytest.mark.gpu
