@@ -287,7 +287,7 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
 }
 
 // ---- mma.sync GEMV over the fragment layout ---------------------------------------------
-struct MmaPlan { int nt, split, kways, cluster; size_t smem; };
+struct MmaPlan { int nt, split, kways, cluster, recv_offset; size_t smem; };
 
 static int mma_split_cap(int tiles, int batches) {
   return std::max(1, std::min(batches, (kNumSMs * 4 + tiles - 1) / tiles));
@@ -295,17 +295,21 @@ static int mma_split_cap(int tiles, int batches) {
 
 static size_t mma_smem(int rows, int nt, int bpc, int kways) {
   const size_t stage = (size_t)rows * (bpc * 128 + 16) * 2 + (size_t)bpc * 2 * 8 * nt * sizeof(float);
-  // k-way reduction lines plus the CTA's own partial for the in-cluster split-K reduction
-  const size_t red = (size_t)kways * rows * 132 * sizeof(float) + (size_t)rows * 128 * sizeof(float);
-  return std::max(stage, red);
+  const size_t red = (size_t)kways * rows * 132 * sizeof(float);  // k-way reduction lines
+  return (std::max(stage, red) + 15) / 16 * 16;
+}
+// the receive buffer of the in-cluster split-K reduction follows the region above
+static size_t mma_recv_bytes(int rows, int split) {
+  const int nout = rows * 128;
+  return (size_t)split * ((nout + split - 1) / split) * sizeof(float);
 }
 
 // Split-K factor, k-ways and reduction mode of the mma.sync GEMV.  Cost model fitted to sweeps
 // on B200, in units of one 128-k batch of one warp (~0.25 us): the CTAs of a launch should be
 // resident at once (a second wave costs a full CTA time); a CTA costs its longest k-way plus a
-// fixed part worth ~1.5 batches; reducing the splits inside a thread-block cluster costs a part
-// that grows with rows x splits, reducing them through the workspace a fixed fence / atomic /
-// re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
+// fixed part worth ~1.5 batches; reducing the splits inside a thread-block cluster costs a small
+// part that grows with rows x splits, reducing them through the workspace a fixed fence /
+// atomic / re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
 // inside one GPC, so a grid that fits by CTA count may still need a second wave).
 static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
   MmaPlan pl;
@@ -334,11 +338,12 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
         const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 0; }
       }
-      if (s > 1 && s <= 8 && g_mma_cluster && (pl.nt == 1 || s <= 4 || g_mma_cluster == 2)) {
-        const int fit = mma_max_active_clusters(pl.nt, seg64, block, smem, s);
+      if (s > 1 && s <= 8 && g_mma_cluster) {
+        const int fit = mma_max_active_clusters(pl.nt, seg64, block, smem + mma_recv_bytes(rows, s), s);
         if (fit > 0) {
           const int waves = (tiles + fit - 1) / fit;
-          const double cost = (double)waves * (per_kway + 1.5) + base + 0.09 * rows * s;
+          // (clusters that need several waves pack worse than single CTAs: measured ~15 % slower)
+          const double cost = (double)waves * (per_kway + 1.5) * (waves > 1 ? 1.15 : 1.0) + base + 0.02 * rows * s;
           if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 1; }
         }
       }
@@ -349,6 +354,8 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
   const int bpc = (batches + best_s - 1) / best_s;
   pl.kways = std::max(1, std::min(best_kw, batches / best_s > 0 ? batches / best_s : 1));
   pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
+  pl.recv_offset = (int)pl.smem;
+  if (pl.cluster) pl.smem += mma_recv_bytes(rows, pl.split);
   return pl;
 }
 
@@ -378,6 +385,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.counters = nullptr;
     // up to 8 splits reduce inside a thread-block cluster; more go through the workspace
     p.cluster = pl.cluster;
+    p.recv_offset = pl.recv_offset;
     if (pl.split > 1 && !p.cluster) {
       const size_t off = partial_offset(v.tiles);
       const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);

@@ -54,17 +54,15 @@ __device__ __forceinline__ uint2 ldg_v2(const void* p) {
   return v;
 }
 
-// thread-block-cluster helpers: barrier across the CTAs of a cluster, load from the shared memory
+// thread-block-cluster helpers: barrier across the CTAs of a cluster, store into the shared memory
 // of CTA `rank` of the cluster at the offset that `addr` has in this CTA
 __device__ __forceinline__ void cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, int rank, float v) {
   uint32_t ra;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-  return v;
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
 }
 
 constexpr int kRedStride = 132;  // floats per (k-way, batch row) line of the k-way reduction
@@ -325,30 +323,31 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   }
 
   if (p.cluster) {
-    // split-K inside a thread-block cluster (the S splits of a tile are one cluster): every CTA
-    // leaves its k-way-reduced partial in its own shared memory; after a cluster barrier CTA r
-    // sums, in split order, the outputs i = r (mod S) from all CTAs' shared memory.
-    float* cpart = red + KW * p.m * kRedStride;
+    // split-K inside a thread-block cluster (the S splits of a tile are one cluster): CTA r owns
+    // the outputs i = r (mod S).  Every CTA pushes its k-way-reduced partial of output i into a
+    // receive buffer in the OWNER's shared memory (slot = the sender's split), one cluster barrier
+    // makes the pushes visible, and each owner sums its S slots in split order.  The receive
+    // buffer is a region of its own: a fast CTA may push while a slow one still computes.
+    float* recv = reinterpret_cast<float*>(reinterpret_cast<char*>(smem) + p.recv_offset);
+    const uint32_t recv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(recv));
+    const int per = (nout + S - 1) / S;  // outputs per owner
     for (int i = tid; i < nout; i += blockDim.x) {
       const int mm = i >> 7, r = i & 127;
       float s = 0.f;
       for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
-      cpart[i] = s;
+      const int j = i / S, owner = i - j * S;
+      st_cluster_f32(recv_addr + (split * per + j) * 4, owner, s);
     }
     cluster_barrier();
-    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(cpart));
-    // outputs of this CTA: i = split + j * S; the S partials of an output are fetched together
-    for (int i = split + tid * S; i < nout; i += blockDim.x * S) {
-      float v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = (u < S) ? ld_cluster_f32(base + i * 4, u) : 0.f;
-      float s = 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) s += v[u];
-      const int mm = i >> 7, n = tile * kTileRows + (i & 127);
-      if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+    for (int j = tid; j < per; j += blockDim.x) {
+      const int i = split + j * S;
+      if (i < nout) {
+        float s = 0.f;
+        for (int u = 0; u < S; ++u) s += recv[u * per + j];
+        const int mm = i >> 7, n = tile * kTileRows + (i & 127);
+        if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+      }
     }
-    cluster_barrier();  // nobody leaves while its shared memory may still be read
     return;
   }
 

@@ -48,6 +48,7 @@ struct MmaParams {
   int batches_per_cta;   // ceil(batches / S): sizes the staged activation slice
   uint32_t zconst;
   int cluster;           // 1: the S splits of a tile are one thread-block cluster and reduce in shared memory
+  int recv_offset;       // byte offset of the cluster reduction's receive buffer in dynamic shared memory
 };
 // clusters of `cluster` CTAs of the mma.sync GEMV the current device holds at once (cached)
 int mma_max_active_clusters(int nt, bool seg64, int block, size_t smem, int cluster);
