@@ -203,6 +203,8 @@ def main():
                     "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
+    ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
+                    "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
                     help="packed layout of the benchmark layers (auto: fragment for these 4-bit shapes)")
     args = ap.parse_args()
@@ -285,8 +287,15 @@ def main():
         for rep in range(REPL):
             run_step(rep)  # builds descriptors / workspaces outside capture
         torch.cuda.synchronize()
+        class Eager:  # --graph 0: the same launches issued one by one (profiling aid)
+            def __init__(self, fn):
+                self.replay = fn
+
         graphs = []
         for rep in range(REPL):
+            if not args.graph:
+                graphs.append(Eager(lambda rep=rep: run_step(rep)))
+                continue
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr, stream=stream):
                 run_step(rep)
@@ -308,11 +317,17 @@ def main():
         for kid in sorted(set(kern_of)):
             gl = []
             for rep in range(REPL):
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr, stream=stream):
+                def sub_step(rep=rep, kid=kid):
                     for ci, (_, _, layer, x, y, _, _) in enumerate(cases[rep]):
                         if kern_of[ci] == kid:
                             layer(x, out=y)
+
+                if not args.graph:
+                    gl.append(Eager(sub_step))
+                    continue
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=stream):
+                    sub_step()
                 gl.append(gr)
             sub_graphs[kid] = gl
 
@@ -371,6 +386,8 @@ def main():
                 N, K = layer0.out_features, layer0.in_features
                 R = max(2, min(48, (400 << 20) // (N * K * BITS // 8) + 1))
                 reps_l = [make_layer(N, K) for _ in range(R)]
+                for l in reps_l:
+                    l._prepare()  # descriptor and workspace now, not inside the capture below
                 st = torch.cuda.Stream(device=dev)
                 with torch.cuda.stream(st):
                     reps_l[0](x, out=y)
@@ -452,7 +469,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS, "launches_per_step": n_cases,
                        "cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
-                       "graph": True, "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
+                       "graph": bool(args.graph), "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches * world,

@@ -400,7 +400,20 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     tl_last_launch[2] = grid.y;
     tl_last_launch[3] = block;
     tl_last_launch[4] = (int)pl.smem;
-    int stt = check_cuda(launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st));
+    cudaError_t ce = launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
+    if (ce != cudaSuccess && p.cluster) {
+      // a cluster launch the device refuses (e.g. a partitioned GPU): same split through the workspace
+      (void)cudaGetLastError();
+      const size_t off = partial_offset(v.tiles);
+      const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);
+      if (workspace && ws_bytes >= need) {
+        p.cluster = 0;
+        p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
+        p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
+        ce = launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
+      }
+    }
+    const int stt = check_cuda(ce);
     if (stt != QFB_OK) return stt;
   }
   return QFB_OK;

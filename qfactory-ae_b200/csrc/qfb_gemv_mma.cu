@@ -56,8 +56,11 @@ __device__ __forceinline__ uint2 ldg_v2(const void* p) {
 
 // thread-block-cluster helpers: barrier across the CTAs of a cluster, store into the shared memory
 // of CTA `rank` of the cluster at the offset that `addr` has in this CTA
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_barrier() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  cluster_arrive();
+  cluster_wait();
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, int rank, float v) {
   uint32_t ra;
@@ -126,6 +129,10 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   const int kw = warp / WPK;
   const int KW = (blockDim.x >> 5) / WPK;
   const int tile = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+  // Shared memory of another CTA of the cluster may only be touched once that CTA has started:
+  // every CTA arrives here, at its start, and waits for the others just before its first remote
+  // store, a whole main loop later (the wait is free by then).
+  if (p.cluster) cluster_arrive();
 
   // balanced ranges of 128-k batches: CTA [bb, be), this warp's k-way [wb, we)
   const int bb = (int)(((long long)split * p.batches) / S);
@@ -331,6 +338,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
     float* recv = reinterpret_cast<float*>(reinterpret_cast<char*>(smem) + p.recv_offset);
     const uint32_t recv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(recv));
     const int per = (nout + S - 1) / S;  // outputs per owner
+    cluster_wait();                      // pairs with the arrive at kernel start: every CTA of the cluster runs
     for (int i = tid; i < nout; i += blockDim.x) {
       const int mm = i >> 7, r = i & 127;
       float s = 0.f;
