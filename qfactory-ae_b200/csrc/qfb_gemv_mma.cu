@@ -80,17 +80,27 @@ __device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t 
 // the RB words (row blocks) of one lane and k-step: RB = 4 reads the lane's whole 16 bytes,
 // RB = 2 its lower or upper 8 bytes
 template <int RB> struct Words;
+// load_if keeps the predicate inside the instruction (no branch around the load), so that the
+// k-steps of a batch stay one basic block the compiler can schedule across
 template <> struct Words<4> {
   uint32_t v[4];
   __device__ __forceinline__ void load(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "l"(p));
   }
+  __device__ __forceinline__ void load_if(const void* p, int pred) {
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %5, 0;\n@q ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n}"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]) : "l"(p), "r"(pred));
+  }
 };
 template <> struct Words<2> {
   uint32_t v[2];
   __device__ __forceinline__ void load(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v[0]), "=r"(v[1]) : "l"(p));
+  }
+  __device__ __forceinline__ void load_if(const void* p, int pred) {
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %3, 0;\n@q ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n}"
+                 : "+r"(v[0]), "+r"(v[1]) : "l"(p), "r"(pred));
   }
 };
 
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
       const int b = b0 + sl;
       if (b >= we) break;
       const int lb = b - bb;
-      const bool more = b + NSLOT < we;
+      const int more = b + NSLOT < we ? 1 : 0;
 #pragma unroll
       for (int seg = 0; seg < NSEG; ++seg) {
         float d[RB][NT][4];
@@ -261,7 +271,8 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
             }
           }
           // the words of this k-step are consumed: fetch the same step of a later batch into them
-          if (more) w[sl][ks].load(wp + ks * kStepBytes);
+          if (RB == 4) w[sl][ks].load_if(wp + ks * kStepBytes, more);  // (measured: a gain for RB = 4 only)
+          else if (more) w[sl][ks].load(wp + ks * kStepBytes);
         }
         // fold the segment's accumulators into the results: s * 2^24 * D - s * z * sum(x)
         float dx[NT][2];
