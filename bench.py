@@ -13,8 +13,8 @@ metric / value: achieved GB/s = the reference's algorithmic-bytes model
 (activations + outputs + packed codes + fp16 scales + packed zeros) per step divided by
 the device time per step, inputs resident in HBM, the step replayed as a CUDA graph.
 e2e: the same bytes over the time of calling each case through the host-buffer entry
-(pinned host activations in, host result out; a step queues its 12 layers and waits for the
-stream once; copies and the wait are inside the timed region).  With N > 1 every rank runs its own replica of the sweep (the path has no
+(pinned host activations in, host result out; a step queues its 12 layers - captured once in a
+CUDA graph - and waits for the stream once; copies and the wait are inside the timed region).  With N > 1 every rank runs its own replica of the sweep (the path has no
 cross-rank exchange; weak scaling) and value is the sum over ranks on the slowest rank's
 time.
 """
@@ -203,6 +203,7 @@ def main():
                     "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
+    ap.add_argument("--host-streams", type=int, default=6, help="streams the end-to-end step spreads its layers over")
     ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
                     "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
@@ -360,17 +361,43 @@ def main():
 
         # end to end through the host-buffer entry point
         e2e_steps = max(3, min(args.steps, 50))
-        # a step queues its 12 layers (pinned x in, y out) and waits for the stream once
+        # a step queues its 12 layers (pinned x in, y out: H2D copy, kernel, D2H copy each) and waits
+        # for the stream once; the queued calls of a step are captured once in a CUDA graph, as a
+        # caller with a fixed set of layers would do, and the graph is replayed every step
+        # (the layers are independent, so they are spread over a few streams: the small PCIe
+        # copies of one layer overlap the kernels and copies of the others)
+        side = [torch.cuda.Stream(device=dev) for _ in range(max(1, args.host_streams))]
+
+        def host_step(rep):
+            main = torch.cuda.current_stream(dev)
+            for sd in side:
+                sd.wait_stream(main)
+            for i, (_, _, layer, _, _, xh, yh) in enumerate(cases[rep]):
+                with torch.cuda.stream(side[i % len(side)]):
+                    layer.forward_host(xh, yh, sync=False)
+            for sd in side:
+                main.wait_stream(sd)
+
+        for i in range(2):
+            host_step(i % REPL)  # allocates the staging buffers outside the capture
+            torch.cuda.current_stream(dev).synchronize()
+        host_graphs = []
+        for rep in range(REPL):
+            if not args.graph:
+                host_graphs.append(Eager(lambda rep=rep: host_step(rep)))
+                continue
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                host_step(rep)
+            host_graphs.append(gr)
         for i in range(3):
-            for _, _, layer, _, _, xh, yh in cases[i % REPL]:
-                layer.forward_host(xh, yh, sync=False)
+            host_graphs[i % REPL].replay()
             torch.cuda.current_stream(dev).synchronize()
         barrier()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for i in range(e2e_steps):
-            for _, _, layer, _, _, xh, yh in cases[i % REPL]:
-                layer.forward_host(xh, yh, sync=False)
+            host_graphs[i % REPL].replay()
             torch.cuda.current_stream(dev).synchronize()
         f1.record()
         barrier()
