@@ -352,7 +352,9 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
   pl.split = best_s;
   pl.cluster = best_cl;
   const int bpc = (batches + best_s - 1) / best_s;
-  pl.kways = std::max(1, std::min(best_kw, batches / best_s > 0 ? batches / best_s : 1));
+  // a power of two (the kernel splits a CTA's range among the k-ways with a shift), no more than the batches of a CTA
+  pl.kways = best_kw;
+  while (pl.kways > 1 && pl.kways > batches / best_s) pl.kways >>= 1;
   pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
   pl.recv_offset = (int)pl.smem;
   if (pl.cluster) pl.smem += mma_recv_bytes(rows, pl.split);
@@ -380,6 +382,8 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.chunks_per_group = (v.group_size == -1 ? v.k : v.group_size) / 64;
     p.batches = v.k / 128;
     p.batches_per_cta = (p.batches + pl.split - 1) / pl.split;
+    p.batches_div = p.batches / pl.split;
+    p.batches_mod = p.batches % pl.split;
     p.zconst = v.zconst;
     p.partial = nullptr;
     p.counters = nullptr;

@@ -144,12 +144,14 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   // store, a whole main loop later (the wait is free by then).
   if (p.cluster) cluster_arrive();
 
-  // balanced ranges of 128-k batches: CTA [bb, be), this warp's k-way [wb, we)
-  const int bb = (int)(((long long)split * p.batches) / S);
-  const int be = (int)(((long long)(split + 1) * p.batches) / S);
+  // balanced ranges of 128-k batches: CTA [bb, be), this warp's k-way [wb, we); no divisions on
+  // this path (the host passes batches / S and batches % S, the k-ways are a power of two)
+  const int bb = split * p.batches_div + min(split, p.batches_mod);
+  const int be = bb + p.batches_div + (split < p.batches_mod ? 1 : 0);
   const int ncta = be - bb;
-  const int wb = bb + (kw * ncta) / KW;
-  const int we = bb + ((kw + 1) * ncta) / KW;
+  const int kw_shift = KW == 4 ? 2 : (KW == 2 ? 1 : 0);
+  const int wb = bb + ((kw * ncta) >> kw_shift);
+  const int we = bb + (((kw + 1) * ncta) >> kw_shift);
 
   // 16 bytes per lane and k-step; this warp reads bytes [sub * 8, sub * 8 + 4 * RB) of them
   const char* wp = reinterpret_cast<const char*>(p.qw) +
@@ -158,9 +160,13 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
 
   // quantisation group of the warp's first segment, and the position inside it
   const int segs_per_group = SEG64 ? p.chunks_per_group : (p.chunks_per_group >> 1);
-  int grp = (wb * NSEG) / segs_per_group;
-  int gpos = wb * NSEG - grp * segs_per_group;
-  const int grp_last = (we * NSEG - 1) / segs_per_group;  // last group this warp touches
+  int grp = wb * NSEG, gpos = 0;
+  int grp_last = we * NSEG - 1;  // last group this warp touches
+  if (segs_per_group != 1) {     // (one segment per group, the common case, needs no division)
+    grp = (wb * NSEG) / segs_per_group;
+    gpos = wb * NSEG - grp * segs_per_group;
+    grp_last = (we * NSEG - 1) / segs_per_group;
+  }
 
   ScaleZero<RB> sz_cur, sz_nxt;
 #pragma unroll

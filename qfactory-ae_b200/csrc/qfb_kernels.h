@@ -46,6 +46,7 @@ struct MmaParams {
   int chunks_per_group;  // group_size / 64 (K / 64 when group-less)
   int batches;           // K / 128
   int batches_per_cta;   // ceil(batches / S): sizes the staged activation slice
+  int batches_div, batches_mod;  // batches / S and batches % S: split s owns batches_div (+1 if s < batches_mod)
   uint32_t zconst;
   int cluster;           // 1: the S splits of a tile are one thread-block cluster and reduce in shared memory
   int recv_offset;       // byte offset of the cluster reduction's receive buffer in dynamic shared memory
