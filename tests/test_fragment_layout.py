@@ -253,3 +253,31 @@ def test_fragment_extreme_codes_and_zeros():
         z = torch.full((K // GS, N), zero, dtype=torch.int32)
         layer = QLinear.init(M, K, N, 4, q.cuda(), GS, s.cuda(), z.cuda(), layout="fragment")
         _check(layer(x.cuda()), x, q, s, z)
+
+
+@pytest.mark.gpu
+def test_fragment_forward_random_shapes_and_plans():
+    """Seeded sweep over odd sizes, every group mode, forced splits / k-ways and both reductions."""
+    L = _native.lib()
+    rnd = random.Random(20241)
+    try:
+        for case in range(48):
+            K = 128 * rnd.choice([1, 2, 3, 5, 8, 11, 16, 24, 32])
+            N = rnd.choice([1, 7, 100, 128, 129, 255, 300, 513, 700])
+            M = rnd.randint(1, 16)
+            gs_ok = [g for g in (64, 128, 256, 384) if K % g == 0] + [-1]
+            GS = rnd.choice(gs_ok)
+            sym = GS != -1 and rnd.random() < 0.3
+            layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=5000 + case)
+            if rnd.random() < 0.7:  # forced plan, otherwise the built-in one
+                L.qfb_set_gemv_tuning(rnd.choice([1, 2, 3, 4, 6, 8, 13]), rnd.choice([1, 2, 4]))
+                L.qfb_set_cluster_reduce(rnd.choice([0, 2]))
+            else:
+                L.qfb_set_gemv_tuning(0, 0)
+                L.qfb_set_cluster_reduce(1)
+            y = layer(x.cuda())
+            assert _native.last_launch()["kernel"] == 3
+            _check(y, x, q, s, z)
+    finally:
+        L.qfb_set_gemv_tuning(0, 0)
+        L.qfb_set_cluster_reduce(1)
