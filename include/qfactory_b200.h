@@ -192,6 +192,23 @@ int qfb_unpack_codes(const qfb_layer* layer, int32_t* codes_out, void* stream);
 /* Dequantised fp16 weight [k, n] = (q - z_eff) * s, through the kernels' decode path. */
 int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream);
 
+/*
+ * Element-wise neighbours of the quantized linears in a decoder layer, one launch each.  The
+ * reference leaves them to its serving stack
+ * (third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-120, 260-285).
+ *   qfb_rmsnorm:  y[r,:] = fp16(x[r,:] * rsqrt(mean(x[r,:]^2) + eps)) * w     x, y fp16 [rows, d], w fp16 [d]
+ *   qfb_silu_mul: out[r,j] = silu(gate_up[r,j]) * gate_up[r,half+j]           gate_up fp16 [rows, 2*half]
+ *   qfb_rope_cache: rotary embedding (interleaved pairs, fp16 arithmetic) of the query and key heads
+ *                 of qkv fp16 [B, T, hq + 2 hkv, hd], in place, at positions pos i64 [T]; the rotated
+ *                 keys and the values are also written into k_cache / v_cache fp16
+ *                 [B, hkv, max_len, hd] at those positions.  cos, sin fp16 [max_len, hd / 2].
+ * d and half are multiples of 8, hd is even; all pointers 16-byte aligned.
+ */
+int qfb_rope_cache(void* qkv, const void* cos, const void* sin, const void* pos, void* k_cache, void* v_cache,
+                   int batch, int tokens, int q_heads, int kv_heads, int head_dim, int max_len, void* stream);
+int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float eps, void* stream);
+int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -650,6 +650,36 @@ static int run_unpack(const qfb_layer* layer, int32_t* codes_out, void* w_out, v
   return check_cuda(launch_unpack(p, static_cast<cudaStream_t>(stream)));
 }
 
+int qfb_rope_cache(void* qkv, const void* cosv, const void* sinv, const void* pos, void* k_cache, void* v_cache,
+                   int batch, int tokens, int q_heads, int kv_heads, int head_dim, int max_len, void* stream) {
+  if (!qkv || !cosv || !sinv || !pos || !k_cache || !v_cache) return QFB_ERR_NULL_POINTER;
+  if (batch < 0 || tokens < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || head_dim % 2 != 0 || max_len <= 0)
+    return QFB_ERR_BAD_SHAPE;
+  if (batch == 0 || tokens == 0) return QFB_OK;
+  return check_cuda(launch_rope_cache(static_cast<__half*>(qkv), static_cast<const __half*>(cosv),
+                                      static_cast<const __half*>(sinv), static_cast<const long long*>(pos),
+                                      static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), batch, tokens,
+                                      q_heads, kv_heads, head_dim, max_len, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float eps, void* stream) {
+  if (!x || !w || !y) return QFB_ERR_NULL_POINTER;
+  if (rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return QFB_ERR_MISALIGNED;
+  if (rows == 0) return QFB_OK;
+  return check_cuda(launch_rmsnorm(static_cast<const __half*>(x), static_cast<const __half*>(w),
+                                   static_cast<__half*>(y), rows, d, eps, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* stream) {
+  if (!gate_up || !out) return QFB_ERR_NULL_POINTER;
+  if (rows < 0 || half <= 0 || half % 8 != 0) return QFB_ERR_BAD_SHAPE;
+  if (!aligned16(gate_up) || !aligned16(out)) return QFB_ERR_MISALIGNED;
+  if (rows == 0) return QFB_OK;
+  return check_cuda(launch_silu_mul(static_cast<const __half*>(gate_up), static_cast<__half*>(out), rows, half,
+                                    static_cast<cudaStream_t>(stream)));
+}
+
 int qfb_unpack_codes(const qfb_layer* layer, int32_t* codes_out, void* stream) {
   if (!codes_out) return QFB_ERR_NULL_POINTER;
   return run_unpack(layer, codes_out, nullptr, stream);

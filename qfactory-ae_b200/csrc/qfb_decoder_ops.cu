@@ -1,0 +1,132 @@
+// Small element-wise neighbours of the quantized linears in a decoder layer: RMSNorm, SiLU * up,
+// rotary embedding with the key / value cache write.  Each replaces a chain of framework kernels
+// (eight for the norm) by one launch; all are HBM / launch bound and hold no state.
+//
+// The reference runs these through its serving stack's own kernels
+// (third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-120, 260-285); they sit on
+// either side of the quantized linears this library replaces.
+#include "qfb_common.cuh"
+#include "qfb_kernels.h"
+
+namespace qfb {
+
+// y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w     (fp16 in / out, fp32 arithmetic;
+// the product with rstd is rounded to fp16 before the weight multiply, as x.half() * w does)
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                      __half* __restrict__ y, int d, float eps) {
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  const int nv = d >> 3;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = xr[i];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(as_h2(u[j]));
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += (i < (int)(blockDim.x >> 5)) ? red[i] : 0.f;
+  const float rstd = rsqrtf(tot / (float)d + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * d);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = xr[i], g = wr[i];
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(as_h2(u[j]));
+      const __half2 n = __floats2half2_rn(f.x * rstd, f.y * rstd);
+      o[j] = as_u32(__hmul2(n, as_h2(gw[j])));
+    }
+    yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// out[r, j] = silu(gu[r, j]) * gu[r, half + j]   for j < half   (fp16, silu and product as fp16 ops)
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int half,
+                                                       long long total_vec) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-element vector each
+  if (i >= total_vec) return;
+  const int vec_per_row = half >> 3;
+  const long long r = i / vec_per_row;
+  const int j = (int)(i - r * vec_per_row);
+  const uint4 a = reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * half)[j];
+  const uint4 b = reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * half + half)[j];
+  const uint32_t ua[4] = {a.x, a.y, a.z, a.w}, ub[4] = {b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 f = __half22float2(as_h2(ua[q]));
+    // silu in fp32, rounded to fp16, then the fp16 product (what F.silu(g) * u computes)
+    const __half2 s = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+    o[q] = as_u32(__hmul2(s, as_h2(ub[q])));
+  }
+  reinterpret_cast<uint4*>(out + (size_t)r * half)[j] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Rotary embedding of the query and key heads of a fused QKV activation, in place, and the write
+// of the rotated keys and the values into the static caches at positions pos[t]:
+//   qkv      fp16 [B, T, hq + 2 hkv, hd]     (pairs (2i, 2i+1) rotate by the angle of pos[t], frequency i)
+//   cos/sin  fp16 [max_len, hd / 2]
+//   k_cache, v_cache  fp16 [B, hkv, max_len, hd]
+// Every product and sum is an fp16 operation, as the framework expression t1*c - t2*s computes.
+__global__ void __launch_bounds__(256) rope_cache_kernel(__half* __restrict__ qkv, const __half* __restrict__ cosv,
+                                                         const __half* __restrict__ sinv, const long long* __restrict__ pos,
+                                                         __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                                                         int T, int hq, int hkv, int hd, int max_len, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one pair of elements each
+  if (idx >= total) return;
+  const int hp = hd >> 1, H = hq + 2 * hkv;
+  const int i = (int)(idx % hp);
+  long long r = idx / hp;
+  const int h = (int)(r % H);
+  r /= H;
+  const int t = (int)(r % T);
+  const int b = (int)(r / T);
+  const long long p = pos[t];
+  __half2* src = reinterpret_cast<__half2*>(qkv + (((size_t)b * T + t) * H + h) * hd) + i;
+  __half2 v = *src;
+  if (h < hq + hkv) {
+    const __half c = cosv[(size_t)p * hp + i], s = sinv[(size_t)p * hp + i];
+    const __half x1 = __low2half(v), x2 = __high2half(v);
+    v = __halves2half2(__hsub(__hmul(x1, c), __hmul(x2, s)), __hadd(__hmul(x1, s), __hmul(x2, c)));
+    *src = v;
+  }
+  if (h >= hq) {
+    const bool is_k = h < hq + hkv;
+    __half* cache = is_k ? k_cache : v_cache;
+    const int hh = is_k ? h - hq : h - hq - hkv;
+    reinterpret_cast<__half2*>(cache + (((size_t)b * hkv + hh) * max_len + (size_t)p) * hd)[i] = v;
+  }
+}
+
+cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sinv, const long long* pos, __half* k_cache,
+                              __half* v_cache, int B, int T, int hq, int hkv, int hd, int max_len, cudaStream_t st) {
+  const long long total = (long long)B * T * (hq + 2 * hkv) * (hd >> 1);
+  rope_cache_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(qkv, cosv, sinv, pos, k_cache, v_cache, T, hq, hkv, hd,
+                                                                      max_len, total);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm(const __half* x, const __half* w, __half* y, int rows, int d, float eps, cudaStream_t st) {
+  rmsnorm_kernel<<<rows, 256, 0, st>>>(x, w, y, d, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(const __half* gu, __half* out, int rows, int half, cudaStream_t st) {
+  const long long total = (long long)rows * (half >> 3);
+  silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gu, out, half, total);
+  return cudaGetLastError();
+}
+
+}  // namespace qfb

@@ -5,8 +5,9 @@ Llama-2-70B architecture (80 layers, d = 8192, 64 query heads / 8 KV heads, FFN 
 vocab 32000), every linear W4A16 g128.  The sharding follows the reference's serve path
 (reference: third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-285 with
 layers/linear.py:382-394, 1100-1124): fused QKV and gate+up are column-parallel (no
-collective), O and down are row-parallel followed by ONE all-reduce each.  RMSNorm, RoPE and
-attention are plain torch: they are not the path this library accelerates.
+collective), O and down are row-parallel followed by ONE all-reduce each.  RMSNorm, SiLU * up and
+RoPE with the cache write are one native launch each (ops.py; `native_ops=False` keeps the plain
+torch expressions, which the tests compare against); attention is torch's SDPA.
 
 Weights are random packed bytes generated on the device (the reference's own end-to-end
 runs also used uninitialised weights, third_party/vllm-qfactory.patch:223-228).
@@ -18,7 +19,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import _native
+from . import _native, ops
 from .parallel import all_reduce_sum
 from .qlinear import QLinear
 
@@ -67,8 +68,10 @@ class DecoderLayer(torch.nn.Module):
 
 
 class QuantDecoder(torch.nn.Module):
-    def __init__(self, cfg: DecoderConfig, world: int = 1, rank: int = 0, device="cuda", seed: int = 0, batch: int = 1):
+    def __init__(self, cfg: DecoderConfig, world: int = 1, rank: int = 0, device="cuda", seed: int = 0, batch: int = 1,
+                 native_ops: bool = True):
         super().__init__()
+        self.native_ops = native_ops
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
         gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
@@ -85,8 +88,9 @@ class QuantDecoder(torch.nn.Module):
         self.k_cache = torch.zeros(cfg.layers, batch, hkv, cfg.max_len, hd, dtype=torch.float16, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
 
-    @staticmethod
-    def _rms(x, w):
+    def _rms(self, x, w):
+        if self.native_ops:
+            return ops.rmsnorm(x.contiguous(), w, 1e-5)
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
 
@@ -108,9 +112,12 @@ class QuantDecoder(torch.nn.Module):
             h = self._rms(x, blk.norm1)
             qkv = blk.qkv(h.view(B * T, -1)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
             q, k, v = qkv[:, :, : blk.hq], qkv[:, :, blk.hq : blk.hq + blk.hkv], qkv[:, :, blk.hq + blk.hkv :]
-            q, k = self._rope(q, pos), self._rope(k, pos)
-            self.k_cache[li].index_copy_(2, pos, k.transpose(1, 2))
-            self.v_cache[li].index_copy_(2, pos, v.transpose(1, 2))
+            if self.native_ops:
+                ops.rope_cache(qkv, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)
+            else:
+                q, k = self._rope(q, pos), self._rope(k, pos)
+                self.k_cache[li].index_copy_(2, pos, k.transpose(1, 2))
+                self.v_cache[li].index_copy_(2, pos, v.transpose(1, 2))
             att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
                                                  attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
             o = blk.o(att.transpose(1, 2).reshape(B * T, -1))
@@ -119,7 +126,7 @@ class QuantDecoder(torch.nn.Module):
             h = self._rms(x, blk.norm2)
             gu = blk.gate_up(h.view(B * T, -1))
             half = gu.shape[-1] // 2
-            act = F.silu(gu[:, :half]) * gu[:, half:]
+            act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
             dn = blk.down(act)
             all_reduce_sum(dn)                                    # row parallel
             x = x + dn.view(B, T, -1)

@@ -1,0 +1,81 @@
+"""The element-wise neighbours of the linears (RMSNorm, SiLU * up, RoPE + cache write) against the
+plain torch expressions they replace in the decoder."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from qfactory import ops
+from qfactory.decoder import DecoderConfig, QuantDecoder
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,d", [(1, 8192), (3, 4096), (16, 512), (130, 1000)])
+def test_rmsnorm_matches_the_torch_expression(rows, d):
+    g = torch.Generator(device="cuda").manual_seed(rows + d)
+    x = (torch.randn(rows, d, generator=g, device="cuda") * 3).half()
+    w = (torch.rand(d, generator=g, device="cuda") + 0.5).half()
+    xf = x.float()
+    want = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
+    got = ops.rmsnorm(x, w, 1e-5)
+    # the reduction order differs, so the fp32 reciprocal root may differ in its last bit: at most one
+    # fp16 step on a few elements
+    diff = (got.float() - want.float()).abs()
+    assert (diff <= want.float().abs() * 2 ** -9 + 1e-6).all()
+    assert (diff == 0).float().mean() > 0.98
+
+
+@pytest.mark.parametrize("rows,half", [(1, 28672), (5, 11008), (16, 1024)])
+def test_silu_mul_matches_the_torch_expression(rows, half):
+    g = torch.Generator(device="cuda").manual_seed(half)
+    gu = (torch.randn(rows, 2 * half, generator=g, device="cuda") * 2).half()
+    want = F.silu(gu[:, :half]) * gu[:, half:]
+    got = ops.silu_mul(gu)
+    diff = (got.float() - want.float()).abs()
+    assert (diff <= want.float().abs() * 2 ** -9 + 1e-6).all()   # the fast exponential: one fp16 step at most
+    assert (diff == 0).float().mean() > 0.97
+
+
+def test_rope_cache_is_bit_identical_to_the_torch_expression():
+    B, T, hq, hkv, hd, L = 2, 5, 8, 2, 64, 32
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(B, T, hq + 2 * hkv, hd, generator=g, device="cuda").half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(L, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().half(), ang.sin().half()
+    pos = torch.tensor([3, 4, 9, 10, 31], device="cuda")
+
+    def rope(t):
+        c, s = cos[pos][None, :, None, :], sin[pos][None, :, None, :]
+        t1, t2 = t[..., 0::2], t[..., 1::2]
+        return torch.stack((t1 * c - t2 * s, t1 * s + t2 * c), dim=-1).flatten(-2)
+
+    q_want, k_want = rope(qkv[:, :, :hq]), rope(qkv[:, :, hq:hq + hkv])
+    v_want = qkv[:, :, hq + hkv:].clone()
+    kc = torch.zeros(B, hkv, L, hd, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    work = qkv.clone()
+    ops.rope_cache(work, cos, sin, pos, kc, vc, hq, hkv)
+    assert torch.equal(work[:, :, :hq], q_want) and torch.equal(work[:, :, hq:hq + hkv], k_want)
+    assert torch.equal(work[:, :, hq + hkv:], v_want)
+    assert torch.equal(kc[:, :, pos], k_want.transpose(1, 2)) and torch.equal(vc[:, :, pos], v_want.transpose(1, 2))
+    untouched = torch.ones(L, dtype=torch.bool, device="cuda")
+    untouched[pos] = False
+    assert (kc[:, :, untouched] == 0).all() and (vc[:, :, untouched] == 0).all()
+
+
+def test_decoder_with_native_ops_matches_decoder_with_torch_ops():
+    cfg = DecoderConfig(layers=2, d_model=512, n_heads=8, n_kv_heads=2, d_ff=1024, vocab=1000, max_len=64)
+    a = QuantDecoder(cfg, device="cuda", seed=4, batch=2, native_ops=True)
+    b = QuantDecoder(cfg, device="cuda", seed=4, batch=2, native_ops=False)
+    for m in (a, b):
+        for blk in m.blocks:
+            for l in (blk.qkv, blk.o, blk.gate_up, blk.down):
+                l.s.mul_(40.0)
+    tokens = torch.randint(0, cfg.vocab, (2, 7), device="cuda")
+    with torch.no_grad():
+        ya = a(tokens, torch.arange(7, device="cuda")).float()
+        yb = b(tokens, torch.arange(7, device="cuda")).float()
+    assert torch.isfinite(ya).all()
+    assert (ya - yb).abs().max() <= 5e-3 * yb.abs().max()
+    assert (a.k_cache[:, :, :, :7].float() - b.k_cache[:, :, :, :7].float()).abs().max() <= 1e-2
