@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(256) rope_cache_kernel(__half* __restrict__ qk
   if (h < hq + hkv) {
     const __half c = cosv[(size_t)p * hp + i], s = sinv[(size_t)p * hp + i];
     const __half x1 = __low2half(v), x2 = __high2half(v);
-    v = __halves2half2(__hsub(__hmul(x1, c), __hmul(x2, s)), __hadd(__hmul(x1, s), __hmul(x2, c)));
+    // (_rn forms: the compiler must not contract a product and a sum into one fused multiply-add)
+    v = __halves2half2(__hsub_rn(__hmul_rn(x1, c), __hmul_rn(x2, s)), __hadd_rn(__hmul_rn(x1, s), __hmul_rn(x2, c)));
     *src = v;
   }
   if (h >= hq) {
