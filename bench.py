@@ -41,6 +41,15 @@ UNIT = "GB/s"
 # captures of the (22016,4096) case summarised under profiles/; traffic grows with the weight
 # bytes, so the average launch of the sweep is scaled by the same factor
 NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": 1.00795}
+# (N, K) of the linear layers of other model families, and squares, for --sweep
+SWEEP_FAMILIES = {
+    "llama2-13b": [(5120, 5120), (27648, 5120), (5120, 13824), (15360, 5120)],
+    "llama2-70b": [(8192, 8192), (57344, 8192), (8192, 28672), (10240, 8192)],
+    "qwen2.5-7b": [(3584, 3584), (37888, 3584), (3584, 18944), (4608, 3584)],
+    "qwen2.5-32b": [(5120, 5120), (55296, 5120), (5120, 27648), (7168, 5120)],
+    "qwen2.5-72b": [(8192, 8192), (59392, 8192), (8192, 29696), (10240, 8192)],
+    "squares-pure": [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (16384, 16384), (32768, 32768)],
+}
 WORKLOAD = "llama7b_layer_sweep_w4a16_g128_asym: (N,K) in {(12288,4096),(4096,4096),(22016,4096),(4096,11008)} x M in {1,4,16}"
 
 
@@ -204,6 +213,8 @@ def main():
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
     ap.add_argument("--host-streams", type=int, default=6, help="streams the end-to-end step spreads its layers over")
+    ap.add_argument("--sweep", default="", help="comma-separated families of SWEEP_FAMILIES: per-shape bandwidth at "
+                    "M = 1 instead of the benchmark (one JSON line per family)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
                     "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
@@ -254,6 +265,54 @@ def main():
         torch.cuda.synchronize()
         print(json.dumps({"case": args.case, "reps": args.reps, "launch": _native.last_launch(),
                           "algorithmic_bytes": algorithmic_bytes(M, N, K)}))
+        return
+
+    if args.sweep:
+        # bandwidth against layer size for other model families' shapes (reference:
+        # reproduce/fig9/plot_bandwidth_size.py, shapes of data/nkg_shapes.json): each layer alone at
+        # M = 1, graph replay over >= 400 MB of rotating weight replicas; one JSON line per family
+        for fam in args.sweep.split(","):
+            rows = []
+            for N, K in SWEEP_FAMILIES[fam]:
+                for gs in ((GS, -1) if fam == "squares-pure" else (GS,)):
+                    R = max(2, min(48, (400 << 20) // (N * K * BITS // 8) + 1))
+                    ls = []
+                    for _ in range(R):
+                        L = QLinear.empty(1, K, N, BITS, gs, sym=False, device=dev, layout=args.layout)
+                        L.w.random_(-128, 127)
+                        if gs != -1:
+                            L.s.uniform_(0.002, 0.02)
+                            L.z.random_(0, 15)
+                        L.flags = flags
+                        L._prepare()
+                        ls.append(L)
+                    x = torch.randn(1, K, device=dev).half()
+                    y = torch.empty(1, N, dtype=torch.float16, device=dev)
+                    st = torch.cuda.Stream(device=dev)
+                    with torch.cuda.stream(st):
+                        ls[0](x, out=y)
+                        torch.cuda.synchronize()
+                        launch = _native.last_launch()
+                        gr = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(gr, stream=st):
+                            for L in ls:
+                                L(x, out=y)
+                        for _ in range(3):
+                            gr.replay()
+                        torch.cuda.synchronize()
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record()
+                        for _ in range(10):
+                            gr.replay()
+                        b.record()
+                        torch.cuda.synchronize()
+                    us = a.elapsed_time(b) * 1e3 / (10 * R)
+                    nb = algorithmic_bytes(1, N, K, BITS, gs, False)
+                    rows.append({"N": N, "K": K, "group": gs, "us": round(us, 2), "GBps": round(nb / us / 1e3, 1),
+                                 "MB": round(nb / 1e6, 1), "kernel": launch["kernel"], "grid_x": launch["grid_x"]})
+                    del gr, ls
+                    torch.cuda.empty_cache()
+            print(json.dumps({"sweep": fam, "bits": BITS, "M": 1, "peak_GBps": measured_peaks()[0], "rows": rows}))
         return
 
     def make_layer(N, K):
