@@ -213,8 +213,9 @@ def main():
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
     ap.add_argument("--host-streams", type=int, default=6, help="streams the end-to-end step spreads its layers over")
-    ap.add_argument("--sweep", default="", help="comma-separated families of SWEEP_FAMILIES: per-shape bandwidth at "
-                    "M = 1 instead of the benchmark (one JSON line per family)")
+    ap.add_argument("--sweep", default="", help="comma-separated sweeps instead of the benchmark, one JSON line each: "
+                    "a family of SWEEP_FAMILIES (sizes at M = 1), 'bits' (2/3/4/8-bit on 8192x8192) or 'batch' "
+                    "(M = 1..1024 on the Llama-70B MLP shapes)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
                     "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
@@ -268,51 +269,63 @@ def main():
         return
 
     if args.sweep:
-        # bandwidth against layer size for other model families' shapes (reference:
-        # reproduce/fig9/plot_bandwidth_size.py, shapes of data/nkg_shapes.json): each layer alone at
-        # M = 1, graph replay over >= 400 MB of rotating weight replicas; one JSON line per family
-        for fam in args.sweep.split(","):
-            rows = []
-            for N, K in SWEEP_FAMILIES[fam]:
-                for gs in ((GS, -1) if fam == "squares-pure" else (GS,)):
-                    R = max(2, min(48, (400 << 20) // (N * K * BITS // 8) + 1))
-                    ls = []
-                    for _ in range(R):
-                        L = QLinear.empty(1, K, N, BITS, gs, sym=False, device=dev, layout=args.layout)
-                        L.w.random_(-128, 127)
-                        if gs != -1:
-                            L.s.uniform_(0.002, 0.02)
-                            L.z.random_(0, 15)
-                        L.flags = flags
-                        L._prepare()
-                        ls.append(L)
-                    x = torch.randn(1, K, device=dev).half()
-                    y = torch.empty(1, N, dtype=torch.float16, device=dev)
-                    st = torch.cuda.Stream(device=dev)
-                    with torch.cuda.stream(st):
-                        ls[0](x, out=y)
-                        torch.cuda.synchronize()
-                        launch = _native.last_launch()
-                        gr = torch.cuda.CUDAGraph()
-                        with torch.cuda.graph(gr, stream=st):
-                            for L in ls:
-                                L(x, out=y)
-                        for _ in range(3):
-                            gr.replay()
-                        torch.cuda.synchronize()
-                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        a.record()
-                        for _ in range(10):
-                            gr.replay()
-                        b.record()
-                        torch.cuda.synchronize()
-                    us = a.elapsed_time(b) * 1e3 / (10 * R)
-                    nb = algorithmic_bytes(1, N, K, BITS, gs, False)
-                    rows.append({"N": N, "K": K, "group": gs, "us": round(us, 2), "GBps": round(nb / us / 1e3, 1),
-                                 "MB": round(nb / 1e6, 1), "kernel": launch["kernel"], "grid_x": launch["grid_x"]})
-                    del gr, ls
-                    torch.cuda.empty_cache()
-            print(json.dumps({"sweep": fam, "bits": BITS, "M": 1, "peak_GBps": measured_peaks()[0], "rows": rows}))
+        # Other sweeps of the reference, each layer alone, graph replay over >= 400 MB of rotating
+        # weight replicas; one JSON line per sweep:
+        #   <family>  bandwidth against layer size at M = 1 (reference: reproduce/fig9/plot_bandwidth_size.py,
+        #             shapes of data/nkg_shapes.json)
+        #   bits      2/3/4/8-bit, asymmetric and symmetric, on (8192,8192), M = 1, group 128
+        #   batch     W4 g128 on the Llama-70B MLP shapes, M = 1 .. 1024 (GEMV -> tcgen05 GEMM)
+        def time_layer(N, K, M, bits, gs, sym):
+            R = max(2, min(48, (400 << 20) // (N * K * bits // 8) + 1))
+            ls = []
+            for _ in range(R):
+                L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=args.layout)
+                L.w.random_(-128, 127)
+                if L.s is not None:
+                    L.s.uniform_(0.002, 0.02)
+                if L.z is not None:
+                    L.z.view(torch.uint8).random_(0, (1 << bits) - 1)
+                L.flags = flags
+                L._prepare()
+                ls.append(L)
+            x = torch.randn(M, K, device=dev).half()
+            y = torch.empty(M, N, dtype=torch.float16, device=dev)
+            st = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(st):
+                ls[0](x, out=y)
+                torch.cuda.synchronize()
+                launch = _native.last_launch()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=st):
+                    for L in ls:
+                        L(x, out=y)
+                for _ in range(3):
+                    gr.replay()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(10):
+                    gr.replay()
+                b.record()
+                torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / (10 * R)
+            nb = algorithmic_bytes(M, N, K, bits, gs, sym)
+            del gr, ls
+            torch.cuda.empty_cache()
+            return {"N": N, "K": K, "M": M, "bits": bits, "group": gs, "sym": sym, "us": round(us, 2),
+                    "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(2.0 * M * N * K / us / 1e6, 1),
+                    "MB": round(nb / 1e6, 1), "kernel": launch["kernel"], "grid_x": launch["grid_x"]}
+
+        for name in args.sweep.split(","):
+            if name == "bits":
+                rows = [time_layer(8192, 8192, 1, b, GS, sym) for b in (2, 3, 4, 8) for sym in (False, True)]
+            elif name == "batch":
+                rows = [time_layer(N, K, M, BITS, GS, False) for N, K in ((28672, 8192), (8192, 28672))
+                        for M in (1, 2, 4, 8, 16, 32, 64, 128, 256, 1024)]
+            else:
+                rows = [time_layer(N, K, 1, BITS, gs, False) for N, K in SWEEP_FAMILIES[name]
+                        for gs in ((GS, -1) if name == "squares-pure" else (GS,))]
+            print(json.dumps({"sweep": name, "peak_GBps": measured_peaks()[0], "rows": rows}), flush=True)
         return
 
     def make_layer(N, K):
