@@ -186,6 +186,18 @@ int qfb_pack_layout(const int32_t* codes, const void* scales, const int32_t* zer
                     void* zeros_out, void* stream);
 int qfb_layout_supported(int layout, int n, int k, int bits, int group_size);
 
+/*
+ * fp16 weight [k, n] -> group-wise asymmetric quantisation, the front end of "construct a layer
+ * from an fp16 weight".  Replaces the reference's test helper asymmetric_quant
+ * (tests/acc_gptq.py:10-29) bit for bit: per group of group_size rows and per column
+ *   scale = (max - min) / (2^bits - 1),  zero = trunc(max(-min / (max - min) * (2^bits - 1) - 1, 0)),
+ *   code  = trunc((w - min) / (max - min) * (2^bits - 1)),      every operation rounded to fp16.
+ * Outputs: codes i32 [k, n], scales f16 [k/group, n], zeros i32 [k/group, n] (GPTQ "zero - 1"
+ * convention): exactly the inputs of qfb_pack.
+ */
+int qfb_quantize(const void* weight, int k, int n, int bits, int group_size, int32_t* codes_out,
+                 void* scales_out, int32_t* zeros_out, void* stream);
+
 /* Inverse of the code packing through the kernels' own bit-extraction path:
  * writes i32 codes [k, n].  Used by the bit-exactness tests. */
 int qfb_unpack_codes(const qfb_layer* layer, int32_t* codes_out, void* stream);

@@ -108,14 +108,17 @@ static TcPlan plan_tc(const LayerView& v, int m) {
     pl.nb = !pl.post ? 64 : m <= 16 ? 16 : 32;
     pl.mtiles = 1;
     const int kblocks = v.k / 128;
-    const int target = kNumSMs * ((pl.post && pl.nb <= 16 && pl.dg == 1) ? 2 : 1);
+    const int target = kNumSMs * ((pl.post && pl.nb <= 32 && pl.dg == 1) ? 2 : 1);
     int split = std::max(1, target / v.tiles);
     split = std::min(split, std::max(1, kblocks / 4));
     split = std::min(split, 32);
     // measured: the wider the batch tile, the dearer a split (partials, reduce, per-CTA fill);
     // beyond 8 rows it only pays while the tiles alone leave most SMs idle or K is very long
     if (pl.nb == 16 && m > 8 && v.tiles >= 90) split = 1;
-    if (pl.nb == 32 && kblocks < 80) split = 1;
+    if (pl.nb == 32) {  // two CTAs per SM: few tiles want a power-of-two split, many tiles none (measured)
+      if (v.tiles >= 90) split = 1;
+      else while (split & (split - 1)) split &= split - 1;
+    }
     if (pl.nb == 64 && kblocks < 160) split = 1;
     if (g_tc_split > 0) split = std::min(g_tc_split, std::max(1, kblocks));
     if (v.tiles > 512) split = 1;  // the counter array holds 512 tiles x 4 row quarters
@@ -625,6 +628,15 @@ int qfb_pack_layout(const int32_t* codes, const void* scales, const int32_t* zer
   p.groups = group_size == -1 ? 1 : k / group_size;
   p.layout = layout;
   return check_cuda(launch_pack(p, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_quantize(const void* weight, int k, int n, int bits, int group_size, int32_t* codes_out, void* scales_out,
+                 int32_t* zeros_out, void* stream) {
+  if (!weight || !codes_out || !scales_out || !zeros_out) return QFB_ERR_NULL_POINTER;
+  if (!valid_bits(bits)) return QFB_ERR_UNSUPPORTED;
+  if (k <= 0 || n <= 0 || group_size <= 0 || k % group_size != 0) return QFB_ERR_BAD_SHAPE;
+  return check_cuda(launch_quantize(static_cast<const __half*>(weight), k, n, bits, group_size, codes_out,
+                                    static_cast<__half*>(scales_out), zeros_out, static_cast<cudaStream_t>(stream)));
 }
 
 static int run_unpack(const qfb_layer* layer, int32_t* codes_out, void* w_out, void* stream) {

@@ -73,9 +73,9 @@ struct TcCfg {
   static constexpr int kZSlot = 256;   // effective zeros of a stage: 128 rows x up to 2 groups
   static constexpr int kSSlot = 512;   // fp16 scales of a stage (PRE mode only)
   static constexpr int kQBytes = kZSlot + (POST ? 0 : kSSlot);
-  static constexpr bool kTwoPerSM = POST && NB <= 16 && DG == 1;   // smallest batches: two CTAs share an SM
+  static constexpr bool kTwoPerSM = POST && NB <= 32 && DG == 1;   // small batches: two CTAs share an SM
   static constexpr int kBudget = kTwoPerSM ? 98 * 1024 : 224 * 1024;
-  static constexpr int kXStages = NB <= 16 ? 6 : NB <= 32 ? 8 : NB <= 64 ? 6 : NB <= 128 ? 4 : (BITS == 8 ? 2 : 3);
+  static constexpr int kXStages = NB <= 16 ? 6 : NB <= 32 ? (POST ? 4 : 8) : NB <= 64 ? 6 : NB <= 128 ? 4 : (BITS == 8 ? 2 : 3);
   static constexpr int kWStagesRaw = (kBudget - kXStages * kXBytes) / (kWBytes + kQBytes);
   static constexpr int kWStages = kWStagesRaw > 16 ? 16 : kWStagesRaw;
   static constexpr int kTmemCols = kTwoPerSM ? 256 : 512;

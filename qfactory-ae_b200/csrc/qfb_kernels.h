@@ -95,6 +95,9 @@ struct PackParams {
 };
 cudaError_t launch_pack(const PackParams& p, cudaStream_t st);
 
+cudaError_t launch_quantize(const __half* w, int k, int n, int bits, int group_size, int32_t* codes, __half* scales,
+                            int32_t* zeros, cudaStream_t st);
+
 struct UnpackParams {
   const uint4* qw;
   const __half* qs;

@@ -238,6 +238,46 @@ __global__ void unpack_kernel(const UnpackParams p) {
   }
 }
 
+// fp16 weight [K, N] -> group-wise asymmetric codes, scales and GPTQ-convention zeros, the front end
+// of "construct a layer from an fp16 weight" (reference: tests/acc_gptq.py:10-29).  One thread per
+// (group, column); every operation is rounded to fp16 exactly where the reference's fp16 tensor
+// expression rounds (each division and product computed in fp32 and rounded once), so the result
+// equals the framework expression bit for bit.
+__device__ __forceinline__ __half h_div(__half a, __half b) { return __float2half_rn(__half2float(a) / __half2float(b)); }
+__device__ __forceinline__ __half h_mul(__half a, float b) { return __float2half_rn(__half2float(a) * b); }
+
+__global__ void quantize_kernel(const __half* __restrict__ w, int k, int n, int group_size, int levels,
+                                int32_t* __restrict__ codes, __half* __restrict__ scales, int32_t* __restrict__ zeros) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int groups = k / group_size;
+  if (idx >= (long long)groups * n) return;
+  const int col = (int)(idx % n), g = (int)(idx / n);
+  const __half* src = w + (size_t)g * group_size * n + col;
+  __half wmax = src[0], wmin = src[0];
+  for (int i = 1; i < group_size; ++i) {
+    const __half v = src[(size_t)i * n];
+    wmax = __hmax(wmax, v);
+    wmin = __hmin(wmin, v);
+  }
+  const __half span = __hsub_rn(wmax, wmin);
+  scales[idx] = __float2half_rn(__half2float(span) / (float)levels);
+  // zero = trunc(max(-min / span * levels - 1, 0))
+  const __half zf = __hsub_rn(h_mul(h_div(__hneg(wmin), span), (float)levels), __float2half_rn(1.f));
+  zeros[idx] = (int32_t)__half2float(__hmax(zf, __float2half_rn(0.f)));
+  for (int i = 0; i < group_size; ++i) {
+    const __half q = h_mul(h_div(__hsub_rn(src[(size_t)i * n], wmin), span), (float)levels);
+    codes[(size_t)(g * group_size + i) * n + col] = (int32_t)__half2float(q);
+  }
+}
+
+cudaError_t launch_quantize(const __half* w, int k, int n, int bits, int group_size, int32_t* codes, __half* scales,
+                            int32_t* zeros, cudaStream_t st) {
+  const long long total = (long long)(k / group_size) * n;
+  quantize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(w, k, n, group_size, (1 << bits) - 1, codes, scales,
+                                                                    zeros);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st) {
   if (p.layout == QFB_LAYOUT_FRAGMENT) {
     const int block = 256;

@@ -79,3 +79,30 @@ def test_decoder_with_native_ops_matches_decoder_with_torch_ops():
     assert torch.isfinite(ya).all()
     assert (ya - yb).abs().max() <= 5e-3 * yb.abs().max()
     assert (a.k_cache[:, :, :, :7].float() - b.k_cache[:, :, :, :7].float()).abs().max() <= 1e-2
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_native_quantizer_matches_the_reference_fixture(golden_dir, bits):
+    import os
+
+    import numpy as np
+
+    from qfactory.quantize import asymmetric_quant
+
+    f = np.load(os.path.join(golden_dir, f"quant_b{bits}.npz"))  # produced by the reference's own helper
+    q, s, z = asymmetric_quant(torch.from_numpy(f["w"]).cuda(), int(f["GS"]), bits)
+    assert np.array_equal(q.cpu().numpy(), f["q"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), f["s"].view(np.uint16))
+    assert np.array_equal(z.cpu().numpy(), f["z"])
+
+
+@pytest.mark.parametrize("bits,GS,K,N", [(4, 128, 1024, 300), (3, 128, 512, 64), (8, 64, 256, 1000), (2, 256, 512, 17)])
+def test_native_quantizer_matches_the_torch_expression(bits, GS, K, N):
+    from qfactory.quantize import asymmetric_quant
+
+    g = torch.Generator().manual_seed(bits * 1000 + K)
+    w = (torch.randn(K, N, generator=g) * 0.05).half()
+    q0, s0, z0 = asymmetric_quant(w, GS, bits)            # CPU: the vectorised torch expression
+    q1, s1, z1 = asymmetric_quant(w.cuda(), GS, bits)     # CUDA: the native kernel
+    assert torch.equal(q1.cpu(), q0) and torch.equal(z1.cpu(), z0)
+    assert torch.equal(s1.cpu().view(torch.int16), s0.view(torch.int16))
