@@ -44,7 +44,7 @@ static int validate_shape(int n, int k, int bits, int group_size) {
 static int validate_layout(int layout, int k, int bits, int group_size) {
   if (layout == QFB_LAYOUT_TILE) return QFB_OK;
   if (layout != QFB_LAYOUT_FRAGMENT) return QFB_ERR_UNSUPPORTED;
-  if (bits != 4) return QFB_ERR_UNSUPPORTED;
+  if (bits != 4 && bits != 8 && bits != 2) return QFB_ERR_UNSUPPORTED;
   if (group_size != -1 && group_size != 64 && group_size % 128 != 0) return QFB_ERR_BAD_SHAPE;
   return k % 128 == 0 ? QFB_OK : QFB_ERR_BAD_SHAPE;
 }
@@ -314,12 +314,13 @@ static size_t mma_recv_bytes(int rows, int split) {
 // part that grows with rows x splits, reducing them through the workspace a fixed fence /
 // atomic / re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
 // inside one GPC, so a grid that fits by CTA count may still need a second wave).
-static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
+static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
-  const int wpk = pl.nt == 1 ? 2 : 4;       // warps per k-way: 2 x 64 rows (m <= 8) or 4 x 32 rows
-  const int kways_max = pl.nt == 1 ? 4 : 2;  // at most 256 threads
+  // warps per k-way: 2 x 64 rows (m <= 8, 2- and 4-bit) or 4 x 32 rows; at most 256 threads
+  const int wpk = (pl.nt == 1 && bits != 8) ? 2 : 4;
+  const int kways_max = 8 / wpk;
   const int cap = mma_split_cap(tiles, batches);
   const size_t smem_max = 100 * 1024;
   int best_s = cap, best_kw = 1, best_cl = 0;
@@ -342,7 +343,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64) {
         if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 0; }
       }
       if (s > 1 && s <= 8 && g_mma_cluster) {
-        const int fit = mma_max_active_clusters(pl.nt, seg64, block, smem + mma_recv_bytes(rows, s), s);
+        const int fit = mma_max_active_clusters(bits, pl.nt, seg64, block, smem + mma_recv_bytes(rows, s), s);
         if (fit > 0) {
           const int waves = (tiles + fit - 1) / fit;
           // (clusters that need several waves pack worse than single CTAs: measured ~15 % slower)
@@ -368,7 +369,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
                    unsigned flags, cudaStream_t st) {
   for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
     const int rows = std::min(kMaxMmaRows, m - m0);
-    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64);
+    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
     MmaParams p;
     p.qw = v.qw;
@@ -401,13 +402,13 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
       p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
     }
     const dim3 grid(pl.split, v.tiles);
-    const int block = (pl.nt == 1 ? 64 : 128) * pl.kways;
+    const int block = ((pl.nt == 1 && v.bits != 8) ? 64 : 128) * pl.kways;
     tl_last_launch[0] = 3;
     tl_last_launch[1] = grid.x;
     tl_last_launch[2] = grid.y;
     tl_last_launch[3] = block;
     tl_last_launch[4] = (int)pl.smem;
-    cudaError_t ce = launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
+    cudaError_t ce = launch_gemv_mma(p, v.bits, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
     if (ce != cudaSuccess && p.cluster) {
       // a cluster launch the device refuses (e.g. a partitioned GPU): same split through the workspace
       (void)cudaGetLastError();
@@ -417,7 +418,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
         p.cluster = 0;
         p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
         p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
-        ce = launch_gemv_mma(p, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
+        ce = launch_gemv_mma(p, v.bits, pl.nt, grid, block, pl.smem, (flags & QFB_FLAG_PDL) != 0, st);
       }
     }
     const int stt = check_cuda(ce);
@@ -501,7 +502,7 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
       }
     }
   }
-  if (bits == 4 && k % 128 == 0) {  // fragment-layout layers: the mma.sync GEMV's split bound
+  if (bits != 3 && k % 128 == 0) {  // fragment-layout layers: the mma.sync GEMV's split bound
     const size_t rows_mma = (size_t)std::min(m_max, kMaxMmaRows);
     partial = std::max(partial, (size_t)mma_split_cap(tiles, k / 128) * rows_mma * npad * sizeof(float));
   }
@@ -562,8 +563,9 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
   if (m == 0) return QFB_OK;
   if (!x || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
-  // fragment-layout layers: the mma.sync GEMV up to 16 rows, the tcgen05 kernel above
-  if (v.layout == QFB_LAYOUT_FRAGMENT && (m <= kMaxMmaRows || (flags & QFB_FLAG_FORCE_SIMT)))
+  // fragment-layout layers: the mma.sync GEMV up to 16 rows, the tcgen05 kernel above (it reads the
+  // 4-bit fragment words; 2- and 8-bit fragment layers run the GEMV 16 rows at a time)
+  if (v.layout == QFB_LAYOUT_FRAGMENT && (m <= kMaxMmaRows || v.bits != 4 || (flags & QFB_FLAG_FORCE_SIMT)))
     return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                    static_cast<cudaStream_t>(stream));
   if (v.layout == QFB_LAYOUT_FRAGMENT || choose_kernel(v, m, flags) == 2)

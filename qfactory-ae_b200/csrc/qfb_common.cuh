@@ -203,6 +203,60 @@ __device__ __forceinline__ void frag4_fields(uint32_t w, uint32_t (&a)[4]) {
   a[2] = hi & 0x000f000fu;
   a[3] = hi & 0x00f000f0u;
 }
+// The fragment layout for 8 and 2 bits follows the same ownership (lane (g, t) holds rows g and
+// g + 8 of each of the four row blocks of a 64-row half, k = 4t .. 4t+3 of a 16-k step):
+//   8-bit: two words per row block (row g, row g + 8), byte i = k 4t + i; the row blocks 0,1 of all
+//          lanes form one 512-byte chunk of the step, the row blocks 2,3 the next one;
+//   2-bit: one word per PAIR of row blocks; the 2-bit field of (row block parity p, row half h,
+//          k offset kk) sits at bit 4p + 2h + 16 (kk & 1) + 8 (kk >> 1), so the four fields a row
+//          needs share one bit offset inside a half-word (and one power-of-two scale).
+// FragCodec<BITS>::decode builds the four A-fragment registers of row block rb from the lane's
+// words of a k-step; shift_lo / shift_hi are the bit offsets of the fields of rows g / g + 8
+// inside a half (the fp16 subnormal they form is q * 2^(shift - 24)).
+// word j of a lane and field position of code (rb, h, kk):
+__host__ __device__ inline int frag_word_of(int bits, int rb, int h) {
+  return bits == 4 ? rb : bits == 8 ? rb * 2 + h : rb >> 1;
+}
+__host__ __device__ inline int frag_bit_of(int bits, int rb, int h, int kk) {
+  if (bits == 8) return 8 * kk;
+  if (bits == 4) return 4 * ((kk >> 1) * 2 + (kk & 1) * 4 + h);
+  return (rb & 1) * 4 + h * 2 + (kk & 1) * 16 + (kk >> 1) * 8;
+}
+template <int BITS> struct FragCodec;
+template <> struct FragCodec<4> {
+  __device__ static __forceinline__ void decode(const uint32_t* v, int rb, uint32_t (&a)[4]) { frag4_fields(v[rb], a); }
+  __host__ __device__ static constexpr int shift_lo(int) { return 0; }
+  __host__ __device__ static constexpr int shift_hi(int) { return 4; }
+};
+template <> struct FragCodec<8> {
+  __device__ static __forceinline__ void decode(const uint32_t* v, int rb, uint32_t (&a)[4]) {
+    a[0] = prmt(v[2 * rb], 0u, 0x4140u);
+    a[2] = prmt(v[2 * rb], 0u, 0x4342u);
+    a[1] = prmt(v[2 * rb + 1], 0u, 0x4140u);
+    a[3] = prmt(v[2 * rb + 1], 0u, 0x4342u);
+  }
+  __host__ __device__ static constexpr int shift_lo(int) { return 0; }
+  __host__ __device__ static constexpr int shift_hi(int) { return 0; }
+};
+template <> struct FragCodec<2> {
+  __device__ static __forceinline__ void decode(const uint32_t* v, int rb, uint32_t (&a)[4]) {
+    const uint32_t w = v[rb >> 1], hi = w >> 8;
+    const uint32_t m0 = 0x00030003u << ((rb & 1) * 4), m1 = m0 << 2;
+    a[0] = w & m0;
+    a[1] = w & m1;
+    a[2] = hi & m0;
+    a[3] = hi & m1;
+  }
+  __host__ __device__ static constexpr int shift_lo(int rb) { return (rb & 1) * 4; }
+  __host__ __device__ static constexpr int shift_hi(int rb) { return (rb & 1) * 4 + 2; }
+};
+// byte offset of word j of a lane inside the k-step of a 64-row half, and bytes of a k-step
+__host__ __device__ inline int frag_word_offset(int bits, int lane, int j) {
+  if (bits == 8) return (j >> 2) * 512 + lane * 16 + (j & 3) * 4;
+  return lane * (4 * bits) + j * 4;
+}
+__host__ __device__ inline int frag_step_bytes(int bits) { return 128 * bits; }
+
 // row inside the 128-row tile held at position `pos` of the fragment-ordered scale / zero arrays
 __host__ __device__ inline int frag_row_of_pos(int pos) {
   return (pos >> 6) * 64 + ((pos >> 1) & 3) * 16 + (pos & 1) * 8 + ((pos >> 3) & 7);

@@ -77,9 +77,8 @@ __device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-// the RB words (row blocks) of one lane and k-step: RB = 4 reads the lane's whole 16 bytes,
-// RB = 2 its lower or upper 8 bytes
-template <int RB> struct Words;
+// the words of one lane and k-step a warp holds: 4 (16 bytes), 2 or 1
+template <int NW> struct Words;
 // load_if keeps the predicate inside the instruction (no branch around the load), so that the
 // k-steps of a batch stay one basic block the compiler can schedule across
 template <> struct Words<4> {
@@ -104,6 +103,16 @@ template <> struct Words<2> {
   }
 };
 
+template <> struct Words<1> {
+  uint32_t v[1];
+  __device__ __forceinline__ void load(const void* p) {
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v[0]) : "l"(p));
+  }
+  __device__ __forceinline__ void load_if(const void* p, int pred) {
+    if (pred) load(p);
+  }
+};
+
 // raw scales (one half2 = rows g, g+8 per row block) and zeros (one byte per row) of a thread's rows
 template <int RB> struct ScaleZero {
   uint32_t s[RB];
@@ -119,16 +128,19 @@ template <int RB> struct ScaleZero {
   }
 };
 
+// BITS  = 4, 8 or 2 (FragCodec in qfb_common.cuh)
 // NT    = number of 8-column batch tiles (m <= 8 * NT)
-// RB    = 16-row blocks per warp: 4 (a warp owns 64 rows) or 2 (32 rows, two batches in flight)
+// RB    = 16-row blocks per warp: 4 (a warp owns 64 rows) or 2 (32 rows)
 // SEG64 = quantisation groups of 64 (a segment = 4 k-steps) instead of >= 128 (8 k-steps)
 // A segment is the run of k-steps whose MMA accumulator is folded into the results at once
 // with one scale and zero per row: min(group, 128) k.
-template <int NT, int RB, bool SEG64>
+template <int BITS, int NT, int RB, bool SEG64>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
+  using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
   constexpr int NSEG = SEG64 ? 2 : 1;  // segments per 128-k batch
-  constexpr int NSLOT = 4 / RB;        // register buffers of one batch each
+  constexpr int NW = RB * BITS / 4;    // words of a lane and k-step this warp holds
+  constexpr int NSLOT = NW >= 4 ? 1 : 2;  // register buffers of one batch each (32 registers in all, 16 for NW = 1)
   constexpr int WPK = 8 / RB;          // warps per k-way: 128 rows / (16 * RB)
   extern __shared__ uint4 smem[];
 
@@ -153,10 +165,12 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   const int wb = bb + ((kw * ncta) >> kw_shift);
   const int we = bb + (((kw + 1) * ncta) >> kw_shift);
 
-  // 16 bytes per lane and k-step; this warp reads bytes [sub * 8, sub * 8 + 4 * RB) of them
+  // 4 * BITS bytes per lane and k-step for the four row blocks; this warp reads the words of
+  // its RB row blocks (for RB = 2: the lower or upper half of them)
+  constexpr int kStepBytes = 128 * BITS, kBatchBytes = 8 * kStepBytes;
   const char* wp = reinterpret_cast<const char*>(p.qw) +
-                   (((size_t)(tile * 2 + wt) * p.ksteps + (size_t)wb * 8) * 32 + lane) * 16 + sub * 8;
-  constexpr int kStepBytes = 32 * 16, kBatchBytes = 8 * kStepBytes;
+                   ((size_t)(tile * 2 + wt) * p.ksteps + (size_t)wb * 8) * kStepBytes +
+                   frag_word_offset(BITS, lane, sub * NW);
 
   // quantisation group of the warp's first segment, and the position inside it
   const int segs_per_group = SEG64 ? p.chunks_per_group : (p.chunks_per_group >> 1);
@@ -175,7 +189,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   for (int i = 0; i < RB / 2; ++i) sz_cur.z[i] = sz_nxt.z[i] = 0;
   auto sz_offset = [&](int gi) { return (((size_t)tile * p.groups + gi) * 2 + wt) * 64 + g * 8 + sub * 4; };
 
-  Words<RB> w[NSLOT][8];
+  Words<NW> w[NSLOT][8];
 #pragma unroll
   for (int sl = 0; sl < NSLOT; ++sl)
     if (wb + sl < we) {
@@ -269,7 +283,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
 #pragma unroll
           for (int rb = 0; rb < RB; ++rb) {
             uint32_t a[4];
-            frag4_fields(w[sl][ks].v[rb], a);
+            FC::decode(w[sl][ks].v, rb, a);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               if (k4 == 0) mma_m16n8k16_zero(d[rb][nt], a, bf[nt][0], bf[nt][1]);
@@ -277,7 +291,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
             }
           }
           // the words of this k-step are consumed: fetch the same step of a later batch into them
-          if (RB == 4) w[sl][ks].load_if(wp + ks * kStepBytes, more);  // (measured: a gain for RB = 4 only)
+          if (NSLOT == 1) w[sl][ks].load_if(wp + ks * kStepBytes, more);  // (measured: a gain with one buffer only)
           else if (more) w[sl][ks].load(wp + ks * kStepBytes);
         }
         // fold the segment's accumulators into the results: s * 2^24 * D - s * z * sum(x)
@@ -298,7 +312,8 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
             z0 = (float)(zb & 0xffu);
             z1 = (float)((zb >> 8) & 0xffu);
           }
-          const float a0 = sf.x * 16777216.f, a1 = sf.y * 1048576.f;  // undo 2^-24 (row g) and 2^-20 (row g+8)
+          // undo the power of two of the subnormal fields: 2^(24 - bit offset inside the half)
+          const float a0 = sf.x * (float)(1 << (24 - FC::shift_lo(rb))), a1 = sf.y * (float)(1 << (24 - FC::shift_hi(rb)));
           const float b0 = -sf.x * z0, b1 = -sf.y * z1;
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
@@ -463,9 +478,9 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   if (tid == 0) p.counters[tile] = 0u;
 }
 
-template <int NT, int RB, bool SEG64>
+template <int BITS, int NT, int RB, bool SEG64>
 static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
-  auto kern = gemv_mma_kernel<NT, RB, SEG64>;
+  auto kern = gemv_mma_kernel<BITS, NT, RB, SEG64>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(block);
@@ -496,9 +511,9 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
 
 // How many clusters of `cluster` CTAs (block threads, smem bytes of dynamic shared memory each)
 // the current device holds at once; cached per configuration.  0 when the query fails.
-template <int NT, int RB, bool SEG64>
+template <int BITS, int NT, int RB, bool SEG64>
 static int query_clusters(int block, size_t smem, int cluster) {
-  auto kern = gemv_mma_kernel<NT, RB, SEG64>;
+  auto kern = gemv_mma_kernel<BITS, NT, RB, SEG64>;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return 0;
@@ -521,31 +536,45 @@ static int query_clusters(int block, size_t smem, int cluster) {
   return n;
 }
 
-int mma_max_active_clusters(int nt, bool seg64, int block, size_t smem, int cluster) {
+// one instantiation per (bit width, batch tiles, group mode); RB follows: 64-row warps for one
+// batch tile of 2- and 4-bit layers, 32-row warps otherwise
+#define QFB_MMA_DISPATCH(FN, ...)                                                                     \
+  do {                                                                                                \
+    if (bits == 4 && nt == 1) return seg64 ? FN<4, 1, 4, true>(__VA_ARGS__) : FN<4, 1, 4, false>(__VA_ARGS__); \
+    if (bits == 4 && nt == 2) return seg64 ? FN<4, 2, 2, true>(__VA_ARGS__) : FN<4, 2, 2, false>(__VA_ARGS__); \
+    if (bits == 8 && nt == 1) return seg64 ? FN<8, 1, 2, true>(__VA_ARGS__) : FN<8, 1, 2, false>(__VA_ARGS__); \
+    if (bits == 8 && nt == 2) return seg64 ? FN<8, 2, 2, true>(__VA_ARGS__) : FN<8, 2, 2, false>(__VA_ARGS__); \
+    if (bits == 2 && nt == 1) return seg64 ? FN<2, 1, 4, true>(__VA_ARGS__) : FN<2, 1, 4, false>(__VA_ARGS__); \
+    if (bits == 2 && nt == 2) return seg64 ? FN<2, 2, 2, true>(__VA_ARGS__) : FN<2, 2, 2, false>(__VA_ARGS__); \
+  } while (0)
+
+static int query_any(int bits, int nt, bool seg64, int block, size_t sm, int cluster) {
+  QFB_MMA_DISPATCH(query_clusters, block, sm, cluster);
+  return 0;
+}
+
+int mma_max_active_clusters(int bits, int nt, bool seg64, int block, size_t smem, int cluster) {
   static std::mutex mu;
   static std::map<unsigned long long, int> cache;
   int dev = 0;
   (void)cudaGetDevice(&dev);
   const size_t smem_kb = (smem + 1023) / 1024;  // the answer only changes with the shared-memory footprint
-  const unsigned long long key = ((unsigned long long)dev << 48) | ((unsigned long long)nt << 44) |
-                                 ((unsigned long long)seg64 << 43) | ((unsigned long long)block << 28) |
-                                 ((unsigned long long)smem_kb << 8) | (unsigned long long)cluster;
+  const unsigned long long key = ((unsigned long long)dev << 52) | ((unsigned long long)bits << 48) |
+                                 ((unsigned long long)nt << 44) | ((unsigned long long)seg64 << 43) |
+                                 ((unsigned long long)block << 28) | ((unsigned long long)smem_kb << 8) |
+                                 (unsigned long long)cluster;
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
-  const size_t sm = smem_kb * 1024;
-  int n;
-  if (nt == 1) n = seg64 ? query_clusters<1, 4, true>(block, sm, cluster) : query_clusters<1, 4, false>(block, sm, cluster);
-  else n = seg64 ? query_clusters<2, 2, true>(block, sm, cluster) : query_clusters<2, 2, false>(block, sm, cluster);
+  const int n = query_any(bits, nt, seg64, block, smem_kb * 1024, cluster);
   cache[key] = n;
   return n;
 }
 
-cudaError_t launch_gemv_mma(const MmaParams& p, int nt, dim3 grid, int block, size_t smem, bool pdl,
+cudaError_t launch_gemv_mma(const MmaParams& p, int bits, int nt, dim3 grid, int block, size_t smem, bool pdl,
                             cudaStream_t st) {
   const bool seg64 = p.chunks_per_group == 1;
-  if (nt == 1) return seg64 ? launch_cfg<1, 4, true>(p, grid, block, smem, pdl, st) : launch_cfg<1, 4, false>(p, grid, block, smem, pdl, st);
-  if (nt == 2) return seg64 ? launch_cfg<2, 2, true>(p, grid, block, smem, pdl, st) : launch_cfg<2, 2, false>(p, grid, block, smem, pdl, st);
+  QFB_MMA_DISPATCH(launch_cfg, p, grid, block, smem, pdl, st);
   return cudaErrorInvalidValue;
 }
 

@@ -31,7 +31,7 @@ cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int bl
 // exact scratch bytes the split-K GEMV needs for m rows (0 when the shape is invalid)
 size_t gemv_scratch_bytes(int m, int n, int k, int bits);
 
-// mma.sync split-K kernel over the fragment layout (4-bit, m <= 16 per launch)
+// mma.sync split-K kernel over the fragment layout (2/4/8-bit, m <= 16 per launch)
 struct MmaParams {
   const uint4* qw;
   const __half* qs;      // null: scale 1 (group-less)
@@ -52,8 +52,8 @@ struct MmaParams {
   int recv_offset;       // byte offset of the cluster reduction's receive buffer in dynamic shared memory
 };
 // clusters of `cluster` CTAs of the mma.sync GEMV the current device holds at once (cached)
-int mma_max_active_clusters(int nt, bool seg64, int block, size_t smem, int cluster);
-cudaError_t launch_gemv_mma(const MmaParams& p, int nt, dim3 grid, int block, size_t smem, bool pdl,
+int mma_max_active_clusters(int bits, int nt, bool seg64, int block, size_t smem, int cluster);
+cudaError_t launch_gemv_mma(const MmaParams& p, int bits, int nt, dim3 grid, int block, size_t smem, bool pdl,
                             cudaStream_t st);
 
 struct TcParams {

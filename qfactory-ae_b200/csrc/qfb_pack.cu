@@ -83,33 +83,35 @@ __global__ void pack_scale_zero_kernel(const PackParams p) {
   }
 }
 
-// ---- fragment layout (4-bit): one thread per packed word / per scale position -----------
-// nibble i of a fragment word holds (row0 + 8 * (i & 1), k0 + kFragNibbleK[i])
-__device__ __forceinline__ int frag_nibble_k(int i) { return (i >> 2) + 2 * ((i >> 1) & 1); }
-
+// ---- fragment layouts (2/4/8-bit): one thread per packed word / per scale position ---------
+// word j of lane (g, t) at k-step ks of the 64-row half wt of a tile; frag_word_of / frag_bit_of
+// (qfb_common.cuh) say which codes it holds
 __global__ void pack_weight_frag_kernel(const PackParams p) {
   const int ksteps = p.k / 16;
-  const long long total = (long long)p.tiles * 2 * ksteps * 32 * 4;
+  const int wpl = p.bits;  // words per lane and k-step (4 row blocks): 4 * bits bytes
+  const long long total = (long long)p.tiles * 2 * ksteps * 32 * wpl;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
-  const int rb = (int)(idx & 3);
-  const int lane = (int)((idx >> 2) & 31);
-  long long t = idx >> 7;
+  const int j = (int)(idx % wpl);
+  long long t = idx / wpl;
+  const int lane = (int)(t & 31); t >>= 5;
   const int ks = (int)(t % ksteps); t /= ksteps;
   const int wt = (int)(t & 1);
   const int tile = (int)(t >> 1);
-  const int row0 = tile * kTileRows + wt * 64 + rb * 16 + (lane >> 2);
-  const int k0 = ks * 16 + 4 * (lane & 3);
+  const int g = lane >> 2, k0 = ks * 16 + 4 * (lane & 3);
   uint32_t word = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int n = row0 + 8 * (i & 1);
-    if (n < p.n) {
-      const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + frag_nibble_k(i)) * p.n + n];
-      word |= (q & 15u) << (4 * i);
+  for (int rb = 0; rb < 4; ++rb)
+    for (int h = 0; h < 2; ++h) {
+      if (frag_word_of(p.bits, rb, h) != j) continue;
+      const int n = tile * kTileRows + wt * 64 + rb * 16 + h * 8 + g;
+      if (n >= p.n) continue;
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + kk) * p.n + n] & ((1u << p.bits) - 1u);
+        word |= q << frag_bit_of(p.bits, rb, h, kk);
+      }
     }
-  }
-  p.qw[idx] = word;
+  char* base = reinterpret_cast<char*>(p.qw) + ((size_t)(tile * 2 + wt) * ksteps + ks) * frag_step_bytes(p.bits);
+  *reinterpret_cast<uint32_t*>(base + frag_word_offset(p.bits, lane, j)) = word;
 }
 
 __global__ void pack_scale_zero_frag_kernel(const PackParams p) {
@@ -132,36 +134,46 @@ __global__ void pack_scale_zero_frag_kernel(const PackParams p) {
   }
 }
 
-// inverse through frag4_fields, the extraction the mma kernel itself runs
+// inverse through FragCodec<BITS>::decode, the extraction the mma kernel itself runs: one thread
+// per (lane, k-step, half tile)
+template <int BITS>
 __global__ void unpack_frag_kernel(const UnpackParams p) {
+  using FC = FragCodec<BITS>;
   const int ksteps = p.k / 16;
-  const long long total = (long long)p.tiles * 2 * ksteps * 32 * 4;
+  const long long total = (long long)p.tiles * 2 * ksteps * 32;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
-  const int rb = (int)(idx & 3);
-  const int lane = (int)((idx >> 2) & 31);
-  long long t = idx >> 7;
+  const int lane = (int)(idx & 31);
+  long long t = idx >> 5;
   const int ks = (int)(t % ksteps); t /= ksteps;
   const int wt = (int)(t & 1);
   const int tile = (int)(t >> 1);
   const int g = lane >> 2;
   const int k0 = ks * 16 + 4 * (lane & 3);
-  uint32_t a[4];
-  frag4_fields(reinterpret_cast<const uint32_t*>(p.qw)[idx], a);
+  const char* base = reinterpret_cast<const char*>(p.qw) + ((size_t)(tile * 2 + wt) * ksteps + ks) * frag_step_bytes(BITS);
+  uint32_t v[BITS];
+#pragma unroll
+  for (int j = 0; j < BITS; ++j) v[j] = *reinterpret_cast<const uint32_t*>(base + frag_word_offset(BITS, lane, j));
   const int grp = k0 / (p.k / p.groups);
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {  // h = 0: row g (fields a[0], a[2]); h = 1: row g + 8 (a[1], a[3], shifted by 4)
-    const int n = tile * kTileRows + wt * 64 + rb * 16 + h * 8 + g;
-    if (n >= p.n) continue;
-    const uint32_t lo = a[h] >> (4 * h), hi = a[2 + h] >> (4 * h);
-    const int q[4] = {(int)(lo & 15u), (int)((lo >> 16) & 15u), (int)(hi & 15u), (int)((hi >> 16) & 15u)};
-    const size_t sz = ((size_t)tile * p.groups + grp) * kTileRows + wt * 64 + g * 8 + rb * 2 + h;
-    const __half sc = p.qs ? p.qs[sz] : __ushort_as_half(0x3C00);
-    const int z = p.qz ? (int)p.qz[sz] : (int)p.zconst;
+  for (int rb = 0; rb < 4; ++rb) {
+    uint32_t a[4];
+    FC::decode(v, rb, a);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (p.codes_out) p.codes_out[(size_t)(k0 + i) * p.n + n] = q[i];
-      if (p.w_out) p.w_out[(size_t)(k0 + i) * p.n + n] = __hmul(__int2half_rn(q[i] - z), sc);
+    for (int h = 0; h < 2; ++h) {  // h = 0: row g (registers a[0], a[2]); h = 1: row g + 8 (a[1], a[3])
+      const int n = tile * kTileRows + wt * 64 + rb * 16 + h * 8 + g;
+      if (n >= p.n) continue;
+      const int sh = h ? FC::shift_hi(rb) : FC::shift_lo(rb);
+      const uint32_t lo = a[h] >> sh, hi = a[2 + h] >> sh, m = (1u << BITS) - 1u;
+      const int q[4] = {(int)(lo & m), (int)((lo >> 16) & m), (int)(hi & m), (int)((hi >> 16) & m)};
+      const size_t sz = ((size_t)tile * p.groups + grp) * kTileRows + wt * 64 + g * 8 + rb * 2 + h;
+      const __half sc = p.qs ? p.qs[sz] : __ushort_as_half(0x3C00);
+      const int z = p.qz ? (int)p.qz[sz] : (int)p.zconst;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (p.codes_out) p.codes_out[(size_t)(k0 + i) * p.n + n] = q[i];
+        if (p.w_out) p.w_out[(size_t)(k0 + i) * p.n + n] = __hmul(__int2half_rn(q[i] - z), sc);
+      }
     }
   }
 }
@@ -169,7 +181,7 @@ __global__ void unpack_frag_kernel(const UnpackParams p) {
 cudaError_t launch_pack(const PackParams& p, cudaStream_t st) {
   if (p.layout == QFB_LAYOUT_FRAGMENT) {
     const int block = 256;
-    const long long total = (long long)p.tiles * 2 * (p.k / 16) * 32 * 4;
+    const long long total = (long long)p.tiles * 2 * (p.k / 16) * 32 * p.bits;
     pack_weight_frag_kernel<<<(unsigned)((total + block - 1) / block), block, 0, st>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -281,8 +293,12 @@ cudaError_t launch_quantize(const __half* w, int k, int n, int bits, int group_s
 cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st) {
   if (p.layout == QFB_LAYOUT_FRAGMENT) {
     const int block = 256;
-    const long long tf = (long long)p.tiles * 2 * (p.k / 16) * 32 * 4;
-    unpack_frag_kernel<<<(unsigned)((tf + block - 1) / block), block, 0, st>>>(p);
+    const long long tf = (long long)p.tiles * 2 * (p.k / 16) * 32;
+    const unsigned gridf = (unsigned)((tf + block - 1) / block);
+    if (p.bits == 4) unpack_frag_kernel<4><<<gridf, block, 0, st>>>(p);
+    else if (p.bits == 8) unpack_frag_kernel<8><<<gridf, block, 0, st>>>(p);
+    else if (p.bits == 2) unpack_frag_kernel<2><<<gridf, block, 0, st>>>(p);
+    else return cudaErrorInvalidValue;
     return cudaGetLastError();
   }
   const long long total = (long long)p.tiles * p.units * kTileRows;

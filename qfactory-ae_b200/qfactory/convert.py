@@ -83,7 +83,7 @@ def convert_params(args, params):
         _check_weight(K, N, weight, NBITS)
         if weight.is_cuda:
             return _pack_native(K, N, NBITS, -1, weight, None, None, lay)[0]
-        return layout.pack_weight_fragment(weight) if frag else layout.pack_weight(weight, NBITS)
+        return layout.pack_weight_fragment(weight, NBITS) if frag else layout.pack_weight(weight, NBITS)
     if len(params) != 3:
         raise ValueError("gptq_gemv requires 3 parameters")
     weight, scale, zero = params
@@ -96,7 +96,7 @@ def convert_params(args, params):
     if weight.is_cuda:
         return _pack_native(K, N, NBITS, GS, weight, scale, zero, lay)
     if frag:
-        return (layout.pack_weight_fragment(weight), layout.pack_scale_fragment(scale),
+        return (layout.pack_weight_fragment(weight, NBITS), layout.pack_scale_fragment(scale),
                 layout.pack_zero_fragment(zero, NBITS) if zero is not None else None)
     w = layout.pack_weight(weight, NBITS)
     s = layout.pack_scale(scale)
@@ -111,10 +111,10 @@ def unpack_params(args, packed):
     frag = layout.resolve_layout(args.get("LAYOUT", "tile"), N, K, NBITS, args.get("GS", -1)) == layout.LAYOUT_FRAGMENT
     if "GS" not in args:
         w = packed[0] if isinstance(packed, (tuple, list)) else packed
-        return layout.unpack_weight_fragment(w, N, K) if frag else layout.unpack_weight(w, N, K, NBITS)
+        return layout.unpack_weight_fragment(w, N, K, NBITS) if frag else layout.unpack_weight(w, N, K, NBITS)
     w, s, z = packed
     if frag:
-        return (layout.unpack_weight_fragment(w, N, K), layout.unpack_scale_fragment(s, N),
+        return (layout.unpack_weight_fragment(w, N, K, NBITS), layout.unpack_scale_fragment(s, N),
                 layout.unpack_zero_fragment(z, N) if z is not None else None)
     return (
         layout.unpack_weight(w, N, K, NBITS),

@@ -180,32 +180,55 @@ def unpack_zero(z: torch.Tensor, N: int) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------
-# Fragment layout (4-bit, K % 128 == 0): the same codes permuted so that one 32-bit word is
-# the A fragment a thread feeds to mma.sync.m16n8k16 (include/qfactory_b200.h).  For lane
-# (g = lane // 4, t = lane % 4) of row block rb in the 64-row half wt of a tile, nibble i of
-# the word at 16-k step ks holds row wt*64 + rb*16 + 8*(i & 1) + g, k = 16*ks + 4*t + NIBBLE_K[i].
-#     qweight  u32 [tiles][2][K/16][32 lanes][4 row blocks]
-#     scales / zeros  [tiles][K/group][128], position wt*64 + g*8 + rb*2 + h <-> row wt*64 + rb*16 + h*8 + g
+# Fragment layouts (2/4/8-bit, K % 128 == 0): the same codes permuted so that the words a lane
+# holds are the A fragments a thread feeds to mma.sync.m16n8k16 (include/qfactory_b200.h and
+# csrc/qfb_common.cuh).  Lane (g = lane // 4, t = lane % 4) of the 64-row half wt of a tile owns,
+# for each of its four row blocks rb, rows g and g + 8 (h = 0, 1) at k = 16*ks + 4*t + kk:
+#   word of the lane that holds code (rb, h, kk):  4-bit rb | 8-bit 2*rb + h | 2-bit rb // 2
+#   bit position inside that word:                 frag_bit_of below
+#   qweight  [tiles][2][K/16] steps of 128*bits bytes: lane-major words (8-bit: two 512-byte chunks,
+#            row blocks 0,1 then 2,3)
+#   scales / zeros  [tiles][K/group][128], position wt*64 + g*8 + rb*2 + h <-> row wt*64 + rb*16 + h*8 + g
 # ---------------------------------------------------------------------------------------
-NIBBLE_K = [(i >> 2) + 2 * ((i >> 1) & 1) for i in range(8)]
+NIBBLE_K = [(i >> 2) + 2 * ((i >> 1) & 1) for i in range(8)]  # 4-bit: k offset held by nibble i (row = i & 1)
+
+
+def frag_word_of(bits: int, rb: int, h: int) -> int:
+    return rb if bits == 4 else (2 * rb + h if bits == 8 else rb // 2)
+
+
+def frag_bit_of(bits: int, rb: int, h: int, kk: int) -> int:
+    if bits == 8:
+        return 8 * kk
+    if bits == 4:
+        return 4 * ((kk >> 1) * 2 + (kk & 1) * 4 + h)
+    return (rb & 1) * 4 + h * 2 + (kk & 1) * 16 + (kk >> 1) * 8
+
+
+def frag_word_slot(bits: int, lane: int, j: int) -> int:
+    """Index (in 32-bit words) of word j of a lane inside a k-step."""
+    if bits == 8:
+        return (j >> 2) * 128 + lane * 4 + (j & 3)
+    return lane * bits + j
 
 
 def fragment_supported(N: int, K: int, bits: int, GS: int) -> bool:
-    return bits == 4 and K % 128 == 0 and (GS in (-1, 64) or GS % 128 == 0)
+    return bits in (2, 4, 8) and K % 128 == 0 and (GS in (-1, 64) or GS % 128 == 0)
 
 
 def resolve_layout(layout, N: int, K: int, bits: int, GS: int, batch_size: int = 1) -> int:
     """'tile' | 'fragment' | 'auto' | 0 | 1 | None -> LAYOUT_*.  'auto' (and None) picks the fragment
-    layout whenever the shape allows it (4-bit, K % 128 == 0, group 64 or a multiple of 128): it
-    feeds the fastest kernel up to 16 rows and the tcgen05 kernel within a few percent of the tile
-    layout above.  `batch_size` is accepted for the callers' convenience and does not matter."""
+    layout for 4-bit layers whenever the shape allows it (K % 128 == 0, group 64 or a multiple of
+    128): it feeds the fastest kernel up to 16 rows and the tcgen05 kernel within a few percent of
+    the tile layout above.  2- and 8-bit layers get it only on request ('fragment'): their batches
+    above 16 rows run 16 rows at a time.  `batch_size` is accepted for the callers' convenience."""
     if layout in (LAYOUT_TILE, "tile"):
         return LAYOUT_TILE
     if layout in (LAYOUT_FRAGMENT, "fragment"):
-        assert fragment_supported(N, K, bits, GS), "the fragment layout needs 4-bit codes and K % 128 == 0"
+        assert fragment_supported(N, K, bits, GS), "the fragment layout needs 2/4/8-bit codes and K % 128 == 0"
         return LAYOUT_FRAGMENT
     assert layout in (None, "auto"), f"unknown layout {layout!r}"
-    return LAYOUT_FRAGMENT if fragment_supported(N, K, bits, GS) else LAYOUT_TILE
+    return LAYOUT_FRAGMENT if (bits == 4 and fragment_supported(N, K, bits, GS)) else LAYOUT_TILE
 
 
 def frag_row_of_pos(device=None) -> torch.Tensor:
@@ -213,27 +236,41 @@ def frag_row_of_pos(device=None) -> torch.Tensor:
     return (pos >> 6) * 64 + ((pos >> 1) & 3) * 16 + (pos & 1) * 8 + ((pos >> 3) & 7)
 
 
-def pack_weight_fragment(q: torch.Tensor) -> torch.Tensor:
-    """int32 codes [K, N] (4-bit) -> int8 [Npad, K/2] in fragment order."""
+def _frag_slots(bits: int, device):
+    """For every (rb, h, g, t, kk): word slot inside the k-step and bit position."""
+    slot = torch.empty(4, 2, 8, 4, 4, dtype=torch.int64)
+    bit = torch.empty(4, 2, 8, 4, 4, dtype=torch.int64)
+    for rb in range(4):
+        for h in range(2):
+            for g in range(8):
+                for t in range(4):
+                    for kk in range(4):
+                        slot[rb, h, g, t, kk] = frag_word_slot(bits, g * 4 + t, frag_word_of(bits, rb, h))
+                        bit[rb, h, g, t, kk] = frag_bit_of(bits, rb, h, kk)
+    return slot.to(device), bit.to(device)
+
+
+def pack_weight_fragment(q: torch.Tensor, bits: int = 4) -> torch.Tensor:
+    """int32 codes [K, N] -> int8 [Npad, K*bits/8] in fragment order."""
     K, N = q.shape
     Np = padded_rows(N)
     T = Np // TILE
     blk = torch.zeros(Np, K, dtype=torch.int64, device=q.device)
     blk[:N] = q.t()
-    v = blk.view(T, 2, 4, 2, 8, K // 16, 4, 4)            # [tile, wt, rb, h, g, ks, t, kk]
-    words = torch.zeros(T, 2, K // 16, 8, 4, 4, dtype=torch.int64, device=q.device)  # [tile, wt, ks, g, t, rb]
-    for i in range(8):
-        words += v[:, :, :, i & 1, :, :, :, NIBBLE_K[i]].permute(0, 1, 4, 3, 5, 2) << (4 * i)
-    return _words_to_bytes(words).reshape(Np, K // 2).view(torch.int8)
+    v = blk.view(T, 2, 4, 2, 8, K // 16, 4, 4).permute(0, 1, 5, 2, 3, 4, 6, 7)   # [tile, wt, ks, rb, h, g, t, kk]
+    slot, bit = _frag_slots(bits, q.device)
+    words = torch.zeros(T, 2, K // 16, 32 * bits, dtype=torch.int64, device=q.device)
+    words.scatter_add_(3, slot.flatten().expand(T, 2, K // 16, -1), (v << bit).reshape(T, 2, K // 16, -1))
+    return _words_to_bytes(words).reshape(Np, K * bits // 8).view(torch.int8)
 
 
-def unpack_weight_fragment(w: torch.Tensor, N: int, K: int) -> torch.Tensor:
+def unpack_weight_fragment(w: torch.Tensor, N: int, K: int, bits: int = 4) -> torch.Tensor:
     Np = padded_rows(N)
     T = Np // TILE
-    words = _bytes_to_words(w.contiguous().view(torch.uint8).view(T, 2, K // 16, 8, 4, 4, 4))  # [tile, wt, ks, g, t, rb]
-    v = torch.empty(T, 2, 4, 2, 8, K // 16, 4, 4, dtype=torch.int64, device=w.device)
-    for i in range(8):
-        v[:, :, :, i & 1, :, :, :, NIBBLE_K[i]] = ((words >> (4 * i)) & 15).permute(0, 1, 5, 3, 2, 4)
+    words = _bytes_to_words(w.contiguous().view(torch.uint8).view(T, 2, K // 16, 32 * bits, 4))
+    slot, bit = _frag_slots(bits, w.device)
+    v = (words[..., slot.flatten()] >> bit.flatten()) & ((1 << bits) - 1)           # [tile, wt, ks, rb*h*g*t*kk]
+    v = v.view(T, 2, K // 16, 4, 2, 8, 4, 4).permute(0, 1, 3, 4, 5, 2, 6, 7)        # [tile, wt, rb, h, g, ks, t, kk]
     return v.reshape(Np, K)[:N].t().contiguous().to(torch.int32)
 
 

@@ -122,7 +122,7 @@ class _PackedLinear(torch.nn.Module):
         recovered from the packed buffers in torch, on whatever device they live on."""
         N, K = self.out_features, self.in_features
         if self.packed_layout == layout.LAYOUT_FRAGMENT:
-            return (layout.unpack_weight_fragment(self.w, N, K),
+            return (layout.unpack_weight_fragment(self.w, N, K, self.n_bits),
                     layout.unpack_scale_fragment(self.s, N) if self.s is not None else None,
                     layout.unpack_zero_fragment(self.z, N) if self.z is not None else None)
         return (layout.unpack_weight(self.w, N, K, self.n_bits),

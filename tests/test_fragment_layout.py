@@ -94,26 +94,57 @@ def test_layout_choice():
         R("fragment", 4096, 4096, 3, 128)
     L = _native.lib()
     assert L.qfb_layout_supported(1, 4096, 4096, 4, 128) == 1
-    assert L.qfb_layout_supported(1, 4096, 4096, 8, 128) == 0
+    assert L.qfb_layout_supported(1, 4096, 4096, 8, 128) == 1   # on request; 'auto' keeps 8-bit on the tile layout
+    assert L.qfb_layout_supported(1, 4096, 4096, 2, 128) == 1
+    assert L.qfb_layout_supported(1, 4096, 4096, 3, 128) == 0
     assert L.qfb_layout_supported(1, 4096, 4160, 4, 64) == 0
     assert L.qfb_layout_supported(0, 4096, 4160, 4, 64) == 1
     assert L.qfb_layout_supported(2, 4096, 4096, 4, 128) == 0
 
 
+@pytest.mark.parametrize("bits", [2, 8])
+def test_fragment_packer_other_bit_widths(bits):
+    """Positions restated from the header: word of the lane, bit inside the word, place of the word."""
+    torch.manual_seed(bits)
+    K, N = 256, 200
+    q = torch.randint(0, 1 << bits, (K, N), dtype=torch.int32)
+    w = layout.pack_weight_fragment(q, bits)
+    assert w.shape == (256, K * bits // 8)
+    assert torch.equal(layout.unpack_weight_fragment(w, N, K, bits), q)
+    words = layout._bytes_to_words(w.view(torch.uint8).reshape(-1, 4))
+    rnd = random.Random(bits)
+    for _ in range(3000):
+        n, k = rnd.randrange(N), rnd.randrange(K)
+        tile, r = divmod(n, 128)
+        wt, r = divmod(r, 64)
+        rb, r = divmod(r, 16)
+        h, g = divmod(r, 8)
+        ks, kk = divmod(k, 16)
+        t, kk = divmod(kk, 4)
+        lane = g * 4 + t
+        if bits == 8:
+            j = 2 * rb + h
+            slot, bit = (j >> 2) * 128 + lane * 4 + (j & 3), 8 * kk
+        else:
+            slot, bit = lane * 2 + rb // 2, (rb & 1) * 4 + h * 2 + (kk & 1) * 16 + (kk >> 1) * 8
+        wi = ((tile * 2 + wt) * (K // 16) + ks) * 32 * bits + slot
+        assert (int(words[wi]) >> bit) & ((1 << bits) - 1) == int(q[k, n])
+
+
 # ---- GPU ---------------------------------------------------------------------------------------
 
-def _frag_layer(M, N, K, GS, sym, seed):
-    x, q, s, z = O.make_case(M, N, K, 4, GS, sym, seed)
+def _frag_layer(M, N, K, GS, sym, seed, bits=4):
+    x, q, s, z = O.make_case(M, N, K, bits, GS, sym, seed)
     if GS == -1:
-        layer = QLinear.init(M, K, N, 4, q.cuda(), layout="fragment")
+        layer = QLinear.init(M, K, N, bits, q.cuda(), layout="fragment")
     else:
-        layer = QLinear.init(M, K, N, 4, q.cuda(), GS, s.cuda(), None if z is None else z.cuda(), layout="fragment")
+        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), None if z is None else z.cuda(), layout="fragment")
     assert layer.packed_layout == layout.LAYOUT_FRAGMENT
     return layer, x, q, s, z
 
 
-def _check(y, x, q, s, z):
-    _, yex = O.reference_forward(x, q, s, z, 4)
+def _check(y, x, q, s, z, bits=4):
+    _, yex = O.reference_forward(x, q, s, z, bits)
     got = y.float().cpu().numpy().astype(np.float64)
     assert np.isfinite(got).all()
     assert np.abs(got - yex).max() <= TOL * np.abs(yex).max()
@@ -281,3 +312,40 @@ def test_fragment_forward_random_shapes_and_plans():
     finally:
         L.qfb_set_gemv_tuning(0, 0)
         L.qfb_set_cluster_reduce(1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("N,K,GS,sym", [(128, 128, 128, False), (200, 512, 64, False), (300, 1024, 256, True), (130, 256, -1, False)])
+def test_fragment_other_bit_widths_packer_and_inverse_bit_exact(bits, N, K, GS, sym):
+    layer, x, q, s, z = _frag_layer(1, N, K, GS, sym, seed=N + K + bits, bits=bits)
+    assert torch.equal(layer.w.cpu().view(torch.uint8).flatten(),
+                       layout.pack_weight_fragment(q, bits).view(torch.uint8).flatten())
+    assert torch.equal(layer.unpack_codes().cpu(), q)
+    if GS != -1:
+        ze = O.symmetric_zero(bits) if sym else O.effective_zero(z.numpy(), bits)
+        want = O.dequant_effective(q, s, ze)
+        assert torch.equal(layer.dequantize().cpu().view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 21])
+@pytest.mark.parametrize("GS,sym", [(128, False), (64, False), (256, True), (-1, False)])
+def test_fragment_other_bit_widths_forward(bits, M, GS, sym):
+    N, K = 328, 1024
+    layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=3000 + 31 * M + bits + (GS % 83), bits=bits)
+    y = layer(x.cuda())
+    assert _native.last_launch()["kernel"] == 3   # above 16 rows: 16 rows at a time
+    _check(y, x, q, s, z, bits)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (4, 1000, 11008), (16, 2048, 4096), (1, 8192, 8192)])
+def test_fragment_other_bit_widths_split_k_shapes(bits, M, N, K):
+    layer, x, q, s, z = _frag_layer(M, N, K, 128, False, seed=bits + M + N, bits=bits)
+    xs = x.cuda()
+    y = layer(xs)
+    _check(y, x, q, s, z, bits)
+    assert torch.equal(y, layer(xs))
