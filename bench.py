@@ -279,7 +279,8 @@ def main():
             R = max(2, min(48, (400 << 20) // (N * K * bits // 8) + 1))
             ls = []
             for _ in range(R):
-                L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=args.layout)
+                lay = "tile" if (args.layout == "fragment" and bits == 3) else args.layout  # no 3-bit fragment layout
+                L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=lay)
                 L.w.random_(-128, 127)
                 if L.s is not None:
                     L.s.uniform_(0.002, 0.02)

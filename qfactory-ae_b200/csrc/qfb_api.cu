@@ -563,9 +563,9 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
   if (m == 0) return QFB_OK;
   if (!x || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
-  // fragment-layout layers: the mma.sync GEMV up to 16 rows, the tcgen05 kernel above (it reads the
-  // 4-bit fragment words; 2- and 8-bit fragment layers run the GEMV 16 rows at a time)
-  if (v.layout == QFB_LAYOUT_FRAGMENT && (m <= kMaxMmaRows || v.bits != 4 || (flags & QFB_FLAG_FORCE_SIMT)))
+  // fragment-layout layers: the mma.sync GEMV up to 16 rows, the tcgen05 kernel (which reads the
+  // same fragment words) above
+  if (v.layout == QFB_LAYOUT_FRAGMENT && (m <= kMaxMmaRows || (flags & QFB_FLAG_FORCE_SIMT)))
     return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                    static_cast<cudaStream_t>(stream));
   if (v.layout == QFB_LAYOUT_FRAGMENT || choose_kernel(v, m, flags) == 2)

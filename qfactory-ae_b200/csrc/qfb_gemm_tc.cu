@@ -113,11 +113,12 @@ template <> struct StageDecode<4> {
     }
   }
 };
-// Fragment layout (4-bit): stage = [2 halves of 64 rows][8 k-steps][32 lanes][4 row blocks x 4 B].
-// Row wt*64 + rb*16 + hh*8 + g owns, in the word of (k-step, lane g*4+t, row block rb), nibbles
-// 0,4,2,6 (hh = 0) or 1,5,3,7 (hh = 1) = k 4t..4t+3 of the step: two LOP3 per word with the
-// row's mask / magic give two exact fp16 pairs in k order.
-struct StageDecodeFragment4 {
+// Fragment layouts: stage = [2 halves of 64 rows][8 k-steps of 128 * BITS bytes] (qfb_common.cuh).
+// Row wt*64 + rb*16 + hh*8 + g owns, in the word frag_word_of(rb, hh) of lane g*4+t, the codes of
+// k 4t..4t+3 of a step: two exact fp16 pairs in k order per word.
+template <int BITS> struct StageDecodeFragment;
+template <> struct StageDecodeFragment<4> {
+  // nibbles 0,4,2,6 (hh = 0) or 1,5,3,7 (hh = 1): two LOP3 with the row's mask / magic
   __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
     const Codec<4>::ZM zm = Codec<4>::zmagic(z);
     const int wt = row >> 6, rb = (row >> 4) & 3, hh = (row >> 3) & 1, g = row & 7;
@@ -133,6 +134,45 @@ struct StageDecodeFragment4 {
         d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(lop3_and_or(word >> 8, mask, magic)), zs);
       }
   }
+};
+template <> struct StageDecodeFragment<8> {
+  // one word = the row's four bytes of k 4t..4t+3
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const Codec<8>::ZM zm = Codec<8>::zmagic(z);
+    const int wt = row >> 6, rb = (row >> 4) & 3, hh = (row >> 3) & 1, g = row & 7;
+    const uint8_t* base = w + wt * 8192 + (4 * h) * 1024 + frag_word_offset(8, g * 4, rb * 2 + hh);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(base + ks * 1024 + t * 16);
+        d[ks * 8 + t * 2] = __hsub2(as_h2(prmt(word, 0x64646464u, 0x4140u)), as_h2(zm.m));
+        d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(prmt(word, 0x64646464u, 0x4342u)), as_h2(zm.m));
+      }
+  }
+};
+template <> struct StageDecodeFragment<2> {
+  // one word = two row blocks; the row's fields sit at bit o = 4 (rb & 1) + 2 hh of each byte pair
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const Codec<2>::ZM zm = Codec<2>::zmagic(z);
+    const int wt = row >> 6, rb = (row >> 4) & 3, hh = (row >> 3) & 1, g = row & 7;
+    const int oi = (rb & 1) * 2 + hh;  // bit offset / 2
+    const uint32_t mask = 0x00030003u << (2 * oi);
+    const uint32_t magic = oi == 0 ? 0x64006400u : oi == 1 ? 0x5C005C00u : oi == 2 ? 0x54005400u : 0x4C004C00u;
+    const __half2 zs = as_h2(oi == 0 ? zm.m[0] : oi == 1 ? zm.m[1] : oi == 2 ? zm.m[2] : zm.m[3]);
+    const uint8_t* base = w + wt * 2048 + (4 * h) * 256 + g * 32 + (rb >> 1) * 4;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t word = *reinterpret_cast<const uint32_t*>(base + ks * 256 + t * 8);
+        d[ks * 8 + t * 2] = __hsub2(as_h2(lop3_and_or(word, mask, magic)), zs);
+        d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(lop3_and_or(word >> 8, mask, magic)), zs);
+      }
+  }
+};
+template <> struct StageDecodeFragment<3> {  // no 3-bit fragment layout: never reached
+  __device__ static __forceinline__ void run(const uint8_t*, int, int, uint32_t, __half2 (&)[32]) {}
 };
 template <> struct StageDecode<8> {
   // stage = [8 units][128 rows][16 B]; thread owns units 4h .. 4h+3
@@ -275,13 +315,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
         mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
-        if (BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT) {
-          // the stage is two runs of 4 KiB: 8 k-steps of the upper and of the lower 64 rows
+        if (BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT) {
+          // the stage is two runs: 8 k-steps (128 * BITS bytes each) of the upper and of the lower 64 rows
           const uint8_t* f0 = reinterpret_cast<const uint8_t*>(p.qw) +
-                              (((size_t)tile * 2) * (size_t)(p.kblocks * 8) + (size_t)(kb0 + i) * 8) * 512;
+                              (((size_t)tile * 2) * (size_t)(p.kblocks * 8) + (size_t)(kb0 + i) * 8) * (128 * BITS);
           tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, f0, Cfg::kWBytes / 2, bar);
-          tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes + Cfg::kWBytes / 2, f0 + (size_t)p.kblocks * 8 * 512,
-                       Cfg::kWBytes / 2, bar);
+          tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes + Cfg::kWBytes / 2,
+                       f0 + (size_t)p.kblocks * 8 * (128 * BITS), Cfg::kWBytes / 2, bar);
         } else {
           tma_bulk_g2s(sbase + w_off + s * Cfg::kWBytes, wsrc + (size_t)i * Cfg::kWBytes, Cfg::kWBytes, bar);
         }
@@ -356,7 +396,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     // with groups of 64 the two halves of a stage belong to different groups: half h reads
     // the second record of the stage's zero / scale slot
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
-    const bool frag = BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT;
+    const bool frag = BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT;
     // position of the row's scale / zero inside the tile's 128 (fragment layers keep them in fragment order)
     const int qrow = qsel + (frag ? frag_pos_of_row(row) : row);
     TT_DECL(6);
@@ -369,7 +409,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       TT_ADD(0);
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qrow] : p.zconst;
       __half2 d[32];
-      if (BITS == 4 && frag) StageDecodeFragment4::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
+      if (BITS != 3 && frag) StageDecodeFragment<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
       else StageDecode<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
       uint32_t rr[32];
       if (!POST && has_s) {
@@ -436,7 +476,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 #pragma unroll
       for (int j = 0; j < NB; ++j) acc[j] = 0.f;
       const size_t sz_row = (size_t)tile * p.groups * kTileRows +
-                            ((BITS == 4 && p.layout == QFB_LAYOUT_FRAGMENT) ? frag_pos_of_row(row) : row);
+                            ((BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT) ? frag_pos_of_row(row) : row);
       const int stages_per_group = p.halfstages_per_group >> 1;  // POST needs groups of whole stages
       int r = 0;
       uint32_t phr = 0;

@@ -218,17 +218,16 @@ def fragment_supported(N: int, K: int, bits: int, GS: int) -> bool:
 
 def resolve_layout(layout, N: int, K: int, bits: int, GS: int, batch_size: int = 1) -> int:
     """'tile' | 'fragment' | 'auto' | 0 | 1 | None -> LAYOUT_*.  'auto' (and None) picks the fragment
-    layout for 4-bit layers whenever the shape allows it (K % 128 == 0, group 64 or a multiple of
-    128): it feeds the fastest kernel up to 16 rows and the tcgen05 kernel within a few percent of
-    the tile layout above.  2- and 8-bit layers get it only on request ('fragment'): their batches
-    above 16 rows run 16 rows at a time.  `batch_size` is accepted for the callers' convenience."""
+    layout whenever the shape allows it (2/4/8-bit, K % 128 == 0, group 64 or a multiple of 128): it
+    feeds the fastest kernel up to 16 rows and the tcgen05 kernel within a few percent of the tile
+    layout above.  `batch_size` is accepted for the callers' convenience and does not matter."""
     if layout in (LAYOUT_TILE, "tile"):
         return LAYOUT_TILE
     if layout in (LAYOUT_FRAGMENT, "fragment"):
         assert fragment_supported(N, K, bits, GS), "the fragment layout needs 2/4/8-bit codes and K % 128 == 0"
         return LAYOUT_FRAGMENT
     assert layout in (None, "auto"), f"unknown layout {layout!r}"
-    return LAYOUT_FRAGMENT if (bits == 4 and fragment_supported(N, K, bits, GS)) else LAYOUT_TILE
+    return LAYOUT_FRAGMENT if fragment_supported(N, K, bits, GS) else LAYOUT_TILE
 
 
 def frag_row_of_pos(device=None) -> torch.Tensor:

@@ -86,7 +86,9 @@ def test_layout_choice():
     assert R("auto", 4096, 4096, 4, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
     assert R(None, 4096, 4096, 4, 128, batch_size=16) == layout.LAYOUT_FRAGMENT
     assert R("auto", 4096, 4096, 4, 128, batch_size=512) == layout.LAYOUT_FRAGMENT   # any batch size
-    assert R("auto", 4096, 4096, 8, 128, batch_size=1) == layout.LAYOUT_TILE      # 4-bit only
+    assert R("auto", 4096, 4096, 8, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
+    assert R("auto", 4096, 4096, 2, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
+    assert R("auto", 4096, 4096, 3, 128, batch_size=1) == layout.LAYOUT_TILE      # no 3-bit fragment layout
     assert R("auto", 4096, 4160, 4, 64, batch_size=1) == layout.LAYOUT_TILE       # K % 128 != 0
     assert R("auto", 4096, 4224, 4, 192, batch_size=1) == layout.LAYOUT_TILE      # group neither 64 nor k*128
     assert R("tile", 4096, 4096, 4, 128, batch_size=1) == layout.LAYOUT_TILE
@@ -94,7 +96,7 @@ def test_layout_choice():
         R("fragment", 4096, 4096, 3, 128)
     L = _native.lib()
     assert L.qfb_layout_supported(1, 4096, 4096, 4, 128) == 1
-    assert L.qfb_layout_supported(1, 4096, 4096, 8, 128) == 1   # on request; 'auto' keeps 8-bit on the tile layout
+    assert L.qfb_layout_supported(1, 4096, 4096, 8, 128) == 1
     assert L.qfb_layout_supported(1, 4096, 4096, 2, 128) == 1
     assert L.qfb_layout_supported(1, 4096, 4096, 3, 128) == 0
     assert L.qfb_layout_supported(1, 4096, 4160, 4, 64) == 0
@@ -269,7 +271,7 @@ def test_fragment_forward_pdl_graph_and_default_layout():
     g.replay()
     torch.cuda.synchronize()
     _check(y, x, q, s, z)
-    other = QLinear.init(64, 2048, 512, 8, q.cuda(), 128, s.cuda(), z.cuda())  # 8-bit: tile layout
+    other = QLinear.init(64, 2048, 512, 3, q.clamp(max=7).cuda(), 128, s.cuda(), z.clamp(max=7).cuda())  # 3-bit: tile layout
     assert other.packed_layout == layout.LAYOUT_TILE
 
 
@@ -330,13 +332,13 @@ def test_fragment_other_bit_widths_packer_and_inverse_bit_exact(bits, N, K, GS, 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("bits", [2, 8])
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 21])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 21, 40, 70, 130, 300])
 @pytest.mark.parametrize("GS,sym", [(128, False), (64, False), (256, True), (-1, False)])
 def test_fragment_other_bit_widths_forward(bits, M, GS, sym):
     N, K = 328, 1024
     layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=3000 + 31 * M + bits + (GS % 83), bits=bits)
     y = layer(x.cuda())
-    assert _native.last_launch()["kernel"] == 3   # above 16 rows: 16 rows at a time
+    assert _native.last_launch()["kernel"] == (3 if M <= 16 else 2)
     _check(y, x, q, s, z, bits)
 
 
