@@ -294,14 +294,15 @@ def test_fragment_forward_random_shapes_and_plans():
     L = _native.lib()
     rnd = random.Random(20241)
     try:
-        for case in range(48):
+        for case in range(96):
             K = 128 * rnd.choice([1, 2, 3, 5, 8, 11, 16, 24, 32])
             N = rnd.choice([1, 7, 100, 128, 129, 255, 300, 513, 700])
-            M = rnd.randint(1, 16)
+            M = rnd.randint(1, 16) if case % 4 else rnd.randint(17, 70)   # every fourth case: the tcgen05 kernel
+            bits = rnd.choice([2, 4, 4, 8])
             gs_ok = [g for g in (64, 128, 256, 384) if K % g == 0] + [-1]
             GS = rnd.choice(gs_ok)
             sym = GS != -1 and rnd.random() < 0.3
-            layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=5000 + case)
+            layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=5000 + case, bits=bits)
             if rnd.random() < 0.7:  # forced plan, otherwise the built-in one
                 L.qfb_set_gemv_tuning(rnd.choice([1, 2, 3, 4, 6, 8, 13]), rnd.choice([1, 2, 4]))
                 L.qfb_set_cluster_reduce(rnd.choice([0, 2]))
@@ -309,8 +310,8 @@ def test_fragment_forward_random_shapes_and_plans():
                 L.qfb_set_gemv_tuning(0, 0)
                 L.qfb_set_cluster_reduce(1)
             y = layer(x.cuda())
-            assert _native.last_launch()["kernel"] == 3
-            _check(y, x, q, s, z)
+            assert _native.last_launch()["kernel"] == (3 if M <= 16 else 2)
+            _check(y, x, q, s, z, bits)
     finally:
         L.qfb_set_gemv_tuning(0, 0)
         L.qfb_set_cluster_reduce(1)
