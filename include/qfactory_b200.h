@@ -211,6 +211,8 @@ int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream);
  * reference leaves them to its serving stack
  * (third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-120, 260-285).
  *   qfb_rmsnorm:  y[r,:] = fp16(x[r,:] * rsqrt(mean(x[r,:]^2) + eps)) * w     x, y fp16 [rows, d], w fp16 [d]
+ *   qfb_add_rmsnorm: x[r,:] += residual[r,:] in place (one fp16 addition), then y = the norm of the sum:
+ *                 the residual add after O / down and the next norm in one pass
  *   qfb_silu_mul: out[r,j] = silu(gate_up[r,j]) * gate_up[r,half+j]           gate_up fp16 [rows, 2*half]
  *   qfb_rope_cache: rotary embedding (interleaved pairs, fp16 arithmetic) of the query and key heads
  *                 of qkv fp16 [B, T, hq + 2 hkv, hd], in place, at positions pos i64 [T]; the rotated
@@ -221,6 +223,7 @@ int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream);
 int qfb_rope_cache(void* qkv, const void* cos, const void* sin, const void* pos, void* k_cache, void* v_cache,
                    int batch, int tokens, int q_heads, int kv_heads, int head_dim, int max_len, void* stream);
 int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float eps, void* stream);
+int qfb_add_rmsnorm(void* x, const void* residual, const void* w, void* y, int rows, int d, float eps, void* stream);
 int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* stream);
 
 #ifdef __cplusplus

@@ -681,8 +681,19 @@ int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float ep
   if (rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y)) return QFB_ERR_MISALIGNED;
   if (rows == 0) return QFB_OK;
-  return check_cuda(launch_rmsnorm(static_cast<const __half*>(x), static_cast<const __half*>(w),
-                                   static_cast<__half*>(y), rows, d, eps, static_cast<cudaStream_t>(stream)));
+  return check_cuda(launch_rmsnorm(const_cast<__half*>(static_cast<const __half*>(x)), nullptr,
+                                   static_cast<const __half*>(w), static_cast<__half*>(y), rows, d, eps,
+                                   static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_add_rmsnorm(void* x, const void* residual, const void* w, void* y, int rows, int d, float eps, void* stream) {
+  if (!x || !residual || !w || !y) return QFB_ERR_NULL_POINTER;
+  if (rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;
+  if (!aligned16(x) || !aligned16(residual) || !aligned16(w) || !aligned16(y)) return QFB_ERR_MISALIGNED;
+  if (rows == 0) return QFB_OK;
+  return check_cuda(launch_rmsnorm(static_cast<__half*>(x), static_cast<const __half*>(residual),
+                                   static_cast<const __half*>(w), static_cast<__half*>(y), rows, d, eps,
+                                   static_cast<cudaStream_t>(stream)));
 }
 
 int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* stream) {

@@ -12,14 +12,26 @@ namespace qfb {
 
 // y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w     (fp16 in / out, fp32 arithmetic;
 // the product with rstd is rounded to fp16 before the weight multiply, as x.half() * w does)
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
-                                                      __half* __restrict__ y, int d, float eps) {
+// With `res` the row is first updated in place, x[r, :] += res[r, :] (one fp16 addition, as the
+// framework's x + o), and the norm is taken of the sum: the residual add and the next norm in one pass.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ res,
+                                                      const __half* __restrict__ w, __half* __restrict__ y, int d,
+                                                      float eps) {
   const int row = blockIdx.x;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d);
+  uint4* xr = reinterpret_cast<uint4*>(x + (size_t)row * d);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * d) : nullptr;
   const int nv = d >> 3;
   float ss = 0.f;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    const uint4 v = xr[i];
+    uint4 v = xr[i];
+    if (rr) {
+      const uint4 r = rr[i];
+      v.x = as_u32(__hadd2(as_h2(v.x), as_h2(r.x)));
+      v.y = as_u32(__hadd2(as_h2(v.y), as_h2(r.y)));
+      v.z = as_u32(__hadd2(as_h2(v.z), as_h2(r.z)));
+      v.w = as_u32(__hadd2(as_h2(v.w), as_h2(r.w)));
+      xr[i] = v;  // re-read below by the same thread
+    }
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -119,8 +131,9 @@ cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sin
   return cudaGetLastError();
 }
 
-cudaError_t launch_rmsnorm(const __half* x, const __half* w, __half* y, int rows, int d, float eps, cudaStream_t st) {
-  rmsnorm_kernel<<<rows, 256, 0, st>>>(x, w, y, d, eps);
+cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half* y, int rows, int d, float eps,
+                           cudaStream_t st) {
+  rmsnorm_kernel<<<rows, 256, 0, st>>>(x, res, w, y, d, eps);
   return cudaGetLastError();
 }
 

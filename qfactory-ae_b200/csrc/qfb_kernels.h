@@ -78,7 +78,8 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bit
                            dim3 grid, bool pdl, cudaStream_t st);
 
 // element-wise neighbours of the linears in a decoder layer (qfb_decoder_ops.cu)
-cudaError_t launch_rmsnorm(const __half* x, const __half* w, __half* y, int rows, int d, float eps, cudaStream_t st);
+cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half* y, int rows, int d, float eps,
+                           cudaStream_t st);
 cudaError_t launch_silu_mul(const __half* gu, __half* out, int rows, int half, cudaStream_t st);
 cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sinv, const long long* pos, __half* k_cache,
                               __half* v_cache, int B, int T, int hq, int hkv, int hd, int max_len, cudaStream_t st);

@@ -94,6 +94,13 @@ class QuantDecoder(torch.nn.Module):
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
 
+    def _add_rms(self, x, r, w):
+        """x += r in place, then the norm of the sum (one launch with the native ops)."""
+        if self.native_ops:
+            return ops.add_rmsnorm(x, r.contiguous(), w, 1e-5)
+        x += r
+        return self._rms(x, w)
+
     def _rope(self, t, pos):
         # t [B, T, H, hd]; pos [T] long
         c, s = self.cos[pos][None, :, None, :], self.sin[pos][None, :, None, :]
@@ -108,8 +115,9 @@ class QuantDecoder(torch.nn.Module):
         x = self.embed[tokens]                                   # [B, T, d]
         # causal mask over the whole static cache: key j visible to query i iff j <= pos[i]
         mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
+        pending = None   # output of the previous down projection, not yet added to the residual stream
         for li, blk in enumerate(self.blocks):
-            h = self._rms(x, blk.norm1)
+            h = self._add_rms(x, pending, blk.norm1) if pending is not None else self._rms(x, blk.norm1)
             qkv = blk.qkv(h.view(B * T, -1)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
             q, k, v = qkv[:, :, : blk.hq], qkv[:, :, blk.hq : blk.hq + blk.hkv], qkv[:, :, blk.hq + blk.hkv :]
             if self.native_ops:
@@ -122,14 +130,14 @@ class QuantDecoder(torch.nn.Module):
                                                  attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
             o = blk.o(att.transpose(1, 2).reshape(B * T, -1))
             all_reduce_sum(o)                                     # row parallel
-            x = x + o.view(B, T, -1)
-            h = self._rms(x, blk.norm2)
+            h = self._add_rms(x, o.view(B, T, -1), blk.norm2)     # x += o, then the norm
             gu = blk.gate_up(h.view(B * T, -1))
             half = gu.shape[-1] // 2
             act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
             dn = blk.down(act)
             all_reduce_sum(dn)                                    # row parallel
-            x = x + dn.view(B, T, -1)
+            pending = dn.view(B, T, -1)                           # added by the next layer's (or the final) norm
+        x = x + pending
         last = self._rms(x[:, -1], self.final_norm)
         return last @ self.lm_head
 

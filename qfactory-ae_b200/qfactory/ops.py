@@ -26,6 +26,19 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: torch
     return out
 
 
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """x += residual (in place, fp16), then the RMS norm of the sum: returns the normed tensor."""
+    assert x.is_cuda and x.dtype == torch.float16 and x.is_contiguous()
+    assert residual.shape == x.shape and residual.dtype == torch.float16 and residual.is_contiguous()
+    d = x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    _native.check(_native.lib().qfb_add_rmsnorm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                                x.numel() // d, d, eps, _stream(x)), "qfb_add_rmsnorm")
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """silu(gate_up[..., :h]) * gate_up[..., h:] with h = half of the last dimension."""
     assert gate_up.is_cuda and gate_up.dtype == torch.float16 and gate_up.is_contiguous()

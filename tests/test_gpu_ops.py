@@ -106,3 +106,16 @@ def test_native_quantizer_matches_the_torch_expression(bits, GS, K, N):
     q1, s1, z1 = asymmetric_quant(w.cuda(), GS, bits)     # CUDA: the native kernel
     assert torch.equal(q1.cpu(), q0) and torch.equal(z1.cpu(), z0)
     assert torch.equal(s1.cpu().view(torch.int16), s0.view(torch.int16))
+
+
+def test_add_rmsnorm_adds_in_place_and_norms_the_sum():
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.randn(5, 4096, generator=g, device="cuda").half()
+    r = torch.randn(5, 4096, generator=g, device="cuda").half()
+    w = (torch.rand(4096, generator=g, device="cuda") + 0.5).half()
+    want_x = x + r
+    want_y = ops.rmsnorm(want_x, w, 1e-5)
+    xs = x.clone()
+    got_y = ops.add_rmsnorm(xs, r, w, 1e-5)
+    assert torch.equal(xs, want_x)          # the fp16 sum, in place
+    assert torch.equal(got_y, want_y)       # same reduction as the plain norm kernel
