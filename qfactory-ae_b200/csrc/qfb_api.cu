@@ -302,9 +302,9 @@ static size_t mma_smem(int rows, int nt, int bpc, int kways) {
   return (std::max(stage, red) + 15) / 16 * 16;
 }
 // the receive buffer of the in-cluster split-K reduction follows the region above
+static int mma_quads_per_owner(int rows, int split) { return (rows * 32 + split - 1) / split; }
 static size_t mma_recv_bytes(int rows, int split) {
-  const int nout = rows * 128;
-  return (size_t)split * ((nout + split - 1) / split) * sizeof(float);
+  return (size_t)split * mma_quads_per_owner(rows, split) * 4 * sizeof(float);
 }
 
 // Split-K factor, k-ways and reduction mode of the mma.sync GEMV.  Cost model fitted to sweeps
@@ -394,6 +394,9 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     // up to 8 splits reduce inside a thread-block cluster; more go through the workspace
     p.cluster = pl.cluster;
     p.recv_offset = pl.recv_offset;
+    p.quads_per_owner = mma_quads_per_owner(rows, pl.split);  // >= 4 (32 quads per row, at most 8 splits in a cluster)
+    p.qper_magic = (uint32_t)(((1ull << 32) + p.quads_per_owner - 1) / p.quads_per_owner);
+    p.status = (workspace && ws_bytes >= kHeaderBytes) ? static_cast<unsigned*>(workspace) : nullptr;
     if (pl.split > 1 && !p.cluster) {
       const size_t off = partial_offset(v.tiles);
       const size_t need = off + (size_t)pl.split * rows * v.npad * sizeof(float);

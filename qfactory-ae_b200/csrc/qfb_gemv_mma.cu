@@ -34,6 +34,7 @@
 
 #include "qfb_common.cuh"
 #include "qfb_kernels.h"
+#include "qfb_ptx.cuh"
 
 namespace qfb {
 
@@ -67,6 +68,12 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, int rank, float v)
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
 }
+__device__ __forceinline__ void st_cluster_v4(uint32_t local_addr, int rank, const float4& v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
 
 constexpr int kRedStride = 132;  // floats per (k-way, batch row) line of the k-way reduction
 
@@ -76,6 +83,17 @@ __device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t 
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
+
+// Development builds only (-DQFB_MMA_STOP_AFTER=n): leave the kernel after phase n, to measure the
+// phases one by one.  0 = the whole kernel.
+#ifndef QFB_MMA_STOP_AFTER
+#define QFB_MMA_STOP_AFTER 0
+#endif
+// 1: one bulk (TMA) copy per activation row, issued by the lanes of warp 0; 0: 16-byte
+// asynchronous copies issued by every thread
+#ifndef QFB_MMA_BULK_STAGE
+#define QFB_MMA_BULK_STAGE 1
+#endif
 
 // the words of one lane and k-step a warp holds: 4 (16 bytes), 2 or 1
 template <int NW> struct Words;
@@ -204,9 +222,31 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   grid_launch_dependents();
   grid_dependency_wait();
 
-  // ---- stage the CTA's activation slice (plain 16-byte asynchronous copies) -----------------
+  // ---- stage the CTA's activation slice ------------------------------------------------------
   const int xstride = p.batches_per_cta * 128 + 16;  // halfs; +16 keeps the fragment loads conflict-free
   __half* x_s = reinterpret_cast<__half*>(smem);
+#if QFB_MMA_BULK_STAGE
+  // one bulk copy per row (256 bytes per batch: sizes and both addresses are multiples of 16),
+  // lane r of warp 0 issues row r; warp 0 waits for the bytes, the barrier below publishes them
+  __shared__ __align__(8) uint64_t xbar;
+  __shared__ int xabort;
+  if (warp == 0) {
+    const uint32_t bar = ptx::smem_u32(&xbar);
+    const uint32_t row_bytes = (uint32_t)ncta * 256u;
+    if (lane == 0) {
+      xabort = 0;
+      ptx::mbar_init(bar, 1);
+      ptx::fence_barrier_init();
+      ptx::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)p.m);
+    }
+    __syncwarp();
+    if (lane < p.m)
+      ptx::tma_bulk_g2s(ptx::smem_u32(x_s + (size_t)lane * xstride), p.x + (size_t)lane * p.k + (size_t)bb * 128,
+                        row_bytes, bar);
+    // bounded: a copy that never lands raises the status word instead of hanging the CTA
+    if (!ptx::mbar_wait(bar, 0, &xabort) && lane == 0 && p.status) atomicExch(p.status, 1u);
+  }
+#else
   {
     const int nvec_row = ncta * 16;
     for (int m = 0; m < p.m; ++m) {
@@ -216,7 +256,9 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
     }
     cp_async_commit_wait_all();
   }
+#endif
   __syncthreads();
+  if (QFB_MMA_STOP_AFTER == 2) return;
 
   // activation row each batch tile of this thread reads (rows >= m repeat the last valid row;
   // their output columns are never stored)
@@ -230,25 +272,40 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   {
     const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};  // fp16 1.0
     const int nwarps = blockDim.x >> 5;
-    for (int sg = warp; sg < ncta * NSEG; sg += nwarps) {
-      float dx[NT][4];
+    // two segments per pass and two accumulators per segment (even / odd k-steps): independent
+    // MMA chains, so the latency of a dependent accumulate is paid KS / 2 times, not KS per segment
+    const int nsegs = ncta * NSEG;
+    for (int sg0 = warp; sg0 < nsegs; sg0 += 2 * nwarps) {
+      float dx[2][NT][2][4];
 #pragma unroll
-      for (int k4 = 0; k4 < KS; ++k4) {
+      for (int u = 0; u < 2; ++u) {
+        const int sg = min(sg0 + u * nwarps, nsegs - 1);  // (a clamped duplicate is computed and dropped)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint2 v = *reinterpret_cast<const uint2*>(xrow[nt] + (sg * KS + k4) * 16);
-          if (k4 == 0) mma_m16n8k16_zero(dx[nt], ones, v.x, v.y);
-          else mma_m16n8k16(dx[nt], ones, v.x, v.y);
+        for (int k4 = 0; k4 < KS; ++k4) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint2 v = *reinterpret_cast<const uint2*>(xrow[nt] + (sg * KS + k4) * 16);
+            if (k4 < 2) mma_m16n8k16_zero(dx[u][nt][k4 & 1], ones, v.x, v.y);
+            else mma_m16n8k16(dx[u][nt][k4 & 1], ones, v.x, v.y);
+          }
         }
       }
       if (g == 0) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-          *reinterpret_cast<float2*>(xsum_s + sg * (8 * NT) + nt * 8 + 2 * t) = make_float2(dx[nt][0], dx[nt][1]);
+        for (int u = 0; u < 2; ++u) {
+          const int sg = sg0 + u * nwarps;
+          if (sg < nsegs) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+              *reinterpret_cast<float2*>(xsum_s + sg * (8 * NT) + nt * 8 + 2 * t) =
+                  make_float2(dx[u][nt][0][0] + dx[u][nt][1][0], dx[u][nt][0][1] + dx[u][nt][1][1]);
+          }
+        }
       }
     }
   }
   __syncthreads();
+  if (QFB_MMA_STOP_AFTER == 3) return;
 
   float acc[RB][NT][4];
 #pragma unroll
@@ -334,6 +391,18 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
     }
   }
 
+  if (QFB_MMA_STOP_AFTER == 4) {  // keep the results alive without storing them
+    float sum = 0.f;
+#pragma unroll
+    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum += acc[rb][nt][i];
+    if (sum == 12345.678f) p.y[0] = __float2half_rn(sum);
+    return;
+  }
+
   // ---- combine the k-ways of the CTA ----------------------------------------------------
   __syncthreads();  // everyone is done reading the staged activations
   float* red = reinterpret_cast<float*>(smem);
@@ -348,44 +417,64 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
         if (mm < p.m) red[(kw * p.m + mm) * kRedStride + r] = acc[rb][nt][i];
       }
   __syncthreads();
+  if (QFB_MMA_STOP_AFTER == 5) return;
 
+  // From here on the outputs of the tile are handled as quads: four consecutive rows of one
+  // batch column (quad q: column q / 32, rows 4 * (q % 32) ...), 16-byte shared-memory accesses.
   const int nout = p.m * kTileRows;
-  if (S == 1) {
-    for (int i = tid; i < nout; i += blockDim.x) {
-      const int mm = i >> 7, r = i & 127;
-      float s = 0.f;
-      for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
-      const int n = tile * kTileRows + r;
-      if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+  const int nq = p.m * (kTileRows / 4);
+  auto kway_sum4 = [&](int q) {
+    const int mm = q >> 5, r = (q & 31) * 4;
+    float4 v = *reinterpret_cast<const float4*>(red + mm * kRedStride + r);
+    for (int w = 1; w < KW; ++w) {
+      const float4 u = *reinterpret_cast<const float4*>(red + (w * p.m + mm) * kRedStride + r);
+      v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
     }
+    return v;
+  };
+  auto store_quad = [&](int q, const float4& v) {
+    const int mm = q >> 5, n = tile * kTileRows + (q & 31) * 4;
+    __half* dst = p.y + (size_t)mm * p.n + n;
+    if (n + 3 < p.n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+      const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+      *reinterpret_cast<uint2*>(dst) = make_uint2(as_u32(lo), as_u32(hi));
+    } else {
+      const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n + i < p.n) dst[i] = __float2half_rn(e[i]);
+    }
+  };
+  if (S == 1) {
+    for (int q = tid; q < nq; q += blockDim.x) store_quad(q, kway_sum4(q));
     return;
   }
 
   if (p.cluster) {
     // split-K inside a thread-block cluster (the S splits of a tile are one cluster): CTA r owns
-    // the outputs i = r (mod S).  Every CTA pushes its k-way-reduced partial of output i into a
-    // receive buffer in the OWNER's shared memory (slot = the sender's split), one cluster barrier
-    // makes the pushes visible, and each owner sums its S slots in split order.  The receive
-    // buffer is a region of its own: a fast CTA may push while a slow one still computes.
-    float* recv = reinterpret_cast<float*>(reinterpret_cast<char*>(smem) + p.recv_offset);
+    // the quads [r * qper, (r + 1) * qper).  Every CTA pushes its k-way-reduced partial of a quad
+    // into a receive buffer in the OWNER's shared memory (slot = the sender's split), one cluster
+    // barrier makes the pushes visible, and each owner sums its S slots in split order.  The
+    // receive buffer is a region of its own: a fast CTA may push while a slow one still computes.
+    float4* recv = reinterpret_cast<float4*>(reinterpret_cast<char*>(smem) + p.recv_offset);
     const uint32_t recv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(recv));
-    const int per = (nout + S - 1) / S;  // outputs per owner
-    cluster_wait();                      // pairs with the arrive at kernel start: every CTA of the cluster runs
-    for (int i = tid; i < nout; i += blockDim.x) {
-      const int mm = i >> 7, r = i & 127;
-      float s = 0.f;
-      for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
-      const int j = i / S, owner = i - j * S;
-      st_cluster_f32(recv_addr + (split * per + j) * 4, owner, s);
+    const int qper = p.quads_per_owner;
+    cluster_wait();  // pairs with the arrive at kernel start: every CTA of the cluster runs
+    for (int q = tid; q < nq; q += blockDim.x) {
+      const float4 v = kway_sum4(q);
+      const int owner = (int)__umulhi((unsigned)q, p.qper_magic);  // q / qper (q < 2^9, qper <= 2^9)
+      st_cluster_v4(recv_addr + (split * qper + (q - owner * qper)) * 16, owner, v);
     }
     cluster_barrier();
-    for (int j = tid; j < per; j += blockDim.x) {
-      const int i = split + j * S;
-      if (i < nout) {
-        float s = 0.f;
-        for (int u = 0; u < S; ++u) s += recv[u * per + j];
-        const int mm = i >> 7, n = tile * kTileRows + (i & 127);
-        if (n < p.n) p.y[(size_t)mm * p.n + n] = __float2half_rn(s);
+    for (int j = tid; j < qper; j += blockDim.x) {
+      const int q = split * qper + j;
+      if (q < nq) {
+        float4 v = recv[j];
+        for (int u = 1; u < S; ++u) {
+          const float4 w = recv[u * qper + j];
+          v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        store_quad(q, v);
       }
     }
     return;
@@ -393,11 +482,9 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
 
   // split-K through the workspace: publish this CTA's partial, the last CTA of the tile to
   // arrive sums them in split order
-  for (int i = tid; i < nout; i += blockDim.x) {
-    const int mm = i >> 7, r = i & 127;
-    float s = 0.f;
-    for (int q = 0; q < KW; ++q) s += red[(q * p.m + mm) * kRedStride + r];
-    p.partial[((size_t)split * p.m + mm) * p.npad + tile * kTileRows + r] = s;
+  for (int q = tid; q < nq; q += blockDim.x) {
+    const int mm = q >> 5, r = (q & 31) * 4;
+    *reinterpret_cast<float4*>(p.partial + ((size_t)split * p.m + mm) * p.npad + tile * kTileRows + r) = kway_sum4(q);
   }
   __threadfence();
   __syncthreads();

@@ -50,6 +50,9 @@ struct MmaParams {
   uint32_t zconst;
   int cluster;           // 1: the S splits of a tile are one thread-block cluster and reduce in shared memory
   int recv_offset;       // byte offset of the cluster reduction's receive buffer in dynamic shared memory
+  int quads_per_owner;   // cluster reduction: ceil(m * 32 / S) quads (4 rows of one batch column) per CTA of the cluster
+  uint32_t qper_magic;   // ceil(2^32 / quads_per_owner): q / quads_per_owner = umulhi(q, qper_magic) for q < 2^9
+  unsigned* status;      // may be null; set to 1 when a bounded wait ran out
 };
 // clusters of `cluster` CTAs of the mma.sync GEMV the current device holds at once (cached)
 int mma_max_active_clusters(int bits, int nt, bool seg64, int block, size_t smem, int cluster);
