@@ -11,7 +11,8 @@ alternated between steps, so every launch streams its weights from HBM.
 
 metric / value: achieved GB/s = the reference's algorithmic-bytes model
 (activations + outputs + packed codes + fp16 scales + packed zeros) per step divided by
-the device time per step, inputs resident in HBM, the step replayed as a CUDA graph.
+the device time per step, inputs resident in HBM, the steps replayed as CUDA graphs of
+10 steps each (--steps-per-graph; the gap between two graph launches is not part of the path).
 e2e: the same bytes over the time of calling each case through the host-buffer entry
 (pinned host activations in, host result out; a step queues its 12 layers - captured once in a
 CUDA graph - and waits for the stream once; copies and the wait are inside the timed region).  With N > 1 every rank runs its own replica of the sweep (the path has no
@@ -216,6 +217,9 @@ def main():
     ap.add_argument("--sweep", default="", help="comma-separated sweeps instead of the benchmark, one JSON line each: "
                     "a family of SWEEP_FAMILIES (sizes at M = 1), 'bits' (2/3/4/8-bit on 8192x8192) or 'batch' "
                     "(M = 1..1024 on the Llama-70B MLP shapes)")
+    ap.add_argument("--steps-per-graph", type=int, default=10, help="steps captured in one CUDA graph (a decoder's graph "
+                    "holds hundreds of layer launches; a single 12-launch step per graph would time the gap between graph "
+                    "launches as much as the kernels)")
     ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
                     "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
@@ -365,15 +369,39 @@ def main():
             def __init__(self, fn):
                 self.replay = fn
 
-        graphs = []
-        for rep in range(REPL):
-            if not args.graph:
-                graphs.append(Eager(lambda rep=rep: run_step(rep)))
-                continue
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr, stream=stream):
-                run_step(rep)
-            graphs.append(gr)
+        G = max(1, args.steps_per_graph) if args.graph else 1
+
+        def capture(step_fn):
+            """One single-step graph per replica, and one graph of G steps that alternate the replicas."""
+            singles = []
+            for rep in range(REPL):
+                if not args.graph:
+                    singles.append(Eager(lambda rep=rep: step_fn(rep)))
+                    continue
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=stream):
+                    step_fn(rep)
+                singles.append(gr)
+            multi = None
+            if G > 1:
+                multi = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(multi, stream=stream):
+                    for j in range(G):
+                        step_fn(j % REPL)
+            return singles, multi
+
+        def replay_steps(gs, n):
+            singles, multi = gs
+            i = 0
+            if multi is not None:
+                while i + G <= n:
+                    multi.replay()
+                    i += G
+            while i < n:
+                singles[i % REPL].replay()
+                i += 1
+
+        graphs = capture(run_step)
 
         def barrier():
             torch.cuda.synchronize()
@@ -389,45 +417,32 @@ def main():
                            _native.lib().qfb_select_kernel(M, layer.out_features, layer.in_features, BITS, flags))
         sub_graphs = {}
         for kid in sorted(set(kern_of)):
-            gl = []
-            for rep in range(REPL):
-                def sub_step(rep=rep, kid=kid):
-                    for ci, (_, _, layer, x, y, _, _) in enumerate(cases[rep]):
-                        if kern_of[ci] == kid:
-                            layer(x, out=y)
+            def sub_step(rep, kid=kid):
+                for ci, (_, _, layer, x, y, _, _) in enumerate(cases[rep]):
+                    if kern_of[ci] == kid:
+                        layer(x, out=y)
 
-                if not args.graph:
-                    gl.append(Eager(sub_step))
-                    continue
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr, stream=stream):
-                    sub_step()
-                gl.append(gr)
-            sub_graphs[kid] = gl
+            sub_graphs[kid] = capture(sub_step)
 
-        for i in range(max(args.warmup, 3)):
-            graphs[i % REPL].replay()
+        replay_steps(graphs, max(args.warmup, 3))
         barrier()
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(args.steps):
-            graphs[i % REPL].replay()
+        replay_steps(graphs, args.steps)
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
 
         kernel_ms = {}
         for kid, gl in sub_graphs.items():
-            for i in range(3):
-                gl[i % REPL].replay()
+            replay_steps(gl, 3)
             torch.cuda.synchronize()
             k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             k0.record()
-            for i in range(args.steps):
-                gl[i % REPL].replay()
+            replay_steps(gl, args.steps)
             k1.record()
             torch.cuda.synchronize()
             kernel_ms[kid] = k0.elapsed_time(k1) / args.steps
@@ -569,7 +584,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS, "launches_per_step": n_cases,
                        "cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
-                       "graph": bool(args.graph), "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
+                       "graph": bool(args.graph), "steps_per_graph": G, "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches * world,

@@ -290,6 +290,9 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
 }
 
 // ---- mma.sync GEMV over the fragment layout ---------------------------------------------
+// warps of the mma.sync GEMV an SM holds: 16 at 128 registers per thread, 20 at 96 (CTAs of up to
+// kMmaSmallBlock threads)
+static int mma_warps_per_sm(int block) { return block <= kMmaSmallBlock ? 20 : 16; }
 struct MmaPlan { int nt, split, kways, cluster, recv_offset; size_t smem; };
 
 static int mma_split_cap(int tiles, int batches) {
@@ -319,7 +322,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
   // warps per k-way: 2 x 64 rows (m <= 8, 2- and 4-bit) or 4 x 32 rows; at most 256 threads
-  const int wpk = (pl.nt == 1 && bits != 8) ? 2 : 4;
+  const int wpk = kTileRows / mma_rows_per_warp(bits, pl.nt);
   const int kways_max = 8 / wpk;
   const int cap = mma_split_cap(tiles, batches);
   const size_t smem_max = 100 * 1024;
@@ -335,9 +338,9 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
       if (smem > smem_max && s < cap) continue;
       const int per_kway = (bpc + kw - 1) / kw;
       const double base = 0.05 * s + 0.01 * (kways_max - kw);
-      // through the workspace: 16 warps of 128 registers per thread and the shared memory bound the residency
+      // through the workspace: the registers (16 or 20 warps per SM) and the shared memory bound the residency
       if (!(g_mma_cluster == 2 && s > 1 && s <= 8)) {
-        const int resident = std::max(1, std::min(16 / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
+        const int resident = std::max(1, std::min(mma_warps_per_sm(block) / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
         const int waves = (tiles * s + kNumSMs * resident - 1) / (kNumSMs * resident);
         const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 0; }
@@ -405,7 +408,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
       p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
     }
     const dim3 grid(pl.split, v.tiles);
-    const int block = ((pl.nt == 1 && v.bits != 8) ? 64 : 128) * pl.kways;
+    const int block = 32 * (kTileRows / mma_rows_per_warp(v.bits, pl.nt)) * pl.kways;
     tl_last_launch[0] = 3;
     tl_last_launch[1] = grid.x;
     tl_last_launch[2] = grid.y;

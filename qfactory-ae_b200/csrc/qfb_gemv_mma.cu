@@ -153,7 +153,7 @@ template <int RB> struct ScaleZero {
 // A segment is the run of k-steps whose MMA accumulator is folded into the results at once
 // with one scale and zero per row: min(group, 128) k.
 template <int BITS, int NT, int RB, bool SEG64>
-__global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
+__device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
   constexpr int NSEG = SEG64 ? 2 : 1;  // segments per 128-k batch
@@ -200,11 +200,13 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
     grp_last = (we * NSEG - 1) / segs_per_group;
   }
 
-  ScaleZero<RB> sz_cur, sz_nxt;
+  // scales and zeros of the group being accumulated: loaded one segment ahead (right after the
+  // fold that consumed the previous group's), into the same registers
+  ScaleZero<RB> sz_cur;
 #pragma unroll
-  for (int i = 0; i < RB; ++i) sz_cur.s[i] = sz_nxt.s[i] = 0;
+  for (int i = 0; i < RB; ++i) sz_cur.s[i] = 0;
 #pragma unroll
-  for (int i = 0; i < RB / 2; ++i) sz_cur.z[i] = sz_nxt.z[i] = 0;
+  for (int i = 0; i < RB / 2; ++i) sz_cur.z[i] = 0;
   auto sz_offset = [&](int gi) { return (((size_t)tile * p.groups + gi) * 2 + wt) * 64 + g * 8 + sub * 4; };
 
   Words<NW> w[NSLOT][8];
@@ -215,10 +217,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
       for (int i = 0; i < 8; ++i) w[sl][i].load(wp + sl * kBatchBytes + i * kStepBytes);
     }
   wp += NSLOT * kBatchBytes;  // from here on: the batch NSLOT ahead of the one being processed
-  if (wb < we) {
-    sz_cur.load(p.qs, p.qz, sz_offset(grp));
-    if (grp < grp_last) sz_nxt.load(p.qs, p.qz, sz_offset(grp + 1));
-  }
+  if (wb < we) sz_cur.load(p.qs, p.qz, sz_offset(grp));
   grid_launch_dependents();
   grid_dependency_wait();
 
@@ -383,8 +382,7 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
         if (++gpos == segs_per_group) {  // the next segment starts a new group
           gpos = 0;
           ++grp;
-          sz_cur = sz_nxt;
-          if (grp < grp_last) sz_nxt.load(p.qs, p.qz, sz_offset(grp + 1));
+          if (grp <= grp_last) sz_cur.load(p.qs, p.qz, sz_offset(grp));
         }
       }
       wp += kBatchBytes;
@@ -565,9 +563,22 @@ __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   if (tid == 0) p.counters[tile] = 0u;
 }
 
+// Two register budgets of the same body: CTAs of up to 256 threads with 128 registers per thread
+// (two per SM, 16 warps), and CTAs of up to 128 threads with 96 (five per SM, 20 warps: measured
+// 7-9 % faster on layers with many row tiles, slower as 256-thread CTAs, which fit only twice
+// either way).
+template <int BITS, int NT, int RB, bool SEG64>
+__global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
+  gemv_mma_body<BITS, NT, RB, SEG64>(p);
+}
+template <int BITS, int NT, int RB, bool SEG64>
+__global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
+  gemv_mma_body<BITS, NT, RB, SEG64>(p);
+}
+
 template <int BITS, int NT, int RB, bool SEG64>
 static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
-  auto kern = gemv_mma_kernel<BITS, NT, RB, SEG64>;
+  auto kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64> : gemv_mma_kernel<BITS, NT, RB, SEG64>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(block);
@@ -600,7 +611,7 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
 // the current device holds at once; cached per configuration.  0 when the query fails.
 template <int BITS, int NT, int RB, bool SEG64>
 static int query_clusters(int block, size_t smem, int cluster) {
-  auto kern = gemv_mma_kernel<BITS, NT, RB, SEG64>;
+  auto kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64> : gemv_mma_kernel<BITS, NT, RB, SEG64>;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return 0;
@@ -634,6 +645,10 @@ static int query_clusters(int block, size_t smem, int cluster) {
     if (bits == 2 && nt == 1) return seg64 ? FN<2, 1, 4, true>(__VA_ARGS__) : FN<2, 1, 4, false>(__VA_ARGS__); \
     if (bits == 2 && nt == 2) return seg64 ? FN<2, 2, 2, true>(__VA_ARGS__) : FN<2, 2, 2, false>(__VA_ARGS__); \
   } while (0)
+
+int mma_rows_per_warp(int bits, int nt) {
+  return (nt == 1 && bits != 8) ? 64 : 32;
+}
 
 static int query_any(int bits, int nt, bool seg64, int block, size_t sm, int cluster) {
   QFB_MMA_DISPATCH(query_clusters, block, sm, cluster);

@@ -54,6 +54,10 @@ struct MmaParams {
   uint32_t qper_magic;   // ceil(2^32 / quads_per_owner): q / quads_per_owner = umulhi(q, qper_magic) for q < 2^9
   unsigned* status;      // may be null; set to 1 when a bounded wait ran out
 };
+// CTAs of the mma.sync GEMV of up to this many threads run the 96-register build (five per SM)
+constexpr int kMmaSmallBlock = 128;
+// rows of a 128-row tile one warp of the mma.sync GEMV owns (64 or 32) for a bit width and number of batch tiles
+int mma_rows_per_warp(int bits, int nt);
 // clusters of `cluster` CTAs of the mma.sync GEMV the current device holds at once (cached)
 int mma_max_active_clusters(int bits, int nt, bool seg64, int block, size_t smem, int cluster);
 cudaError_t launch_gemv_mma(const MmaParams& p, int bits, int nt, dim3 grid, int block, size_t smem, bool pdl,
