@@ -295,8 +295,14 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
 static int mma_warps_per_sm(int block) { return block <= kMmaSmallBlock ? 20 : 16; }
 struct MmaPlan { int nt, split, kways, cluster, recv_offset; size_t smem; };
 
+// most splits through the workspace (its size follows from this bound)
 static int mma_split_cap(int tiles, int batches) {
   return std::max(1, std::min(batches, (kNumSMs * 4 + tiles - 1) / tiles));
+}
+// most splits inside a cluster: enough CTAs of the smallest block to fill every slot of the device once
+static int mma_cluster_split_cap(int tiles, int batches, int min_block) {
+  const int slots = kNumSMs * (mma_warps_per_sm(min_block) * 32 / min_block);
+  return std::max(1, std::min(std::min(batches, 8), (slots + tiles - 1) / tiles));
 }
 
 static size_t mma_smem(int rows, int nt, int bpc, int kways) {
@@ -324,9 +330,10 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
   // warps per k-way: 2 x 64 rows (m <= 8, 2- and 4-bit) or 4 x 32 rows; at most 256 threads
   const int wpk = kTileRows / mma_rows_per_warp(bits, pl.nt);
   const int kways_max = 8 / wpk;
-  const int cap = mma_split_cap(tiles, batches);
+  const int cap_ws = mma_split_cap(tiles, batches);
+  const int cap = std::max(cap_ws, g_mma_cluster ? mma_cluster_split_cap(tiles, batches, 32 * wpk) : 1);
   const size_t smem_max = 100 * 1024;
-  int best_s = cap, best_kw = 1, best_cl = 0;
+  int best_s = cap_ws, best_kw = 1, best_cl = 0;
   double best_cost = 1e30;
   for (int kw = kways_max; kw >= 1; kw >>= 1) {
     if (g_tune_kways > 0 && kw != std::min(g_tune_kways, kways_max)) continue;
@@ -339,7 +346,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
       const int per_kway = (bpc + kw - 1) / kw;
       const double base = 0.05 * s + 0.01 * (kways_max - kw);
       // through the workspace: the registers (16 or 20 warps per SM) and the shared memory bound the residency
-      if (!(g_mma_cluster == 2 && s > 1 && s <= 8)) {
+      if (s <= cap_ws && !(g_mma_cluster == 2 && s > 1 && s <= 8)) {
         const int resident = std::max(1, std::min(mma_warps_per_sm(block) / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
         const int waves = (tiles * s + kNumSMs * resident - 1) / (kNumSMs * resident);
         const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
@@ -349,8 +356,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
         const int fit = mma_max_active_clusters(bits, pl.nt, seg64, block, smem + mma_recv_bytes(rows, s), s);
         if (fit > 0) {
           const int waves = (tiles + fit - 1) / fit;
-          // (clusters that need several waves pack worse than single CTAs: measured ~15 % slower)
-          const double cost = (double)waves * (per_kway + 1.5) * (waves > 1 ? 1.15 : 1.0) + base + 0.02 * rows * s;
+          const double cost = (double)waves * (per_kway + 1.5) + base + 0.02 * rows * s;
           if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 1; }
         }
       }
