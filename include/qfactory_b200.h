@@ -163,6 +163,10 @@ int qfb_read_status(const void* workspace, void* stream, unsigned* status_out);
 void qfb_set_gemv_tuning(int split_k, int k_ways);
 /* Tuning override of the tensor-core kernel's split-K factor for batches <= 64 (0 = built-in). */
 void qfb_set_tensor_split(int split_k);
+/* Tuning override of the tensor-core kernel's decode groups where it scales in the decode (batches
+ * > 32, or groups of 64): 1 = eight decode warps, 2 = two groups of eight that take alternate
+ * stages; 0 = built-in choice (2). */
+void qfb_set_tensor_decode_groups(int groups);
 /* mma.sync GEMV (fragment layout), how K splits are reduced: 1 (default) lets the cost model
  * choose between a thread-block cluster (distributed shared memory, at most 8 splits) and the
  * workspace; 0 always uses the workspace; 2 uses a cluster whenever there are 2..8 splits. */

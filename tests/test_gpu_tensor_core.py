@@ -138,3 +138,25 @@ def test_kernel_selection_rule():
     assert L.qfb_select_kernel(4, 4096, 4096, 4, 0) == 2
     assert L.qfb_select_kernel(4, 4096, 4096, 4, _native.FLAG_FORCE_SIMT) == 1
     assert L.qfb_select_kernel(4, 4096, 4160, 4, 0) == 1          # K not a multiple of 128
+
+
+@pytest.mark.parametrize("M,GS,bits", [(40, 128, 4), (64, 64, 4), (130, 128, 4), (300, 256, 8), (200, 128, 2), (90, -1, 4), (150, 128, 3)])
+def test_one_and_two_decode_groups_give_identical_results(M, GS, bits):
+    """Where the scale is applied in the decode the kernel runs two decode groups on alternate
+    stages (768 threads); one group (512 threads) must give the same bits."""
+    L = _native.lib()
+    try:
+        L.qfb_set_tensor_decode_groups(2)
+        info2, layer, x = _run(M, 384, 2048, bits, GS, False, seed=900 + M)
+        xs = x.cuda()
+        y2 = layer(xs).clone()
+        L.qfb_set_tensor_decode_groups(1)
+        y1 = layer(xs).clone()
+        info1 = _native.last_launch()
+        torch.cuda.synchronize()
+    finally:
+        L.qfb_set_tensor_decode_groups(0)
+    assert torch.equal(y1, y2)
+    # 16- and 32-wide batch tiles with per-stage accumulators always run one group
+    if info2["block"] == 768:
+        assert info1["block"] == 512
