@@ -41,7 +41,7 @@ UNIT = "GB/s"
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch, from the ncu
 # captures of the (22016,4096) case summarised under profiles/; traffic grows with the weight
 # bytes, so the average launch of the sweep is scaled by the same factor
-NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": 1.00795}
+NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": 1.008, "gemv_mma_kernel_small": 1.008}
 # (N, K) of the linear layers of other model families, and squares, for --sweep
 SWEEP_FAMILIES = {
     "llama2-13b": [(5120, 5120), (27648, 5120), (5120, 13824), (15360, 5120)],
@@ -411,10 +411,14 @@ def main():
 
         # which kernel serves each case, and one graph per kernel so that the dominant kernel's
         # own time can be measured with events in this same run
+        # (the mma.sync GEMV has two register builds, picked by the CTA size: they show up under two
+        # names in a profile, so they are told apart here as well: 4 = its build for small CTAs)
         kern_of = []
-        for _, M, layer, *_ in cases[0]:
-            kern_of.append(3 if layer.packed_layout else
-                           _native.lib().qfb_select_kernel(M, layer.out_features, layer.in_features, BITS, flags))
+        for _, M, layer, x, y, _, _ in cases[0]:
+            layer(x, out=y)
+            info = _native.last_launch()
+            kern_of.append(4 if info["kernel"] == 3 and info["block"] <= 128 else info["kernel"])
+        torch.cuda.synchronize()
         sub_graphs = {}
         for kid in sorted(set(kern_of)):
             def sub_step(rep, kid=kid):
@@ -566,7 +570,7 @@ def main():
         e2e_val = sb * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
         launches = n_cases * args.steps
         # dominant kernel = the one with the larger share of the step's device time
-        names = {1: "gemv_splitk_kernel", 2: "qgemm_tc_kernel", 3: "gemv_mma_kernel"}
+        names = {1: "gemv_splitk_kernel", 2: "qgemm_tc_kernel", 3: "gemv_mma_kernel", 4: "gemv_mma_kernel_small"}
         shares = {}
         for kid, kms in kernel_ms.items():
             idx = [ci for ci in range(n_cases) if kern_of[ci] == kid]

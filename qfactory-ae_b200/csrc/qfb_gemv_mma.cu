@@ -91,9 +91,6 @@ __device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t 
 #endif
 // 1: one bulk (TMA) copy per activation row, issued by the lanes of warp 0; 0: 16-byte
 // asynchronous copies issued by every thread
-#ifndef QFB_MMA_MAX_CARVEOUT
-#define QFB_MMA_MAX_CARVEOUT 1
-#endif
 #ifndef QFB_MMA_BULK_STAGE
 #define QFB_MMA_BULK_STAGE 1
 #endif
@@ -607,17 +604,6 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-#if QFB_MMA_MAX_CARVEOUT
-  // One shared-memory carve-out for every launch of this kernel family: consecutive launches with
-  // different shared-memory needs (3 KB at one row, 40-80 KB at sixteen) otherwise switch the
-  // SMs' L1 / shared-memory split between kernels, which cannot happen while CTAs of the
-  // previous kernel are resident and so serialises the launches.  The kernel streams its weights
-  // past L1, so the smaller L1 costs nothing.
-  {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (e != cudaSuccess) return e;
-  }
-#endif
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
