@@ -229,6 +229,16 @@ int qfb_rope_cache(void* qkv, const void* cos, const void* sin, const void* pos,
 int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float eps, void* stream);
 int qfb_add_rmsnorm(void* x, const void* residual, const void* w, void* y, int rows, int d, float eps, void* stream);
 int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* stream);
+/*
+ * Single-query (decode step) attention over the static cache, one launch: for every batch row and
+ * query head, softmax(q . K^T / sqrt(hd)) . V over the keys 0 .. pos[0] (pos: one i64 on the
+ * device, so a captured graph can be replayed at the next position).
+ *   qkv fp16 [B, hq + 2 hkv, hd] (queries already rotated, e.g. by qfb_rope_cache, which also wrote
+ *   position pos into the caches); k_cache, v_cache fp16 [B, hkv, max_len, hd]; out fp16 [B, hq * hd].
+ * hd = 128, hq / hkv in {1, 2, 4, 8}, max_len <= 16384; otherwise QFB_ERR_UNSUPPORTED.
+ */
+int qfb_decode_attention(const void* qkv, const void* pos, const void* k_cache, const void* v_cache, void* out,
+                         int batch, int q_heads, int kv_heads, int head_dim, int max_len, void* stream);
 
 #ifdef __cplusplus
 }

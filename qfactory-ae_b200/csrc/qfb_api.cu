@@ -694,6 +694,20 @@ int qfb_rope_cache(void* qkv, const void* cosv, const void* sinv, const void* po
                                       q_heads, kv_heads, head_dim, max_len, static_cast<cudaStream_t>(stream)));
 }
 
+int qfb_decode_attention(const void* qkv, const void* pos, const void* k_cache, const void* v_cache, void* out, int batch,
+                         int q_heads, int kv_heads, int head_dim, int max_len, void* stream) {
+  if (!qkv || !pos || !k_cache || !v_cache || !out) return QFB_ERR_NULL_POINTER;
+  if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_len <= 0) return QFB_ERR_BAD_SHAPE;
+  if (!decode_attention_supported(q_heads, kv_heads, head_dim, max_len)) return QFB_ERR_UNSUPPORTED;
+  if (!aligned16(qkv) || !aligned16(k_cache) || !aligned16(v_cache) || (reinterpret_cast<uintptr_t>(out) & 1u))
+    return QFB_ERR_MISALIGNED;
+  if (batch == 0) return QFB_OK;
+  return check_cuda(launch_decode_attention(static_cast<const __half*>(qkv), static_cast<const __half*>(k_cache),
+                                            static_cast<const __half*>(v_cache), static_cast<const long long*>(pos),
+                                            static_cast<__half*>(out), batch, q_heads, kv_heads, max_len,
+                                            static_cast<cudaStream_t>(stream)));
+}
+
 int qfb_rmsnorm(const void* x, const void* w, void* y, int rows, int d, float eps, void* stream) {
   if (!x || !w || !y) return QFB_ERR_NULL_POINTER;
   if (rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;

@@ -88,6 +88,10 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bit
 cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half* y, int rows, int d, float eps,
                            cudaStream_t st);
 cudaError_t launch_silu_mul(const __half* gu, __half* out, int rows, int half, cudaStream_t st);
+// single-query attention over the static cache (qfb_decode_attention.cu)
+bool decode_attention_supported(int hq, int hkv, int hd, int max_len);
+cudaError_t launch_decode_attention(const __half* qkv, const __half* k_cache, const __half* v_cache, const long long* pos,
+                                    __half* out, int B, int hq, int hkv, int max_len, cudaStream_t st);
 cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sinv, const long long* pos, __half* k_cache,
                               __half* v_cache, int B, int T, int hq, int hkv, int hd, int max_len, cudaStream_t st);
 

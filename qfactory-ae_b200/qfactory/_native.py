@@ -27,7 +27,7 @@ EXPORTS = (
     "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_set_tensor_decode_groups", "qfb_set_cluster_reduce", "qfb_read_status",
     "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
-    "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize",
+    "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention",
 )
 
 
@@ -116,6 +116,8 @@ def lib() -> ctypes.CDLL:
     L.qfb_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, ctypes.c_float, vp]
     L.qfb_rope_cache.restype = i32
     L.qfb_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
+    L.qfb_decode_attention.restype = i32
+    L.qfb_decode_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     L.qfb_quantize.restype = i32
     L.qfb_quantize.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.qfb_silu_mul.restype = i32

@@ -126,9 +126,13 @@ class QuantDecoder(torch.nn.Module):
                 q, k = self._rope(q, pos), self._rope(k, pos)
                 self.k_cache[li].index_copy_(2, pos, k.transpose(1, 2))
                 self.v_cache[li].index_copy_(2, pos, v.transpose(1, 2))
-            att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
-                                                 attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
-            o = blk.o(att.transpose(1, 2).reshape(B * T, -1))
+            if self.native_ops and T == 1 and ops.decode_attention_supported(blk.hq, blk.hkv, blk.hd, cfg.max_len):
+                att2d = ops.decode_attention(qkv, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)   # [B, hq * hd]
+            else:
+                att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
+                                                     attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
+                att2d = att.transpose(1, 2).reshape(B * T, -1)
+            o = blk.o(att2d)
             all_reduce_sum(o)                                     # row parallel
             h = self._add_rms(x, o.view(B, T, -1), blk.norm2)     # x += o, then the norm
             gu = blk.gate_up(h.view(B * T, -1))

@@ -63,3 +63,27 @@ def rope_cache(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: tor
     _native.check(_native.lib().qfb_rope_cache(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
                                                k_cache.data_ptr(), v_cache.data_ptr(), B, T, q_heads, kv_heads, hd,
                                                k_cache.shape[2], _stream(qkv)), "qfb_rope_cache")
+
+
+def decode_attention_supported(q_heads: int, kv_heads: int, head_dim: int, max_len: int) -> bool:
+    """Shapes `decode_attention` serves (the decoder falls back to the framework's attention otherwise)."""
+    return (head_dim == 128 and kv_heads > 0 and q_heads % kv_heads == 0 and q_heads // kv_heads in (1, 2, 4, 8)
+            and 0 < max_len <= 16384)
+
+
+def decode_attention(qkv: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, q_heads: int,
+                     kv_heads: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of ONE new token per batch row over the static cache: qkv [B, 1, q_heads + 2 kv_heads, hd]
+    with the queries already rotated (`rope_cache`, which also wrote position pos into the caches),
+    pos [1] int64 on the device, caches [B, kv_heads, max_len, hd].  Returns [B, q_heads * hd], the
+    O projection's input."""
+    B, T, H, hd = qkv.shape
+    assert T == 1 and H == q_heads + 2 * kv_heads and qkv.is_contiguous() and qkv.dtype == torch.float16
+    assert pos.dtype == torch.int64 and pos.numel() == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape == v_cache.shape == (B, kv_heads, k_cache.shape[2], hd)
+    if out is None:
+        out = torch.empty(B, q_heads * hd, dtype=torch.float16, device=qkv.device)
+    _native.check(_native.lib().qfb_decode_attention(qkv.data_ptr(), pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                     out.data_ptr(), B, q_heads, kv_heads, hd, k_cache.shape[2],
+                                                     _stream(qkv)), "qfb_decode_attention")
+    return out

@@ -119,3 +119,58 @@ def test_add_rmsnorm_adds_in_place_and_norms_the_sum():
     got_y = ops.add_rmsnorm(xs, r, w, 1e-5)
     assert torch.equal(xs, want_x)          # the fp16 sum, in place
     assert torch.equal(got_y, want_y)       # same reduction as the plain norm kernel
+
+
+@pytest.mark.parametrize("hq,hkv", [(64, 8), (32, 4), (8, 8), (16, 8), (32, 8)])
+@pytest.mark.parametrize("B,max_len,p", [(1, 512, 0), (1, 512, 5), (2, 512, 63), (1, 512, 64), (3, 512, 383), (1, 512, 511),
+                                         (2, 128, 100), (1, 64, 40), (1, 1024, 700), (1, 4096, 4095), (1, 200, 199)])
+def test_decode_attention_matches_an_fp32_reference(hq, hkv, B, max_len, p):
+    """One query per row over the keys 0..p of the static cache, against softmax(q k^T / sqrt(d)) v in fp32."""
+    hd = 128
+    g = torch.Generator(device="cuda").manual_seed(hq * 1000 + max_len + p)
+    qkv = torch.randn(B, 1, hq + 2 * hkv, hd, generator=g, device="cuda").half()
+    kc = torch.randn(B, hkv, max_len, hd, generator=g, device="cuda").half()
+    vc = torch.randn(B, hkv, max_len, hd, generator=g, device="cuda").half()
+    # positions past p hold values that must not leak into the result
+    kc[:, :, p + 1 :] = 1000.0
+    vc[:, :, p + 1 :] = 1000.0
+    pos = torch.tensor([p], dtype=torch.int64, device="cuda")
+    assert ops.decode_attention_supported(hq, hkv, hd, max_len)
+    out = ops.decode_attention(qkv, pos, kc, vc, hq, hkv)
+    q = qkv[:, 0, :hq].float()                                       # [B, hq, hd]
+    G = hq // hkv
+    k = kc[:, :, : p + 1].float().repeat_interleave(G, dim=1)        # [B, hq, n, hd]
+    v = vc[:, :, : p + 1].float().repeat_interleave(G, dim=1)
+    s = torch.einsum("bhd,bhnd->bhn", q, k) / hd ** 0.5
+    ref = torch.einsum("bhn,bhnd->bhd", torch.softmax(s, dim=-1), v).reshape(B, hq * hd)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-3 * max(1.0, ref.abs().max().item()), err
+
+
+def test_decode_attention_rejects_unsupported_shapes():
+    assert not ops.decode_attention_supported(64, 8, 64, 512)      # head dimension
+    assert not ops.decode_attention_supported(48, 8, 128, 512)     # six query heads per key/value head
+    assert not ops.decode_attention_supported(64, 8, 128, 1 << 15)
+
+
+def test_decode_step_with_native_attention_matches_torch_ops():
+    """A prefill, then single-token steps: the native attention (head dimension 128, four query heads
+    per key/value head) against the framework's masked attention over the whole cache."""
+    cfg = DecoderConfig(layers=2, d_model=1024, n_heads=8, n_kv_heads=2, d_ff=1024, vocab=1000, max_len=64)
+    assert cfg.head_dim == 128
+    a = QuantDecoder(cfg, device="cuda", seed=5, batch=2, native_ops=True)
+    b = QuantDecoder(cfg, device="cuda", seed=5, batch=2, native_ops=False)
+    for m in (a, b):
+        for blk in m.blocks:
+            for l in (blk.qkv, blk.o, blk.gate_up, blk.down):
+                l.s.mul_(20.0)
+    tokens = torch.randint(0, cfg.vocab, (2, 9), device="cuda")
+    with torch.no_grad():
+        a(tokens, torch.arange(9, device="cuda"))
+        b(tokens, torch.arange(9, device="cuda"))
+        for step in range(3):
+            tok = torch.randint(0, cfg.vocab, (2, 1), device="cuda")
+            pos = torch.tensor([9 + step], device="cuda")
+            ya, yb = a(tok, pos).float(), b(tok, pos).float()
+            assert torch.isfinite(ya).all()
+            assert (ya - yb).abs().max() <= 5e-3 * yb.abs().max()
