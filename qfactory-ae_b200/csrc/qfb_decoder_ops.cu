@@ -17,6 +17,10 @@ namespace qfb {
 __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* __restrict__ x, const __half* __restrict__ res,
                                                       const __half* __restrict__ w, __half* __restrict__ y, int d,
                                                       float eps) {
+  // programmatic dependent launch: the next kernel (a quantized linear, which fetches its weights
+  // before it waits for this one) may start now; nothing is read or written before the wait
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   uint4* xr = reinterpret_cast<uint4*>(x + (size_t)row * d);
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * d) : nullptr;
@@ -67,6 +71,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* __restrict__ x, co
 // out[r, j] = silu(gu[r, j]) * gu[r, half + j]   for j < half   (fp16, silu and product as fp16 ops)
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ gu, __half* __restrict__ out, int half,
                                                        long long total_vec) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-element vector each
   if (i >= total_vec) return;
   const int vec_per_row = half >> 3;
@@ -96,6 +102,8 @@ __global__ void __launch_bounds__(256) rope_cache_kernel(__half* __restrict__ qk
                                                          const __half* __restrict__ sinv, const long long* __restrict__ pos,
                                                          __half* __restrict__ k_cache, __half* __restrict__ v_cache,
                                                          int T, int hq, int hkv, int hd, int max_len, long long total) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one pair of elements each
   if (idx >= total) return;
   const int hp = hd >> 1, H = hq + 2 * hkv;
@@ -123,24 +131,38 @@ __global__ void __launch_bounds__(256) rope_cache_kernel(__half* __restrict__ qk
   }
 }
 
+// Every kernel of this file is launched with programmatic stream serialisation: it may become
+// resident while its predecessor drains, and waits (griddepcontrol.wait) before touching memory.
+template <class... KArgs, class... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sinv, const long long* pos, __half* k_cache,
                               __half* v_cache, int B, int T, int hq, int hkv, int hd, int max_len, cudaStream_t st) {
   const long long total = (long long)B * T * (hq + 2 * hkv) * (hd >> 1);
-  rope_cache_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(qkv, cosv, sinv, pos, k_cache, v_cache, T, hq, hkv, hd,
-                                                                      max_len, total);
-  return cudaGetLastError();
+  return launch_pdl(rope_cache_kernel, (unsigned)((total + 255) / 256), 256, st, qkv, cosv, sinv, pos, k_cache, v_cache, T, hq,
+                    hkv, hd, max_len, total);
 }
 
 cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half* y, int rows, int d, float eps,
                            cudaStream_t st) {
-  rmsnorm_kernel<<<rows, 256, 0, st>>>(x, res, w, y, d, eps);
-  return cudaGetLastError();
+  return launch_pdl(rmsnorm_kernel, (unsigned)rows, 256, st, x, res, w, y, d, eps);
 }
 
 cudaError_t launch_silu_mul(const __half* gu, __half* out, int rows, int half, cudaStream_t st) {
   const long long total = (long long)rows * (half >> 3);
-  silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(gu, out, half, total);
-  return cudaGetLastError();
+  return launch_pdl(silu_mul_kernel, (unsigned)((total + 255) / 256), 256, st, gu, out, half, total);
 }
 
 }  // namespace qfb
