@@ -2,7 +2,7 @@
 // tensor-core instruction (mma.sync m16n8k16), reading the "fragment" packed layout.
 //
 // Replaces the reference's kernel_gptq / kernel_gemv templates
-// (qfactory/include/gptq_gemv.h:14-154, qfactory/include/gemv.h:12-94) for 4-bit layers.
+// (qfactory/include/gptq_gemv.h:14-154, qfactory/include/gemv.h:12-94) for 2-, 4- and 8-bit layers.
 //
 // Why a third kernel.  On B200 the fp16x2 CUDA-core instructions and the integer/logic pipe both
 // issue at half rate, so a CUDA-core GEMV that spends LOP3 + HSUB2 + HFMA2 per code pair is
@@ -23,9 +23,11 @@
 // Mapping.  A CTA owns one 128-row tile and a range of 128-k batches; warp (wt, kw) owns the
 // 64-row half wt and the k-way kw of that range.  One 128-bit load per thread brings the words
 // of four row blocks for one 16-k step, so consecutive steps of a warp are consecutive 512-byte
-// runs.  Partial sums of the k-ways are combined in shared memory, those of the K splits
-// through the fp32 workspace by the last CTA of the tile to arrive, in split order
-// (deterministic; the counters reset themselves).
+// runs.  The CTA's activation slice arrives by one bulk (TMA) copy per batch row.  Partial sums
+// of the k-ways are combined in shared memory, those of the K splits either inside a thread-block
+// cluster (pushed into the owner's shared memory, one cluster barrier) or through the fp32
+// workspace by the last CTA of the tile to arrive; both in split order (deterministic; the
+// counters reset themselves).
 //
 // Ordering under programmatic dependent launch: weight, scale and zero loads are issued before
 // griddepcontrol.wait; activations, workspace and output are only touched after it.
