@@ -213,7 +213,7 @@ def main():
                     "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
     ap.add_argument("--reps", type=int, default=8)
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
-    ap.add_argument("--host-streams", type=int, default=6, help="streams the end-to-end step spreads its layers over")
+    ap.add_argument("--host-streams", type=int, default=8, help="streams the end-to-end step spreads its layers over")
     ap.add_argument("--sweep", default="", help="comma-separated sweeps instead of the benchmark, one JSON line each: "
                     "a family of SWEEP_FAMILIES (sizes at M = 1), 'bits' (2/3/4/8-bit on 8192x8192) or 'batch' "
                     "(M = 1..1024 on the Llama-70B MLP shapes)")
