@@ -113,8 +113,7 @@ class QuantDecoder(torch.nn.Module):
         cfg = self.cfg
         B, T = tokens.shape
         x = self.embed[tokens]                                   # [B, T, d]
-        # causal mask over the whole static cache: key j visible to query i iff j <= pos[i]
-        mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
+        mask = None   # built on first use: the single-token step with the native attention needs none
         pending = None   # output of the previous down projection, not yet added to the residual stream
         for li, blk in enumerate(self.blocks):
             h = self._add_rms(x, pending, blk.norm1) if pending is not None else self._rms(x, blk.norm1)
@@ -129,6 +128,9 @@ class QuantDecoder(torch.nn.Module):
             if self.native_ops and T == 1 and ops.decode_attention_supported(blk.hq, blk.hkv, blk.hd, cfg.max_len):
                 att2d = ops.decode_attention(qkv, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)   # [B, hq * hd]
             else:
+                if mask is None:
+                    # causal mask over the whole static cache: key j visible to query i iff j <= pos[i]
+                    mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
                 att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
                                                      attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
                 att2d = att.transpose(1, 2).reshape(B * T, -1)
