@@ -13,6 +13,9 @@ metric / value: achieved GB/s = the reference's algorithmic-bytes model
 (activations + outputs + packed codes + fp16 scales + packed zeros) per step divided by
 the device time per step, inputs resident in HBM, the steps replayed as CUDA graphs of
 10 steps each (--steps-per-graph; the gap between two graph launches is not part of the path).
+The K steps of --steps are timed as one pass with CUDA events, and the pass is repeated (at least
+7 times, until 0.25 s of device time): value and ms_per_step are the MEDIAN pass, `spread` holds
+the fastest and slowest one.
 e2e: the same bytes over the time of calling each case through the host-buffer entry
 (pinned host activations in, host result out; a step queues its 12 layers - captured once in a
 CUDA graph - and waits for the stream once; copies and the wait are inside the timed region).  With N > 1 every rank runs its own replica of the sweep (the path has no
@@ -38,9 +41,9 @@ BATCHES = [1, 4, 16]
 BITS, GS = 4, 128
 METRIC = "w4a16_g128_gemv_achieved_hbm_bandwidth"
 UNIT = "GB/s"
-# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch, from the ncu
-# captures of the (22016,4096) case summarised under profiles/; traffic grows with the weight
-# bytes, so the average launch of the sweep is scaled by the same factor
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch, from profiler
+# captures of the (22016,4096) case; traffic grows with the weight bytes, so the average launch
+# of the sweep is scaled by the same factor
 NCU_TRAFFIC_RATIO = {"qgemm_tc_kernel": 1.00592, "gemv_splitk_kernel": 1.0179, "gemv_mma_kernel": 1.008, "gemv_mma_kernel_small": 1.008}
 # (N, K) of the linear layers of other model families, and squares, for --sweep
 SWEEP_FAMILIES = {
@@ -78,6 +81,23 @@ def measured_peaks():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a GEMM timed alone (burst), measured on this pool, else the fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured burst"
+        except Exception:
+            pass
+    return 1590.0, "fallback burst"
+
+
+def bench_config(world):
+    """The workload description both arms print (the CPU arm runs the same 12 cases)."""
+    return {"workload": WORKLOAD, "bits": BITS, "group_size": GS, "cases_per_step": len(SHAPES) * len(BATCHES),
+            "batches": BATCHES, "parallelism": f"replicas x{world}"}
 
 
 class ClockSampler:
@@ -139,39 +159,36 @@ def use_all_host_threads(torch):
 
 def run_reference(args, rank, world):
     """The reference's own CPU path for this workload (dequantize, then fp16 matmul, in torch
-    on the host cores), restated in oracle/qf_oracle.py.  Each step is a bounded sample of
-    the sweep: the four layer shapes at M = 1."""
+    on the host cores), restated in oracle/qf_oracle.py.  One step = the same 12 cases as the
+    GPU arm: the four layer shapes at M = 1, 4 and 16, each dequantised and multiplied."""
     if rank != 0:
         return
     import torch
     from oracle import qf_oracle as O
 
     use_all_host_threads(torch)
-    cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
-    nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
+    cases = [O.make_case(M, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES for M in BATCHES]
+    nbytes = step_bytes()
 
     def one_step():
         for x, q, s, z in cases:
             O.qlinear_fp16(x, O.dequant_effective(q, s, O.effective_zero(z.numpy(), BITS)))
 
-    for _ in range(min(args.warmup, 2)):
+    warm = max(args.warmup, 0)
+    for _ in range(warm):
         one_step()
     t0 = time.perf_counter()
-    done = 0
     for _ in range(args.steps):
         one_step()
-        done += 1
-        if time.perf_counter() - t0 > 150:  # keep the arm within a few minutes
-            break
-    dt = (time.perf_counter() - t0) / done
+    dt = (time.perf_counter() - t0) / args.steps
     val = nbytes / dt / 1e9
     cores = torch.get_num_threads()
-    sample = f"4 layer shapes at M=1 per step, {done} steps timed"
+    sample = f"the 12 cases (4 layer shapes x M in 1,4,16) per step, {args.steps} steps timed after {warm} warm-up steps"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
-        "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS},
+        "config": bench_config(world),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -183,17 +200,17 @@ def cpu_baseline_sample(budget_s=12.0):
     from oracle import qf_oracle as O
 
     use_all_host_threads(torch)
-    cases = [O.make_case(1, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES]
-    nbytes = sum(algorithmic_bytes(1, N, K) for _, N, K in SHAPES)
+    cases = [O.make_case(M, N, K, BITS, GS, False, seed=0) for _, N, K in SHAPES for M in BATCHES]
+    nbytes = step_bytes()
     best, t_start, passes = float("inf"), time.perf_counter(), 0
-    while passes < 2 or (time.perf_counter() - t_start < budget_s and passes < 50):
+    while passes < 2 or (time.perf_counter() - t_start < budget_s and passes < 30):
         t0 = time.perf_counter()
         for x, q, s, z in cases:
             O.qlinear_fp16(x, O.dequant_effective(q, s, O.effective_zero(z.numpy(), BITS)))
         best = min(best, time.perf_counter() - t0)
         passes += 1
     return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"dequant + fp16 matmul of the 4 layer shapes at M=1, best of {passes} passes"}
+            "sample": f"dequant + fp16 matmul of the 12 cases (4 layer shapes x M in 1,4,16), best of {passes} passes"}
 
 
 def main():
@@ -202,11 +219,13 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--pdl", type=int, default=int(os.environ.get("QFB_BENCH_PDL", "1")),
+    ap.add_argument("--pdl", type=int, default=1,
                     help="launch with programmatic stream serialisation (weights prefetch under the previous kernel's tail)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--per-shape", type=int, default=1)
-    ap.add_argument("--decode", type=int, default=int(os.environ.get("QFB_BENCH_DECODE", "1")),
+    ap.add_argument("--extras", type=int, default=1, help="also report the bit-width sweep, the tcgen05 GEMM regime and the "
+                    "eager per-call host cost (one GPU only)")
+    ap.add_argument("--decode", type=int, default=1,
                     help="also report decode tok/s of the Llama-2-70B-architecture decoder, tensor-parallel over the ranks")
     ap.add_argument("--decode-batch", type=int, default=1)
     ap.add_argument("--case", default="", help="profiling aid: run ONE layer NxKxM a few times (4 weight replicas in "
@@ -240,8 +259,6 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     _native.lib()  # fail loudly if the native library is missing
-    if os.environ.get("QFB_TC_MIN_M"):  # tuning experiments only
-        _native.lib().qfb_set_tensor_min_batch(int(os.environ["QFB_TC_MIN_M"]))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -272,6 +289,50 @@ def main():
                           "algorithmic_bytes": algorithmic_bytes(M, N, K)}))
         return
 
+    # one layer alone: graph replay over >= 400 MB of rotating weight replicas, so that every
+    # launch streams its weights from HBM; time per launch from events around the replays
+    def time_layer(N, K, M, bits, gs, sym):
+        R = max(2, min(48, (400 << 20) // (N * K * bits // 8) + 1))
+        ls = []
+        for _ in range(R):
+            lay = "tile" if (args.layout == "fragment" and bits == 3) else args.layout  # no 3-bit fragment layout
+            L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=lay)
+            L.w.random_(-128, 127)
+            if L.s is not None:
+                L.s.uniform_(0.002, 0.02)
+            if L.z is not None:
+                L.z.view(torch.uint8).random_(0, (1 << bits) - 1)
+            L.flags = flags
+            L._prepare()
+            ls.append(L)
+        x = torch.randn(M, K, device=dev).half()
+        y = torch.empty(M, N, dtype=torch.float16, device=dev)
+        st = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(st):
+            ls[0](x, out=y)
+            torch.cuda.synchronize()
+            launch = _native.last_launch()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=st):
+                for L in ls:
+                    L(x, out=y)
+            for _ in range(3):
+                gr.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                gr.replay()
+            b.record()
+            torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (10 * R)
+        nb = algorithmic_bytes(M, N, K, bits, gs, sym)
+        del gr, ls
+        torch.cuda.empty_cache()
+        return {"N": N, "K": K, "M": M, "bits": bits, "group": gs, "sym": sym, "us": round(us, 2),
+                "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(2.0 * M * N * K / us / 1e6, 1),
+                "MB": round(nb / 1e6, 1), "kernel": launch["kernel"], "grid_x": launch["grid_x"]}
+
     if args.sweep:
         # Other sweeps of the reference, each layer alone, graph replay over >= 400 MB of rotating
         # weight replicas; one JSON line per sweep:
@@ -279,48 +340,6 @@ def main():
         #             shapes of data/nkg_shapes.json)
         #   bits      2/3/4/8-bit, asymmetric and symmetric, on (8192,8192), M = 1, group 128
         #   batch     W4 g128 on the Llama-70B MLP shapes, M = 1 .. 1024 (GEMV -> tcgen05 GEMM)
-        def time_layer(N, K, M, bits, gs, sym):
-            R = max(2, min(48, (400 << 20) // (N * K * bits // 8) + 1))
-            ls = []
-            for _ in range(R):
-                lay = "tile" if (args.layout == "fragment" and bits == 3) else args.layout  # no 3-bit fragment layout
-                L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=lay)
-                L.w.random_(-128, 127)
-                if L.s is not None:
-                    L.s.uniform_(0.002, 0.02)
-                if L.z is not None:
-                    L.z.view(torch.uint8).random_(0, (1 << bits) - 1)
-                L.flags = flags
-                L._prepare()
-                ls.append(L)
-            x = torch.randn(M, K, device=dev).half()
-            y = torch.empty(M, N, dtype=torch.float16, device=dev)
-            st = torch.cuda.Stream(device=dev)
-            with torch.cuda.stream(st):
-                ls[0](x, out=y)
-                torch.cuda.synchronize()
-                launch = _native.last_launch()
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr, stream=st):
-                    for L in ls:
-                        L(x, out=y)
-                for _ in range(3):
-                    gr.replay()
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                for _ in range(10):
-                    gr.replay()
-                b.record()
-                torch.cuda.synchronize()
-            us = a.elapsed_time(b) * 1e3 / (10 * R)
-            nb = algorithmic_bytes(M, N, K, bits, gs, sym)
-            del gr, ls
-            torch.cuda.empty_cache()
-            return {"N": N, "K": K, "M": M, "bits": bits, "group": gs, "sym": sym, "us": round(us, 2),
-                    "GBps": round(nb / us / 1e3, 1), "TFLOPs": round(2.0 * M * N * K / us / 1e6, 1),
-                    "MB": round(nb / 1e6, 1), "kernel": launch["kernel"], "grid_x": launch["grid_x"]}
-
         for name in args.sweep.split(","):
             if name == "bits":
                 rows = [time_layer(8192, 8192, 1, b, GS, sym) for b in (2, 3, 4, 8) for sym in (False, True)]
@@ -433,12 +452,22 @@ def main():
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        replay_steps(graphs, args.steps)
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
+        # a pass = the K steps of --steps between two events; passes are repeated (>= 7, until a
+        # quarter of a second of device time) and the median pass is the one reported
+        pass_ms = []
+        while len(pass_ms) < 7 or (sum(pass_ms) < 250.0 and len(pass_ms) < 200):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record()
+            replay_steps(graphs, args.steps)
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)   # every rank counts the same passes
+            pass_ms.append(float(t[0]))
+        srt = sorted(pass_ms)
+        ms = srt[len(srt) // 2]
 
         kernel_ms = {}
         for kid, gl in sub_graphs.items():
@@ -528,40 +557,139 @@ def main():
                 med = a.elapsed_time(b) / (10 * R)
                 del gr, reps_l
                 nb = algorithmic_bytes(M, N, K)
-                per_shape.append({"layer": name, "N": N, "K": K, "M": M, "us": round(med * 1e3, 2),
-                                  "GBps": round(nb / (med * 1e-3) / 1e9, 1), "launch": launch})
+                gbps = nb / (med * 1e-3) / 1e9
+                per_shape.append({"layer": name, "N": N, "K": K, "M": M, "us": round(med * 1e3, 2), "GBps": round(gbps, 1),
+                                  "frac": round(gbps / measured_peaks()[0], 3), "kernel": launch["kernel"],
+                                  "grid": [launch["grid_x"], launch["grid_y"]], "block": launch["block"]})
 
     # free the sweep's device memory before the decoder is built
     case_meta = [(M, layer.out_features, layer.in_features) for _, M, layer, *_ in cases[0]]
     del graphs, sub_graphs, cases
     torch.cuda.empty_cache()
 
+    # ---- one GPU only: the other stated configurations, each layer alone -------------------------
+    extras = {}
+    if args.extras and world == 1:
+        tpeak, tkind = measured_tensor_peak()
+        hpeak = measured_peaks()[0]
+        try:
+            # bit-width sweep on (8192,8192), M = 1, group 128, asymmetric and symmetric
+            extras["bits"] = [{"bits": r["bits"], "sym": r["sym"], "us": r["us"], "GBps": r["GBps"],
+                               "frac": round(r["GBps"] / hpeak, 3), "kernel": r["kernel"]}
+                              for r in (time_layer(8192, 8192, 1, b, GS, sym) for b in (2, 3, 4, 8) for sym in (False, True))]
+            # batch sweep on the Llama-70B MLP shapes across the GEMV -> tcgen05 GEMM boundary
+            rows = []
+            for N, K in ((28672, 8192), (8192, 28672)):
+                for M in (16, 32, 64, 128, 256, 1024):
+                    r = time_layer(N, K, M, BITS, GS, False)
+                    rows.append({"N": N, "K": K, "M": M, "us": r["us"], "GBps": r["GBps"], "TFLOPs": r["TFLOPs"],
+                                 "frac_tensor": round(r["TFLOPs"] / tpeak, 3), "frac_hbm": round(r["GBps"] / hpeak, 3),
+                                 "kernel": r["kernel"]})
+            extras["gemm"] = {"tensor_peak_TFLOPs": tpeak, "tensor_peak_kind": tkind, "rows": rows}
+            # host cost of one eager call (no graph): 400 calls of the (4096,4096) layer at M = 1 issued
+            # back to back, wall clock from the first call to the return of the last (the device is
+            # faster than the host here, so this is the per-call host time: validation, plan lookup, launch)
+            L = QLinear.empty(1, 4096, 4096, BITS, GS, sym=False, device=dev, layout=args.layout)
+            L.w.random_(-128, 127)
+            L.s.uniform_(0.002, 0.02)
+            L.z.random_(0, 15)
+            L.flags = flags
+            xe = torch.randn(1, 4096, device=dev).half()
+            ye = torch.empty(1, 4096, dtype=torch.float16, device=dev)
+            for _ in range(20):
+                L(xe, out=ye)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(400):
+                L(xe, out=ye)
+            host_s = time.perf_counter() - t0
+            torch.cuda.synchronize()
+            total_s = time.perf_counter() - t0
+            extras["eager"] = {"layer": "4096x4096 M=1", "host_us_per_call": round(host_s / 400 * 1e6, 2),
+                               "us_per_call_with_device": round(total_s / 400 * 1e6, 2)}
+            del L
+        except Exception as e:
+            extras["error"] = str(e)[:200]
+        torch.cuda.empty_cache()
+
+    # ---- tensor-parallel decoder: numeric check, then decode tokens/s -----------------------------
     # secondary figure: decode tokens/s of the random-init Llama-2-70B-architecture decoder,
     # all linears W4A16 g128, prompt 128 then 256 greedy steps, tensor-parallel over the ranks
     decode = None
     if args.decode and 8 % world == 0:
         try:
-            from qfactory.decoder import DecoderConfig, QuantDecoder, run_decode
+            from qfactory.decoder import DecoderConfig, QuantDecoder, run_decode, teacher_forced_logits, time_linears
+
+            decode = {}
+            if world > 1:
+                # the SAME seeded network, sharded over the ranks (column / row shards of one set of
+                # tensors) against the unsharded model on this GPU: 80 prompt tokens (more rows than the
+                # peer-memory kernel takes: the process group's all-reduce), then 4 single-token steps
+                # (the peer-memory kernel), same tokens fed to both
+                small = DecoderConfig(layers=2, d_model=1024, n_heads=8, n_kv_heads=8, d_ff=4096, vocab=2048, max_len=128,
+                                      scale_boost=40.0)
+                gtok = torch.Generator(device=dev).manual_seed(7)
+                toks = torch.randint(0, small.vocab, (2, 84), generator=gtok, device=dev)
+                tp_model = QuantDecoder(small, world=world, rank=rank, device=dev, seed=11, batch=2, weights="seeded")
+                got = teacher_forced_logits(tp_model, toks, prompt_len=80).float()
+                status = tp_model.comm.read_status() if tp_model.comm is not None else 0
+                coll = tp_model.collective_name()
+                tp_model.close()
+                one = QuantDecoder(small, world=1, rank=0, device=dev, seed=11, batch=2, weights="seeded")
+                want = teacher_forced_logits(one, toks, prompt_len=80).float()
+                err = torch.stack([(got - want).abs().max() / want.abs().max(), torch.tensor(float(status), device=dev)])
+                dist.all_reduce(err, op=dist.ReduceOp.MAX)
+                decode["tp_check"] = {"max_rel_err": float(err[0]), "ok": bool(float(err[0]) <= 2e-2 and float(err[1]) == 0),
+                                      "device_status": int(err[1]), "collective": coll,
+                                      "model": "2 layers, d=1024, one seeded network sharded over the ranks vs unsharded"}
+                del tp_model, one
+                torch.cuda.empty_cache()
 
             cfg = DecoderConfig()
             model = QuantDecoder(cfg, world=world, rank=rank, device=dev, batch=args.decode_batch)
-            sec, _ = run_decode(model, prompt_len=128, steps=256)
-            dt = torch.tensor([sec], dtype=torch.float64, device=dev)
+
+            def timed_decode():
+                sec, _ = run_decode(model, prompt_len=128, steps=256)
+                dt = torch.tensor([sec], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+                return float(dt[0])
+
+            sec = timed_decode()
+            decode.update({"model": "llama2-70b-architecture random init, W4A16 g128 (output projection included)",
+                           "tp": world, "batch": args.decode_batch, "prompt": 128, "steps": 256,
+                           "tok_per_s": 256 * args.decode_batch / sec, "ms_per_step": sec / 256 * 1e3,
+                           "collective": model.collective_name()})
+            if model.comm is not None:
+                decode["device_status"] = model.comm.read_status()
+            # where the step's time goes: the linears alone (the step's quantized linears replayed back to
+            # back from a graph), and the reductions (the step with every reduction left out, and, where
+            # the peer-memory kernel is in use, the step with NCCL instead)
+            decode["linears_ms_per_step"] = time_linears(model) * 1e3
             if world > 1:
-                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-            sec = float(dt[0])
-            decode = {"model": "llama2-70b-architecture random init, W4A16 g128", "tp": world, "batch": args.decode_batch,
-                      "prompt": 128, "steps": 256, "tok_per_s": 256 * args.decode_batch / sec,
-                      "ms_per_step": sec / 256 * 1e3, "collective": "nccl all_reduce after O and down" if world > 1 else "none"}
+                used = model.collective
+                model.collective = "none"
+                sec_none = timed_decode()
+                decode["allreduce_ms_per_step"] = (sec - sec_none) / 256 * 1e3
+                decode["ms_per_step_without_reductions"] = sec_none / 256 * 1e3
+                if model.comm is not None:
+                    model.collective = "nccl"
+                    sec_nccl = timed_decode()
+                    decode["nccl"] = {"tok_per_s": 256 * args.decode_batch / sec_nccl, "ms_per_step": sec_nccl / 256 * 1e3,
+                                      "allreduce_ms_per_step": (sec_nccl - sec_none) / 256 * 1e3}
+                model.collective = used
+            model.close()
             del model
             torch.cuda.empty_cache()
         except Exception as e:  # the headline line must not depend on the secondary figure
-            decode = {"error": str(e)[:200]}
+            import traceback
 
-    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+            decode = dict(decode or {}, error=(str(e) + " | " + traceback.format_exc().strip().splitlines()[-2].strip())[:300])
+
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    e2e_ms = float(t[0])
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -586,9 +714,12 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "bits": BITS, "group_size": GS, "launches_per_step": n_cases,
-                       "cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
-                       "graph": bool(args.graph), "steps_per_graph": G, "pdl": bool(args.pdl), "parallelism": f"replicas x{world}"},
+            "config": bench_config(world),
+            "protocol": {"cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
+                         "graph": bool(args.graph), "steps_per_graph": G, "pdl": bool(args.pdl), "launches_per_step": n_cases,
+                         "timed": f"{len(pass_ms)} passes of {args.steps} steps, CUDA events, max over ranks per pass; value = median pass"},
+            "spread": {"passes": len(pass_ms), "ms_per_step_min": srt[0] / args.steps, "ms_per_step_median": ms / args.steps,
+                       "ms_per_step_max": srt[-1] / args.steps},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches * world,
@@ -600,6 +731,7 @@ def main():
             "per_shape": per_shape,
             "decode": decode,
         }
+        out.update(extras)
         ratio = NCU_TRAFFIC_RATIO.get(shares[dom]["kernel"])
         if ratio:
             out["roofline"]["traffic"] = int(ratio * shares[dom]["bytes_per_step"] / shares[dom]["launches_per_step"])

@@ -65,8 +65,12 @@ typedef enum qfb_status {
 /* flags for qfb_linear_forward */
 #define QFB_FLAG_PDL 1u          /* launch with programmatic stream serialisation: the kernel
                                     prefetches weights before it waits for the preceding kernel */
-#define QFB_FLAG_FORCE_SIMT 2u   /* always use the CUDA-core split-K kernel */
-#define QFB_FLAG_FORCE_TENSOR 4u /* always use the tcgen05 kernel (if the shape allows) */
+#define QFB_FLAG_FORCE_SIMT 2u   /* never the tcgen05 kernel: tile-layout layers run the CUDA-core
+                                    split-K kernel, fragment-layout layers the mma.sync GEMV (in
+                                    passes of 16 rows), whatever the batch size */
+#define QFB_FLAG_FORCE_TENSOR 4u /* tile-layout layers: always the tcgen05 kernel (if the shape
+                                    allows); fragment-layout layers still run the mma.sync GEMV
+                                    up to 16 rows */
 #define QFB_FLAG_NO_SYNC 8u      /* qfb_linear_forward_host only: do not synchronise the stream; the
                                     caller queues several layers and synchronises once */
 
@@ -222,6 +226,9 @@ int qfb_dequantize(const qfb_layer* layer, void* w_out, void* stream);
  *                 of qkv fp16 [B, T, hq + 2 hkv, hd], in place, at positions pos i64 [T]; the rotated
  *                 keys and the values are also written into k_cache / v_cache fp16
  *                 [B, hkv, max_len, hd] at those positions.  cos, sin fp16 [max_len, hd / 2].
+ *                 A position outside [0, max_len) is skipped: no rotation and no cache write for
+ *                 that token (qfb_decode_attention clamps the same way), so a graph replayed past
+ *                 the cache length never writes out of bounds.
  * d and half are multiples of 8, hd is even; all pointers 16-byte aligned.
  */
 int qfb_rope_cache(void* qkv, const void* cos, const void* sin, const void* pos, void* k_cache, void* v_cache,
@@ -239,6 +246,52 @@ int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* strea
  */
 int qfb_decode_attention(const void* qkv, const void* pos, const void* k_cache, const void* v_cache, void* out,
                          int batch, int q_heads, int kv_heads, int head_dim, int max_len, void* stream);
+
+/*
+ * One-shot all-reduce over peer memory for the row-parallel linears (O and down projections) of a
+ * tensor-parallel decoder, fused with the residual add and the RMS norm that follow it.  Replaces
+ * the collective after a row-parallel linear in the reference's serving stack
+ * (third_party/vllm-bitblas/vllm/model_executor/layers/linear.py:1100-1124; the one-shot
+ * peer-memory kernel that stack prefers for small messages:
+ * third_party/vllm-bitblas/csrc/custom_all_reduce.cuh:133-150, 210-226).
+ *
+ * Set-up (allocates; once per process, not on the hot path): every rank calls qfb_comm_alloc,
+ * exchanges the 64-byte handle with its peers by any means (the Python side uses the process
+ * group), opens the peers' handles with qfb_comm_open and hands the `world` base pointers, by
+ * rank, to qfb_comm_create.  A rank's buffer holds a status word, per-row epochs, a flag table
+ * and two data slots of `slot_bytes`.
+ *
+ * Use: the row-parallel linear writes its fp16 partial [rows, d] into the local slot
+ * (qfb_comm_slot) and qfb_allreduce_add_rmsnorm then computes, identically on every rank,
+ *     s = fp16(sum over ranks of the slots, in rank order, fp32)
+ *     x != NULL:  x[r,:] += s (in place, one fp16 addition);  otherwise the row is s itself
+ *     w != NULL:  out[r,:] = fp16(row * rsqrt(mean(row^2) + eps)) * w;   w == NULL: out = row (if out)
+ * Consecutive reductions on a communicator MUST alternate between slot 0 and slot 1, and every
+ * rank must issue the same sequence of calls (rows, slot): that is what makes a slot safe to
+ * rewrite.  rows <= qfb_comm_max_rows(), rows * d * 2 <= slot_bytes, d % 8 == 0, d <= 16384,
+ * world in {1, 2, 4, 8}.  Peer memory is read with plain loads; no multicast.
+ *
+ * Every wait on a peer's flag is bounded (qfb_comm_set_timeout_us, default 5 s): when it runs out
+ * the kernel records it and returns normally with whatever the slots held; qfb_comm_read_status
+ * then returns QFB_ERR_DEVICE_FLAG once and clears the word.  CUDA-graph safe: flags hold epochs
+ * that only grow and live in device memory.
+ */
+typedef struct qfb_comm qfb_comm;
+size_t qfb_comm_buffer_bytes(size_t slot_bytes);
+int qfb_comm_max_rows(void);
+int qfb_comm_alloc(size_t slot_bytes, void** base_out, void* ipc_handle_out /* 64 bytes */);
+int qfb_comm_free(void* base);
+int qfb_comm_open(const void* ipc_handle, void** ptr_out);
+int qfb_comm_close(void* ptr);
+int qfb_comm_create(int rank, int world, void* const* bases, size_t slot_bytes, qfb_comm** out);
+void qfb_comm_destroy(qfb_comm* comm);
+void qfb_comm_set_timeout_us(qfb_comm* comm, unsigned microseconds);
+void* qfb_comm_slot(const qfb_comm* comm, int slot);
+size_t qfb_comm_flag_offset(int row, int source_rank);
+int qfb_allreduce_add_rmsnorm(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,
+                              float eps, void* stream);
+int qfb_comm_read_status(qfb_comm* comm, void* stream, unsigned* status_out);
+int qfb_comm_last_cuda_error(void);
 
 #ifdef __cplusplus
 }

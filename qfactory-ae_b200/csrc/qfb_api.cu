@@ -2,13 +2,34 @@
 // split-K heuristics and launches.  No entry point here allocates device memory.
 #include <algorithm>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "qfb_common.cuh"
 #include "qfb_kernels.h"
 
 namespace qfb {
 
-constexpr int kNumSMs = 148;
+constexpr int kDefaultSMs = 148;  // B200; used when no device can be asked (size queries on a machine without a GPU)
+// multiprocessors of the current device (asked once per device)
+static int num_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return kDefaultSMs;
+  }
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = kDefaultSMs;
+    }
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 constexpr size_t kCounterAlign = 256;
 constexpr int kMaxSimtRows = 8;  // activation rows one SIMT launch handles
 constexpr int kMaxMmaRows = 16;  // activation rows one mma.sync GEMV launch handles
@@ -79,7 +100,7 @@ static int make_view(const qfb_layer* L, LayerView* v) {
 
 // Upper bound of the split-K factor for a shape; sizes the workspace.
 static int split_cap(int tiles, int units) {
-  int cap = (kNumSMs * 16 + tiles - 1) / tiles;
+  int cap = (num_sms() * 16 + tiles - 1) / tiles;
   return std::max(1, std::min(cap, units));
 }
 
@@ -109,7 +130,7 @@ static TcPlan plan_tc(const LayerView& v, int m) {
     pl.nb = !pl.post ? 64 : m <= 16 ? 16 : 32;
     pl.mtiles = 1;
     const int kblocks = v.k / 128;
-    const int target = kNumSMs * ((pl.post && pl.nb <= 32 && pl.dg == 1) ? 2 : 1);
+    const int target = num_sms() * ((pl.post && pl.nb <= 32 && pl.dg == 1) ? 2 : 1);
     int split = std::max(1, target / v.tiles);
     split = std::min(split, std::max(1, kblocks / 4));
     split = std::min(split, 32);
@@ -130,9 +151,9 @@ static TcPlan plan_tc(const LayerView& v, int m) {
     pl.post = false;
     pl.nb = 64;
     for (int nb : {256, 128}) {
-      if (m >= nb && (long long)v.tiles * ((m + nb - 1) / nb) >= kNumSMs) { pl.nb = nb; break; }
+      if (m >= nb && (long long)v.tiles * ((m + nb - 1) / nb) >= num_sms()) { pl.nb = nb; break; }
     }
-    if (pl.nb == 64 && (long long)v.tiles * ((m + 127) / 128) >= kNumSMs / 2) pl.nb = 128;
+    if (pl.nb == 64 && (long long)v.tiles * ((m + 127) / 128) >= num_sms() / 2) pl.nb = 128;
     pl.mtiles = (m + pl.nb - 1) / pl.nb;
 
   }
@@ -193,10 +214,6 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   p.partial = nullptr;
   p.counters = nullptr;
   p.status = nullptr;
-  p.dbg = nullptr;
-#ifdef QFB_TC_TIMING
-  if (workspace && ws_bytes >= kHeaderBytes) p.dbg = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 16);  // header words 2..31
-#endif
   if (workspace && ws_bytes >= kHeaderBytes) p.status = static_cast<unsigned*>(workspace);
   if (pl.split > 1) {
     const size_t off = partial_offset(v.tiles);
@@ -302,11 +319,11 @@ struct MmaPlan { int nt, split, kways, cluster, recv_offset; size_t smem; };
 
 // most splits through the workspace (its size follows from this bound)
 static int mma_split_cap(int tiles, int batches) {
-  return std::max(1, std::min(batches, (kNumSMs * 4 + tiles - 1) / tiles));
+  return std::max(1, std::min(batches, (num_sms() * 4 + tiles - 1) / tiles));
 }
 // most splits inside a cluster: enough CTAs of the smallest block to fill every slot of the device once
 static int mma_cluster_split_cap(int tiles, int batches, int min_block) {
-  const int slots = kNumSMs * (mma_warps_per_sm(min_block) * 32 / min_block);
+  const int slots = num_sms() * (mma_warps_per_sm(min_block) * 32 / min_block);
   return std::max(1, std::min(std::min(batches, 8), (slots + tiles - 1) / tiles));
 }
 
@@ -328,7 +345,7 @@ static size_t mma_recv_bytes(int rows, int split) {
 // part that grows with rows x splits, reducing them through the workspace a fixed fence /
 // atomic / re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
 // inside one GPC, so a grid that fits by CTA count may still need a second wave).
-static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
+static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits) {
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
@@ -353,7 +370,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
       // through the workspace: the registers (16 or 20 warps per SM) and the shared memory bound the residency
       if (s <= cap_ws && !(g_mma_cluster == 2 && s > 1 && s <= 8)) {
         const int resident = std::max(1, std::min(mma_warps_per_sm(block) / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
-        const int waves = (tiles * s + kNumSMs * resident - 1) / (kNumSMs * resident);
+        const int waves = (tiles * s + num_sms() * resident - 1) / (num_sms() * resident);
         const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
         if (cost < best_cost) { best_cost = cost; best_s = s; best_kw = kw; best_cl = 0; }
       }
@@ -376,6 +393,26 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
   pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
   pl.recv_offset = (int)pl.smem;
   if (pl.cluster) pl.smem += mma_recv_bytes(rows, pl.split);
+  return pl;
+}
+
+// The search above asks the occupancy API and walks a few hundred candidates: its result is kept
+// per (device, shape, rows, group mode, bit width, tuning overrides), so a repeated call costs a
+// map lookup on the host.
+static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, int, int, int, int, int, int, int, int>, MmaPlan> cache;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  const auto key = std::make_tuple(dev, tiles, k, rows, (int)seg64, bits, g_tune_split, g_tune_kways, g_mma_cluster);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+  }
+  const MmaPlan pl = plan_mma_search(tiles, k, rows, seg64, bits);
+  std::lock_guard<std::mutex> lock(mu);
+  cache[key] = pl;
   return pl;
 }
 

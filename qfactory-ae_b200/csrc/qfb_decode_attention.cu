@@ -247,12 +247,21 @@ template <int G>
 cudaError_t launch_g(const __half* qkv, const __half* kc, const __half* vc, const long long* pos, __half* out, int B, int hq,
                      int hkv, int max_len, cudaStream_t st) {
   // up to 8 key splits, at least 64 keys of capacity each, no more than fill the device
-  // (more CTAs than about four per SM only add launch and merge work: measured at 16 rows)
+  // (more CTAs than about four per SM only add launch and merge work: measured at 16 rows);
+  // but never so few that the scores of a split outgrow the shared memory of a CTA
   const int by_len = std::max(1, max_len / 64), by_fill = std::max(1, (148 * 4) / std::max(1, hkv * B));
-  const int ns = std::min(8, std::min(by_len, by_fill));
-  const int chunk_max = (((max_len + ns - 1) / ns) + 7) & ~7;
-  const size_t smem = (size_t)8 * kQStride * sizeof(__half) + ((size_t)G * chunk_max + 16 + 4 * G * kHD) * sizeof(float) +
-                      (size_t)ns * G * kRecvStride * sizeof(float);
+  int ns = std::min(8, std::min(by_len, by_fill));
+  auto smem_for = [&](int nsplit, int* chunk) {
+    const int cm = (((max_len + nsplit - 1) / nsplit) + 7) & ~7;
+    if (chunk) *chunk = cm;
+    return (size_t)8 * kQStride * sizeof(__half) + ((size_t)G * cm + 16 + 4 * G * kHD) * sizeof(float) +
+           (size_t)nsplit * G * kRecvStride * sizeof(float);
+  };
+  constexpr size_t kSmemBudget = 200 * 1024;
+  while (ns < 8 && smem_for(ns, nullptr) > kSmemBudget) ++ns;
+  int chunk_max = 0;
+  const size_t smem = smem_for(ns, &chunk_max);
+  if (smem > kSmemBudget) return cudaErrorInvalidConfiguration;  // (not reachable for max_len <= 16384)
   auto kern = decode_attention_kernel<G>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

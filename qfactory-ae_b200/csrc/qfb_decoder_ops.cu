@@ -114,6 +114,9 @@ __global__ void __launch_bounds__(256) rope_cache_kernel(__half* __restrict__ qk
   const int t = (int)(r % T);
   const int b = (int)(r / T);
   const long long p = pos[t];
+  // a position outside the tables and the caches (a graph replayed past max_len, a bad caller)
+  // is skipped: no rotation, no cache write
+  if (p < 0 || p >= max_len) return;
   __half2* src = reinterpret_cast<__half2*>(qkv + (((size_t)b * T + t) * H + h) * hd) + i;
   __half2 v = *src;
   if (h < hq + hkv) {

@@ -35,32 +35,12 @@ namespace qfb {
 
 using namespace ptx;
 
-// Optional per-role cycle accounting for CTA (0,0,0), compiled in with -DQFB_TC_TIMING.
-#ifdef QFB_TC_TIMING
-#define TT_DECL(n) long long tt_[n] = {}; long long tt_t0_ = 0; (void)tt_t0_
-#define TT_START() (tt_t0_ = clock64())
-#define TT_ADD(i) do { const long long tt_now_ = clock64(); tt_[i] += tt_now_ - tt_t0_; tt_t0_ = tt_now_; } while (0)
-#define TT_DUMP(base, n) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) for (int ti_ = 0; ti_ < n; ++ti_) p.dbg[(base) + ti_] = tt_[ti_]; } while (0)
-#else
-#define TT_DECL(n)
-#define TT_START()
-#define TT_ADD(i)
-#define TT_DUMP(base, n)
-#endif
-
 constexpr int kStageK = 128;              // k per pipeline stage
 constexpr int kStepsPerStage = kStageK / 16;
 constexpr int kAColsPerSlot = kStageK / 2;  // one 32-bit column holds two fp16 k
 constexpr int kDecodeWarps = 8;
 // sleep between polls of a barrier that is not ready yet, per role (ns)
-#ifndef QFB_SLEEP_SCALE
-#define QFB_SLEEP_SCALE 100
-#define QFB_SLEEP_PRODUCER 100
-#define QFB_SLEEP_MMA 20
-#define QFB_SLEEP_DECODE 20
-#endif
-constexpr unsigned kSleepScale = QFB_SLEEP_SCALE, kSleepProducer = QFB_SLEEP_PRODUCER, kSleepMma = QFB_SLEEP_MMA,
-                   kSleepDecode = QFB_SLEEP_DECODE;
+constexpr unsigned kSleepScale = 100, kSleepProducer = 100, kSleepMma = 20, kSleepDecode = 20;
 
 // DG = decode groups: 1 -> 8 decode warps (512 threads, two CTAs per SM for the smallest batch
 // tile), 2 -> two groups of 8 decode warps that take alternate stages (768 threads, one CTA per SM).
@@ -307,11 +287,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       int g0 = (kb0 * 2) / hpg, gpos = (kb0 * 2) % hpg;
       const uint32_t ng = hpg == 1 ? 2u : 1u;
       const uint32_t zb = has_z ? ng * 128u : 0u, sb = (!POST && has_s) ? ng * 256u : 0u;
-      TT_DECL(2);
-      TT_START();
       for (int i = 0; i < nkb; ++i) {
         if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp, kSleepProducer)) break;
-        TT_ADD(0);
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
         mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
@@ -330,9 +307,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         gpos += 2;
         if (hpg == 1) { g0 += 2; gpos = 0; } else if (gpos >= hpg) { gpos = 0; ++g0; }
         if (++s == NS) { s = 0; ph ^= 1; }
-        TT_ADD(1);
       }
-      TT_DUMP(0, 2);
     }
     __syncwarp();
   } else if (warp == 3) {
@@ -360,18 +335,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_f16_m128(NB);
       const int e = (warp == 1) ? 0 : 1;
-      TT_DECL(5);
-      TT_START();
       for (int i = e; i < nkb; i += Cfg::kIssuers) {
         const int xs = i % NX, r = i % R;
         const uint32_t phx = (uint32_t)(i / NX) & 1u, phr = (uint32_t)(i / R) & 1u;
         if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp, kSleepMma)) break;
-        TT_ADD(0);
         if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp, kSleepMma)) break;
-        TT_ADD(1);
         if (POST) {
           if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp, kSleepMma)) break;
-          TT_ADD(3);
         }
         tc_fence_after();
         const uint32_t a_tmem = tmem_base + r * kAColsPerSlot;
@@ -381,10 +351,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         mma_f16_ts_stage8(d_tmem, a_tmem, (uint32_t)bd0, (uint32_t)bd1, (uint32_t)(bd0 >> 32), idesc,
                           POST ? 0u : (i >= Cfg::kIssuers ? 1u : 0u));
         mma_commit(smem_u32(&bar_done[r]));
-        TT_ADD(2);
       }
       mma_commit(smem_u32(&bar_final));  // every MMA this thread issued is complete
-      if (e == 0) { TT_DUMP(8, 5); }
     }
     __syncwarp();
   } else if (warp >= 4 && warp < Cfg::kScaleWarp0) {
@@ -399,14 +367,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     const bool frag = BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT;
     // position of the row's scale / zero inside the tile's 128 (fragment layers keep them in fragment order)
     const int qrow = qsel + (frag ? frag_pos_of_row(row) : row);
-    TT_DECL(6);
-    TT_START();
     for (int i = grp; i < nkb; i += DG) {
       // ring positions and phases of stage i (NS, R, NX are compile-time constants: multiply-shift, no division)
       const int s = i % NS, r = i % R;
       const uint32_t phs = (uint32_t)(i / NS) & 1u, phr = ((uint32_t)(i / R) & 1u) ^ 1u;
       if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode)) break;
-      TT_ADD(0);
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qrow] : p.zconst;
       __half2 d[32];
       if (BITS != 3 && frag) StageDecodeFragment<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
@@ -423,28 +388,23 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       // the packed stage is in registers: hand the shared-memory slot back to the producer
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
-      TT_ADD(1);
       // slot r was last read by the MMAs of stage i - R
       if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepDecode)) break;
       // ... and the activation tile of that stage is free as well: tell its producer.  The
       // decode warps cannot fall behind the commits (the MMAs need their stores), so this
       // relay never misses a phase; R <= NX makes it reach every tile that is still needed.
       if (i >= R && (warp & 7) == 4 && lane == 0) mbar_arrive(smem_u32(&bar_xempty[(i - R) % NX]));
-      TT_ADD(3);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + r * kAColsPerSlot + h * 32;
       tmem_st_x16(taddr, reinterpret_cast<const uint32_t(&)[16]>(rr[0]));
       tmem_st_x16(taddr + 16, reinterpret_cast<const uint32_t(&)[16]>(rr[16]));
-      TT_ADD(4);
       // publish at once: the MMAs of this stage start a whole decode earlier than with a deferred
       // hand-off, which matters more than the store latency exposed here (measured)
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_afull[r]));
-      TT_ADD(5);
     }
-    if (warp == 4 && lane == 0) { TT_DUMP(16, 6); }
   } else if (warp >= Cfg::kScaleWarp0) {
     // ------------------------------ scale / epilogue warps --------------------
     const int q = warp & 3;
@@ -475,8 +435,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       const int stages_per_group = p.halfstages_per_group >> 1;  // POST needs groups of whole stages
       int r = 0;
       uint32_t phr = 0;
-      TT_DECL(3);
-      TT_START();
       // scales are fetched two stages ahead of their use
       // group of stage kb0 + j, advanced without divisions: (gq, gr) = divmod(kb0 + j, stages_per_group)
       int gq = (kb0 + 2) / stages_per_group, gr = (kb0 + 2) % stages_per_group;
@@ -489,9 +447,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         sc0 = sc1;
         sc1 = scale_at(i + 2, gq);
         if (++gr == stages_per_group) { gr = 0; ++gq; }
-        TT_ADD(0);
         if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepScale)) { ok = false; break; }
-        TT_ADD(1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase + r * NB;
         constexpr int CH = NB < 32 ? NB : 32;  // columns read back per wait
@@ -501,20 +457,16 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 #pragma unroll
           for (int c = 0; c < CH; c += 16) tmem_ld_x16(taddr + c0 + c, reinterpret_cast<uint32_t(&)[16]>(v[c]));
           tmem_wait_ld();
-          TT_ADD(2);
           if (c0 + CH == NB) {  // the accumulator is free as soon as its last chunk is in registers
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_dempty[r]));
           }
-          TT_ADD(3);
 #pragma unroll
           for (int j = 0; j < CH; ++j) acc[c0 + j] = fmaf(sval, __uint_as_float(v[j]), acc[c0 + j]);
         }
         if (++r == R) { r = 0; phr ^= 1; }
-        TT_ADD(4);
       }
-      if (warp == Cfg::kScaleWarp0 && lane == 0) { TT_DUMP(24, 5); }
       if (ok) {
         grid_dependency_wait();  // y and the workspace may still be in use by the preceding kernel
 #pragma unroll
@@ -596,12 +548,9 @@ template <int BITS, int NB, bool POST, int DG>
 static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
   auto kern = qgemm_tc_kernel<BITS, NB, POST, DG>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  // the attribute belongs to the (function, device) pair: set it on every launch, it is cheap
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(Cfg::kThreads);

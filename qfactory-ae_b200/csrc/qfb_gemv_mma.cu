@@ -86,17 +86,6 @@ __device__ __forceinline__ void mma_m16n8k16_zero(float (&d)[4], const uint32_t 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-// Development builds only (-DQFB_MMA_STOP_AFTER=n): leave the kernel after phase n, to measure the
-// phases one by one.  0 = the whole kernel.
-#ifndef QFB_MMA_STOP_AFTER
-#define QFB_MMA_STOP_AFTER 0
-#endif
-// 1: one bulk (TMA) copy per activation row, issued by the lanes of warp 0; 0: 16-byte
-// asynchronous copies issued by every thread
-#ifndef QFB_MMA_BULK_STAGE
-#define QFB_MMA_BULK_STAGE 1
-#endif
-
 // the words of one lane and k-step a warp holds: 4 (16 bytes), 2 or 1
 template <int NW> struct Words;
 // load_if keeps the predicate inside the instruction (no branch around the load), so that the
@@ -226,7 +215,6 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   // ---- stage the CTA's activation slice ------------------------------------------------------
   const int xstride = p.batches_per_cta * 128 + 16;  // halfs; +16 keeps the fragment loads conflict-free
   __half* x_s = reinterpret_cast<__half*>(smem);
-#if QFB_MMA_BULK_STAGE
   // one bulk copy per row (256 bytes per batch: sizes and both addresses are multiples of 16),
   // lane r of warp 0 issues row r; warp 0 waits for the bytes, the barrier below publishes them
   __shared__ __align__(8) uint64_t xbar;
@@ -247,19 +235,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     // bounded: a copy that never lands raises the status word instead of hanging the CTA
     if (!ptx::mbar_wait(bar, 0, &xabort) && lane == 0 && p.status) atomicExch(p.status, 1u);
   }
-#else
-  {
-    const int nvec_row = ncta * 16;
-    for (int m = 0; m < p.m; ++m) {
-      const __half* src = p.x + (size_t)m * p.k + (size_t)bb * 128;
-      __half* dst = x_s + (size_t)m * xstride;
-      for (int j = tid; j < nvec_row; j += blockDim.x) cp_async_16(dst + j * 8, src + j * 8);
-    }
-    cp_async_commit_wait_all();
-  }
-#endif
   __syncthreads();
-  if (QFB_MMA_STOP_AFTER == 2) return;
 
   // activation row each batch tile of this thread reads (rows >= m repeat the last valid row;
   // their output columns are never stored)
@@ -306,7 +282,6 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     }
   }
   __syncthreads();
-  if (QFB_MMA_STOP_AFTER == 3) return;
 
   float acc[RB][NT][4];
 #pragma unroll
@@ -391,18 +366,6 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     }
   }
 
-  if (QFB_MMA_STOP_AFTER == 4) {  // keep the results alive without storing them
-    float sum = 0.f;
-#pragma unroll
-    for (int rb = 0; rb < RB; ++rb)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sum += acc[rb][nt][i];
-    if (sum == 12345.678f) p.y[0] = __float2half_rn(sum);
-    return;
-  }
-
   // ---- combine the k-ways of the CTA ----------------------------------------------------
   __syncthreads();  // everyone is done reading the staged activations
   float* red = reinterpret_cast<float*>(smem);
@@ -417,7 +380,6 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
         if (mm < p.m) red[(kw * p.m + mm) * kRedStride + r] = acc[rb][nt][i];
       }
   __syncthreads();
-  if (QFB_MMA_STOP_AFTER == 5) return;
 
   // From here on the outputs of the tile are handled as quads: four consecutive rows of one
   // batch column (quad q: column q / 32, rows 4 * (q % 32) ...), 16-byte shared-memory accesses.

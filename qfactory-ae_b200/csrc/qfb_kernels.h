@@ -71,14 +71,13 @@ struct TcParams {
   float* partial;        // [S, m, npad] split-K partial sums
   unsigned* counters;    // [m tiles, n tiles] arrival counters, zero between launches
   unsigned* status;      // set to 1 when a bounded wait ran out
-  long long* dbg;        // optional cycle counters (timing builds only)
   int m, n, k, npad;
   int groups;
   int kblocks;               // K / 128 pipeline stages
   int steps_per_group;       // group_size / 16 MMA k-steps per quantisation group (K / 16 when group-less)
   int halfstages_per_group;  // group_size / 64
   uint32_t zconst;
-  int layout;                // QFB_LAYOUT_TILE, or QFB_LAYOUT_FRAGMENT (4-bit only)
+  int layout;                // QFB_LAYOUT_TILE, or QFB_LAYOUT_FRAGMENT (2-, 4- and 8-bit)
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
 cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,

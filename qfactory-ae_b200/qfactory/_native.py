@@ -28,6 +28,9 @@ EXPORTS = (
     "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
     "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention",
+    "qfb_comm_buffer_bytes", "qfb_comm_max_rows", "qfb_comm_alloc", "qfb_comm_free", "qfb_comm_open", "qfb_comm_close",
+    "qfb_comm_create", "qfb_comm_destroy", "qfb_comm_set_timeout_us", "qfb_comm_slot", "qfb_comm_flag_offset",
+    "qfb_allreduce_add_rmsnorm", "qfb_comm_read_status", "qfb_comm_last_cuda_error",
 )
 
 
@@ -122,6 +125,32 @@ def lib() -> ctypes.CDLL:
     L.qfb_quantize.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.qfb_silu_mul.restype = i32
     L.qfb_silu_mul.argtypes = [vp, vp, i32, i32, vp]
+    L.qfb_comm_buffer_bytes.restype = sz
+    L.qfb_comm_buffer_bytes.argtypes = [sz]
+    L.qfb_comm_max_rows.restype = i32
+    L.qfb_comm_alloc.restype = i32
+    L.qfb_comm_alloc.argtypes = [sz, ctypes.POINTER(vp), vp]
+    L.qfb_comm_free.restype = i32
+    L.qfb_comm_free.argtypes = [vp]
+    L.qfb_comm_open.restype = i32
+    L.qfb_comm_open.argtypes = [vp, ctypes.POINTER(vp)]
+    L.qfb_comm_close.restype = i32
+    L.qfb_comm_close.argtypes = [vp]
+    L.qfb_comm_create.restype = i32
+    L.qfb_comm_create.argtypes = [i32, i32, ctypes.POINTER(vp), sz, ctypes.POINTER(vp)]
+    L.qfb_comm_destroy.restype = None
+    L.qfb_comm_destroy.argtypes = [vp]
+    L.qfb_comm_set_timeout_us.restype = None
+    L.qfb_comm_set_timeout_us.argtypes = [vp, u32]
+    L.qfb_comm_slot.restype = vp
+    L.qfb_comm_slot.argtypes = [vp, i32]
+    L.qfb_comm_flag_offset.restype = sz
+    L.qfb_comm_flag_offset.argtypes = [i32, i32]
+    L.qfb_allreduce_add_rmsnorm.restype = i32
+    L.qfb_allreduce_add_rmsnorm.argtypes = [vp, i32, vp, vp, vp, i32, i32, ctypes.c_float, vp]
+    L.qfb_comm_read_status.restype = i32
+    L.qfb_comm_read_status.argtypes = [vp, vp, ctypes.POINTER(u32)]
+    L.qfb_comm_last_cuda_error.restype = i32
     _lib = L
     return L
 
@@ -138,3 +167,11 @@ def last_launch() -> dict:
     v = [ctypes.c_int(0) for _ in range(5)]
     lib().qfb_get_last_launch(*[ctypes.byref(x) for x in v])
     return dict(zip(("kernel", "grid_x", "grid_y", "block", "smem"), (x.value for x in v)))
+
+
+def version_or_zero() -> int:
+    """`qfb_version()` of the built library, 0 when it has not been built (state_dict tags only)."""
+    try:
+        return int(lib().qfb_version())
+    except NativeError:
+        return 0

@@ -1,0 +1,162 @@
+"""Peer-memory communicator of the tensor-parallel decoder: one symmetric buffer per rank, mapped
+into every peer, and the fused `all-reduce + residual add + RMS norm` kernel that runs on it
+(C ABI: the qfb_comm_* entry points of include/qfactory_b200.h).
+
+It takes the place of the collective call after a row-parallel linear in the reference's serving
+stack (reference: third_party/vllm-bitblas/vllm/model_executor/layers/linear.py:1100-1124) for the
+small messages of a decode step, as that stack's own one-shot kernel does (reference:
+third_party/vllm-bitblas/vllm/distributed/device_communicators/custom_all_reduce.py:242-255).
+Larger messages (a prefill) stay on the process group's all-reduce.
+
+The buffers are exchanged as CUDA IPC handles over the process group at construction; after that
+no host communication is involved and the kernels are CUDA-graph safe.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+
+
+class _DevView:
+    """A device address exposed through the CUDA array interface, so that torch can alias it."""
+
+    def __init__(self, ptr, shape, owner):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f2", "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+        self._owner = owner
+
+
+class PeerComm:
+    """`world` symmetric buffers with two data slots of `slot_rows x d` fp16 each.
+
+    `PeerComm.from_process_group(d, slot_rows, group)` builds one over the ranks of a process group
+    (one process per GPU of one node).  `PeerComm.local_emulation(...)` builds the `world` buffers
+    of all ranks inside ONE process on one GPU, for tests that play a peer's part by hand.
+    """
+
+    def __init__(self, rank, world, bases, d, slot_rows, device, owned=None, opened=()):
+        L = _native.lib()
+        self._lib, self.rank, self.world, self.d, self.device = L, rank, world, d, device
+        self.slot_rows = min(slot_rows, L.qfb_comm_max_rows())
+        self.slot_bytes = self.slot_rows * d * 2
+        self.bases = list(bases)
+        self._owned, self._opened = owned, list(opened)
+        arr = (ctypes.c_void_p * world)(*self.bases)
+        h = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _native.check(L.qfb_comm_create(rank, world, arr, self.slot_bytes, ctypes.byref(h)), "qfb_comm_create")
+        self._h = h
+        self._slots = [torch.as_tensor(_DevView(L.qfb_comm_slot(h, s), (self.slot_rows, d), self), device=device)
+                       for s in (0, 1)]
+        self._next = 0
+
+    # -- construction -----------------------------------------------------------
+    @staticmethod
+    def _alloc(slot_bytes, device):
+        L = _native.lib()
+        base, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            _native.check(L.qfb_comm_alloc(slot_bytes, ctypes.byref(base), handle), "qfb_comm_alloc")
+        return base.value, handle.raw
+
+    @classmethod
+    def from_process_group(cls, d, slot_rows, device, group=None):
+        L = _native.lib()
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        slot_rows = min(slot_rows, L.qfb_comm_max_rows())
+        base, handle = cls._alloc(slot_rows * d * 2, device)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        bases, opened = [], []
+        with torch.cuda.device(device):
+            for r in range(world):
+                if r == rank:
+                    bases.append(base)
+                    continue
+                p = ctypes.c_void_p()
+                _native.check(L.qfb_comm_open(handles[r], ctypes.byref(p)), f"qfb_comm_open(rank {r})")
+                bases.append(p.value)
+                opened.append(p.value)
+        comm = cls(rank, world, bases, d, slot_rows, device, owned=base, opened=opened)
+        dist.barrier(group)   # every rank has mapped every buffer before anyone raises a flag
+        return comm
+
+    @classmethod
+    def local_emulation(cls, rank, world, d, slot_rows, device="cuda"):
+        """All `world` buffers allocated by this process on one GPU; returns the communicator of
+        `rank`.  `peer_slot(r, slot)` and `raise_flag(...)` let a test write a peer's partial and
+        raise its flag before the kernel is launched (the kernel of a second rank is never run
+        beside this one on the same GPU: kernels that wait on one another must not share a GPU)."""
+        L = _native.lib()
+        device = torch.device(device)
+        slot_rows = min(slot_rows, L.qfb_comm_max_rows())
+        bases = [cls._alloc(slot_rows * d * 2, device)[0] for _ in range(world)]
+        comm = cls(rank, world, bases, d, slot_rows, device, owned=None, opened=())
+        comm._emulated = bases
+        return comm
+
+    # -- use ----------------------------------------------------------------------
+    def slot(self, which: int, rows: int) -> torch.Tensor:
+        """fp16 [rows, d] view of the local data slot `which` (the row-parallel linear's `out=`)."""
+        return self._slots[which][:rows]
+
+    def next_slot(self) -> int:
+        """Slots must alternate between consecutive reductions; this hands out 0, 1, 0, ..."""
+        s = self._next
+        self._next ^= 1
+        return s
+
+    def fits(self, rows: int, d: int) -> bool:
+        return d == self.d and 0 < rows <= self.slot_rows
+
+    def allreduce_add_rmsnorm(self, which, x, weight, rows, eps=1e-5, out=None):
+        """Sum slot `which` over the ranks; `x` (fp16 [rows, d], may be None) += the sum in place;
+        returns the RMS norm of the row with `weight` (or the row itself when `weight` is None)."""
+        if out is None:
+            out = torch.empty(rows, self.d, dtype=torch.float16, device=self.device)
+        st = self._lib.qfb_allreduce_add_rmsnorm(
+            self._h, which, None if x is None else x.data_ptr(), None if weight is None else weight.data_ptr(),
+            out.data_ptr(), rows, self.d, eps, torch.cuda.current_stream(self.device).cuda_stream)
+        if st != 0:
+            _native.check(st, "qfb_allreduce_add_rmsnorm")
+        return out
+
+    def set_timeout_us(self, us: int) -> None:
+        self._lib.qfb_comm_set_timeout_us(self._h, us)
+
+    def read_status(self) -> int:
+        """0, or 8 (QFB_ERR_DEVICE_FLAG) once after a wait on a peer's flag ran out."""
+        st = ctypes.c_uint(0)
+        return self._lib.qfb_comm_read_status(self._h, torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(st))
+
+    # -- emulation helpers (tests) ---------------------------------------------------
+    def peer_slot(self, r: int, which: int, rows: int) -> torch.Tensor:
+        off = self._lib.qfb_comm_slot(self._h, which) - self.bases[self.rank]
+        return torch.as_tensor(_DevView(self.bases[r] + off, (self.slot_rows, self.d), self), device=self.device)[:rows]
+
+    def raise_flag(self, row: int, source_rank: int, epoch: int) -> None:
+        """Store `epoch` into this rank's flag (row, source_rank), as peer `source_rank` would."""
+        off = self._lib.qfb_comm_flag_offset(row, source_rank)
+        v = _DevView(self.bases[self.rank] + off, (2,), self)   # two halfs = the 32-bit flag
+        t = torch.as_tensor(v, device=self.device).view(torch.int32)
+        t.fill_(epoch)
+
+    def close(self):
+        L = self._lib
+        if self._h:
+            L.qfb_comm_destroy(self._h)
+            self._h = None
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                L.qfb_comm_close(p)
+            self._opened = []
+            if self._owned:
+                L.qfb_comm_free(self._owned)
+                self._owned = None
+            for p in getattr(self, "_emulated", []):
+                L.qfb_comm_free(p)
+            self._emulated = []

@@ -5,12 +5,21 @@ Llama-2-70B architecture (80 layers, d = 8192, 64 query heads / 8 KV heads, FFN 
 vocab 32000), every linear W4A16 g128.  The sharding follows the reference's serve path
 (reference: third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-285 with
 layers/linear.py:382-394, 1100-1124): fused QKV and gate+up are column-parallel (no
-collective), O and down are row-parallel followed by ONE all-reduce each.  RMSNorm, SiLU * up and
-RoPE with the cache write are one native launch each (ops.py; `native_ops=False` keeps the plain
-torch expressions, which the tests compare against); attention is torch's SDPA.
+collective), O and down are row-parallel followed by ONE all-reduce each.  RMSNorm, SiLU * up,
+RoPE with the cache write and the single-token attention are one native launch each (ops.py;
+`native_ops=False` keeps the plain torch expressions, which the tests compare against); the
+prefill's attention is torch's SDPA.
 
-Weights are random packed bytes generated on the device (the reference's own end-to-end
-runs also used uninitialised weights, third_party/vllm-qfactory.patch:223-228).
+The all-reduce of a decode step (at most 64 rows) is the library's one-shot peer-memory kernel,
+fused with the residual add and the RMS norm that follow it (comm.py): the row-parallel linear
+writes its partial into the communicator's slot, one launch does the rest.  Larger row counts (a
+prefill) use the process group's all-reduce (NCCL), as does everything when `collective='nccl'`.
+
+Weights: `weights='packed'` draws random packed bytes on the device (the reference's own
+end-to-end runs also used uninitialised weights, third_party/vllm-qfactory.patch:223-228);
+`weights='seeded'` draws ONE set of codes / scales / zeros from the seed, the same on every rank,
+and each rank packs its column or row shard of it (parallel.py), so that a tensor-parallel model
+is the same network as the single-GPU one and their outputs can be compared.
 """
 from __future__ import annotations
 
@@ -20,7 +29,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native, ops
-from .parallel import all_reduce_sum
+from .parallel import all_reduce_sum, shard_columns, shard_rows
 from .qlinear import QLinear
 
 
@@ -36,49 +45,106 @@ class DecoderConfig:
     group_size: int = 128
     max_len: int = 512
     rope_theta: float = 10000.0
+    scale_boost: float = 1.0   # multiplies the (small) random scales: >1 makes the linears matter in numeric checks
 
     @property
     def head_dim(self):
         return self.d_model // self.n_heads
 
 
-def _random_layer(K, N, bits, gs, device, gen, batch=1):
+def _random_layer(K, N, bits, gs, device, gen, batch=1, boost=1.0):
     # the batch the decoder is built for picks the packed layout (fragment up to 16 rows)
     L = QLinear.empty(batch, K, N, bits, gs, sym=False, device=device)
     L.w.copy_(torch.randint(-128, 128, L.w.shape, generator=gen, dtype=torch.int8, device=device))
     # small scales keep the residual stream of a random-weight network finite
-    L.s.copy_((torch.rand(L.s.shape, generator=gen, device=device) * 2e-4 + 1e-4).half())
+    L.s.copy_(((torch.rand(L.s.shape, generator=gen, device=device) * 2e-4 + 1e-4) * boost).half())
     L.z.copy_(torch.randint(7, 10, L.z.shape, generator=gen, dtype=torch.int8, device=device))
     # programmatic dependent launch: the layer's weight prefetch overlaps the tail of whatever ran before
     L.flags = _native.FLAG_PDL
     return L
 
 
+def seeded_tensors(K, N, bits, gs, gen, device, boost=1.0):
+    """Codes [K,N], scales [K/gs,N], GPTQ-convention zeros [K/gs,N] of one full (unsharded) linear,
+    drawn on `device` from `gen`; the distributions keep the residual stream of a random network finite."""
+    q = torch.randint(0, 1 << bits, (K, N), generator=gen, dtype=torch.int32, device=device)
+    s = ((torch.rand(K // gs, N, generator=gen, device=device) * 2e-4 + 1e-4) * boost).half()
+    z = torch.randint((1 << bits) // 2 - 2, (1 << bits) // 2 + 1, (K // gs, N), generator=gen, dtype=torch.int32, device=device)
+    return q, s, z
+
+
+def _packed(K, N, cfg, parts, batch):
+    """QLinear of the column-wise concatenation of (codes, scales, zeros) parts."""
+    q = torch.cat([p[0] for p in parts], dim=1)
+    s = torch.cat([p[1] for p in parts], dim=1)
+    z = torch.cat([p[2] for p in parts], dim=1)
+    L = QLinear.init(batch, K, N, cfg.bits, q, cfg.group_size, s, z)
+    L.flags = _native.FLAG_PDL
+    return L
+
+
 class DecoderLayer(torch.nn.Module):
-    def __init__(self, cfg: DecoderConfig, world: int, device, gen, batch: int = 1):
+    def __init__(self, cfg: DecoderConfig, world: int, device, gen, batch: int = 1, weights: str = "packed", rank: int = 0):
         super().__init__()
         d, hd = cfg.d_model, cfg.head_dim
         self.hq, self.hkv, self.hd = cfg.n_heads // world, cfg.n_kv_heads // world, hd
-        self.qkv = _random_layer(d, (self.hq + 2 * self.hkv) * hd, cfg.bits, cfg.group_size, device, gen, batch)   # column parallel
-        self.o = _random_layer(self.hq * hd, d, cfg.bits, cfg.group_size, device, gen, batch)                       # row parallel
-        self.gate_up = _random_layer(d, 2 * cfg.d_ff // world, cfg.bits, cfg.group_size, device, gen, batch)        # column parallel
-        self.down = _random_layer(cfg.d_ff // world, d, cfg.bits, cfg.group_size, device, gen, batch)               # row parallel
+        nq, nkv, ff = cfg.n_heads * hd, cfg.n_kv_heads * hd, cfg.d_ff
+        if weights == "packed":
+            self.qkv = _random_layer(d, (self.hq + 2 * self.hkv) * hd, cfg.bits, cfg.group_size, device, gen, batch, cfg.scale_boost)   # column parallel
+            self.o = _random_layer(self.hq * hd, d, cfg.bits, cfg.group_size, device, gen, batch, cfg.scale_boost)                       # row parallel
+            self.gate_up = _random_layer(d, 2 * cfg.d_ff // world, cfg.bits, cfg.group_size, device, gen, batch, cfg.scale_boost)        # column parallel
+            self.down = _random_layer(cfg.d_ff // world, d, cfg.bits, cfg.group_size, device, gen, batch, cfg.scale_boost)               # row parallel
+        else:
+            # the full tensors of the layer, identical on every rank; this rank keeps its shards:
+            # the query / key / value (gate / up) column shards are fused, O and down are split along K
+            T = lambda K, N: seeded_tensors(K, N, cfg.bits, cfg.group_size, gen, device, cfg.scale_boost)
+            col = lambda t: shard_columns(*t, rank, world)
+            row = lambda t: shard_rows(*t, rank, world, cfg.group_size)
+            full = {}
+            for name, (K_, N_) in (("q", (d, nq)), ("k", (d, nkv)), ("v", (d, nkv)), ("o", (nq, d)), ("gate", (d, ff)),
+                                   ("up", (d, ff)), ("down", (ff, d))):
+                full[name] = T(K_, N_)     # drawn in this fixed order on every rank
+            tq, tk, tv, to, tg, tu, td = (full[n] for n in ("q", "k", "v", "o", "gate", "up", "down"))
+            self.full = full if weights == "seeded_keep" else None
+            self.qkv = _packed(d, (self.hq + 2 * self.hkv) * hd, cfg, [col(tq), col(tk), col(tv)], batch)
+            self.o = _packed(nq // world, d, cfg, [row(to)], batch)
+            self.gate_up = _packed(d, 2 * ff // world, cfg, [col(tg), col(tu)], batch)
+            self.down = _packed(ff // world, d, cfg, [row(td)], batch)
         self.norm1 = torch.nn.Parameter(torch.ones(d, dtype=torch.float16, device=device), requires_grad=False)
         self.norm2 = torch.nn.Parameter(torch.ones(d, dtype=torch.float16, device=device), requires_grad=False)
 
 
 class QuantDecoder(torch.nn.Module):
+    """`collective`: 'auto' (the peer-memory kernel for decode steps when a process group with more
+    than one rank exists, NCCL otherwise), 'nccl' (the process group's all-reduce everywhere) or
+    'none' (no reduction at all: an ablation for timing, the outputs are then wrong for world > 1).
+    `weights`: 'packed' | 'seeded' | 'seeded_keep' (as 'seeded', and the layers keep the full tensors
+    in `.full` for reference computations)."""
+
     def __init__(self, cfg: DecoderConfig, world: int = 1, rank: int = 0, device="cuda", seed: int = 0, batch: int = 1,
-                 native_ops: bool = True):
+                 native_ops: bool = True, weights: str = "packed", collective: str = "auto"):
         super().__init__()
         self.native_ops = native_ops
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
+        assert weights in ("packed", "seeded", "seeded_keep") and collective in ("auto", "nccl", "none")
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
-        gen = torch.Generator(device=device).manual_seed(seed * 1000 + rank)
-        self.blocks = torch.nn.ModuleList([DecoderLayer(cfg, world, device, gen, batch) for _ in range(cfg.layers)])
+        self.collective = collective
+        # packed bytes differ per rank (they are that rank's shard of some network); seeded tensors
+        # are the whole network, drawn identically everywhere
+        gen = torch.Generator(device=device).manual_seed(seed * 1000 + (rank if weights == "packed" else 0))
+        self.blocks = torch.nn.ModuleList([DecoderLayer(cfg, world, device, gen, batch, weights, rank) for _ in range(cfg.layers)])
         g0 = torch.Generator(device=device).manual_seed(seed)  # replicated tensors: same on every rank
         self.embed = (torch.randn(cfg.vocab, cfg.d_model, generator=g0, device=device) * 0.02).half()
-        self.lm_head = (torch.randn(cfg.d_model, cfg.vocab, generator=g0, device=device) * 0.02).half()
+        # the output projection is a quantized linear like the others (replicated: 0.13 GB at 4 bits)
+        if weights == "packed":
+            self.lm_head = _random_layer(cfg.d_model, cfg.vocab, cfg.bits, cfg.group_size, device, g0, batch)
+            self.lm_head.s.mul_(100.0)
+            self.lm_head_full = None
+        else:
+            t = seeded_tensors(cfg.d_model, cfg.vocab, cfg.bits, cfg.group_size, g0, device)
+            t = (t[0], (t[1].float() * 100.0).half(), t[2])
+            self.lm_head = _packed(cfg.d_model, cfg.vocab, cfg, [t], batch)
+            self.lm_head_full = t if weights == "seeded_keep" else None
         self.final_norm = torch.ones(cfg.d_model, dtype=torch.float16, device=device)
         hd = cfg.head_dim
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=device).float() / hd))
@@ -87,6 +153,37 @@ class QuantDecoder(torch.nn.Module):
         hkv = cfg.n_kv_heads // world
         self.k_cache = torch.zeros(cfg.layers, batch, hkv, cfg.max_len, hd, dtype=torch.float16, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
+        # peer-memory communicator for the reductions of a decode step
+        self.comm, self.comm_error = None, None
+        if world > 1 and collective == "auto":
+            import torch.distributed as dist
+
+            if dist.is_available() and dist.is_initialized():
+                try:
+                    from .comm import PeerComm
+
+                    self.comm = PeerComm.from_process_group(cfg.d_model, 64, torch.device(device))
+                except Exception as e:  # peers not mappable (no peer access, IPC closed): NCCL serves every reduction
+                    self.comm_error = str(e)[:160]
+                # all ranks must agree, or their call sequences diverge
+                ok = torch.tensor([1 if self.comm is not None else 0], device=device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if int(ok[0]) == 0 and self.comm is not None:
+                    self.comm.close()
+                    self.comm, self.comm_error = None, "a peer could not map the buffers"
+
+    def collective_name(self):
+        if self.world == 1:
+            return "none"
+        if self.collective == "none":
+            return "none (ablation)"
+        if self.comm is not None:
+            return "one-shot peer-memory all-reduce fused with add + rmsnorm (decode), nccl (prefill)"
+        return "nccl all_reduce after O and down" + (f" (peer setup failed: {self.comm_error})" if self.comm_error else "")
+
+    def _reduce(self, t):
+        if self.collective != "none":
+            all_reduce_sum(t)
 
     def _rms(self, x, w):
         if self.native_ops:
@@ -112,12 +209,18 @@ class QuantDecoder(torch.nn.Module):
         be replayed with new positions).  Returns logits of the last position [B, vocab]."""
         cfg = self.cfg
         B, T = tokens.shape
-        x = self.embed[tokens]                                   # [B, T, d]
+        R = B * T
+        x = self.embed[tokens]                                   # [B, T, d], contiguous
+        x2 = x.view(R, -1)
+        fused = self.comm is not None and self.collective == "auto" and self.native_ops and self.comm.fits(R, cfg.d_model)
         mask = None   # built on first use: the single-token step with the native attention needs none
         pending = None   # output of the previous down projection, not yet added to the residual stream
+        h = None         # fused path: the normed input of the next layer, made by the reduction kernel
+        nblk = len(self.blocks)
         for li, blk in enumerate(self.blocks):
-            h = self._add_rms(x, pending, blk.norm1) if pending is not None else self._rms(x, blk.norm1)
-            qkv = blk.qkv(h.view(B * T, -1)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
+            if h is None:
+                h = self._add_rms(x, pending, blk.norm1) if pending is not None else self._rms(x, blk.norm1)
+            qkv = blk.qkv(h.view(R, -1)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
             q, k, v = qkv[:, :, : blk.hq], qkv[:, :, blk.hq : blk.hq + blk.hkv], qkv[:, :, blk.hq + blk.hkv :]
             if self.native_ops:
                 ops.rope_cache(qkv, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)
@@ -133,19 +236,47 @@ class QuantDecoder(torch.nn.Module):
                     mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
                 att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
                                                      attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
-                att2d = att.transpose(1, 2).reshape(B * T, -1)
-            o = blk.o(att2d)
-            all_reduce_sum(o)                                     # row parallel
-            h = self._add_rms(x, o.view(B, T, -1), blk.norm2)     # x += o, then the norm
-            gu = blk.gate_up(h.view(B * T, -1))
+                att2d = att.transpose(1, 2).reshape(R, -1)
+            if fused:
+                # row parallel: the partial goes straight into the communicator's slot; ONE launch then
+                # sums it over the ranks, adds it to the residual stream and applies the next norm
+                blk.o(att2d, out=self.comm.slot(0, R))
+                h = self.comm.allreduce_add_rmsnorm(0, x2, blk.norm2, R)
+            else:
+                o = blk.o(att2d)
+                self._reduce(o)                                       # row parallel
+                h = self._add_rms(x, o.view(B, T, -1), blk.norm2)     # x += o, then the norm
+            gu = blk.gate_up(h.view(R, -1))
             half = gu.shape[-1] // 2
             act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
-            dn = blk.down(act)
-            all_reduce_sum(dn)                                    # row parallel
-            pending = dn.view(B, T, -1)                           # added by the next layer's (or the final) norm
-        x = x + pending
-        last = self._rms(x[:, -1], self.final_norm)
-        return last @ self.lm_head
+            if fused:
+                blk.down(act, out=self.comm.slot(1, R))
+                last = li + 1 == nblk
+                if not last:
+                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.blocks[li + 1].norm1, R)
+                elif T == 1:
+                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.final_norm, R)     # the final norm of every row
+                else:
+                    self.comm.allreduce_add_rmsnorm(1, x2, None, R, out=x2)            # x += sum; the final norm follows
+                    h = None
+                pending = None
+            else:
+                dn = blk.down(act)
+                self._reduce(dn)                                      # row parallel
+                pending = dn.view(B, T, -1)                           # added by the next layer's (or the final) norm
+                h = None
+        if fused and T == 1:
+            last = h.view(B, -1)
+        else:
+            if pending is not None:
+                x = x + pending
+            last = self._rms(x[:, -1], self.final_norm)
+        return self.lm_head(last)
+
+    def close(self):
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
 
 
 def quantized_bytes_per_token(cfg: DecoderConfig, world: int = 1) -> int:
@@ -195,3 +326,59 @@ def run_decode(model: QuantDecoder, prompt_len: int = 128, steps: int = 256, use
         e1.record()
         torch.cuda.synchronize(dev)
     return e0.elapsed_time(e1) * 1e-3, tok.flatten()
+
+
+def teacher_forced_logits(model: QuantDecoder, tokens: torch.Tensor, prompt_len: int) -> torch.Tensor:
+    """Logits after feeding `tokens` [B, L]: the first `prompt_len` as one prefill, the rest one at a
+    time (eager launches, no graph).  Two models given the same tokens can be compared on the result
+    without their greedy choices drifting apart."""
+    dev = model.embed.device
+    L = tokens.shape[1]
+    assert L <= model.cfg.max_len and 0 < prompt_len <= L
+    with torch.no_grad():
+        logits = model(tokens[:, :prompt_len].contiguous(), torch.arange(prompt_len, device=dev))
+        for t in range(prompt_len, L):
+            logits = model(tokens[:, t : t + 1].contiguous(), torch.full((1,), t, dtype=torch.long, device=dev))
+    torch.cuda.synchronize(dev)
+    return logits
+
+
+def time_linears(model: QuantDecoder, reps: int = 3) -> float:
+    """Device seconds of the quantized linears of ONE decode step alone: every layer's four linears
+    and the output projection, launched back to back from a CUDA graph on inputs of the decode
+    step's shapes (each layer streams its own weights, as in the step)."""
+    cfg, B, dev = model.cfg, model.batch, model.embed.device
+    blk0 = model.blocks[0]
+    with torch.no_grad():
+        h = torch.randn(B, cfg.d_model, device=dev).half()
+        att = torch.randn(B, blk0.hq * blk0.hd, device=dev).half()
+        act = torch.randn(B, blk0.down.in_features, device=dev).half()
+        outs = {id(l): torch.empty(B, l.out_features, dtype=torch.float16, device=dev)
+                for l in (blk0.qkv, blk0.o, blk0.gate_up, blk0.down, model.lm_head)}
+
+        def step():
+            for blk in model.blocks:
+                blk.qkv(h, out=outs[id(blk0.qkv)])
+                blk.o(att, out=outs[id(blk0.o)])
+                blk.gate_up(h, out=outs[id(blk0.gate_up)])
+                blk.down(act, out=outs[id(blk0.down)])
+            model.lm_head(h, out=outs[id(model.lm_head)])
+
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(s)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        g.replay()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) * 1e-3 / reps

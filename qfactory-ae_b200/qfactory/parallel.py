@@ -10,8 +10,8 @@ matmul) (reference: third_party/vllm-bitblas/vllm/model_executor/layers/linear.p
   row parallel     split K: every rank owns K/p input features (a whole number of quantisation
                    groups); the full-width partial results are summed with ONE all-reduce
 
-The collective is `torch.distributed.all_reduce` (NCCL over NVLink on GPUs, gloo in the CPU
-tests).  Kernels never read peer memory.
+The collective here is `torch.distributed.all_reduce` (NCCL over NVLink on GPUs, gloo in the CPU
+tests); the decoder's decode steps use the peer-memory kernel of comm.py instead.
 """
 from __future__ import annotations
 
@@ -47,41 +47,3 @@ def all_reduce_sum(t: torch.Tensor, group=None) -> torch.Tensor:
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
-
-
-class ColumnParallelQLinear(torch.nn.Module):
-    """y_local = x @ dequant(W[:, shard])^T: disjoint output features, no collective."""
-
-    def __init__(self, local_layer: torch.nn.Module):
-        super().__init__()
-        self.layer = local_layer
-
-    def forward(self, x, out=None):
-        return self.layer(x) if out is None else self.layer(x, out=out)
-
-
-class RowParallelQLinear(torch.nn.Module):
-    """y = sum over ranks of x_shard @ dequant(W[shard, :])^T, one all-reduce."""
-
-    def __init__(self, local_layer: torch.nn.Module, group=None):
-        super().__init__()
-        self.layer = local_layer
-        self.group = group
-
-    def forward(self, x_shard, out=None):
-        y = self.layer(x_shard) if out is None else self.layer(x_shard, out=out)
-        return all_reduce_sum(y, self.group)
-
-
-def make_column_parallel(K, N, bits, q, group_size, s, z, rank, world, batch_size=1):
-    from .qlinear import QLinear
-
-    ql, sl, zl = shard_columns(q, s, z, rank, world)
-    return ColumnParallelQLinear(QLinear.init(batch_size, K, N // world, bits, ql, group_size, sl, zl))
-
-
-def make_row_parallel(K, N, bits, q, group_size, s, z, rank, world, batch_size=1, group=None):
-    from .qlinear import QLinear
-
-    ql, sl, zl = shard_rows(q, s, z, rank, world, group_size)
-    return RowParallelQLinear(QLinear.init(batch_size, K // world, N, bits, ql, group_size, sl, zl), group)

@@ -4,8 +4,9 @@
 Same names, arguments and error behaviour as the reference (reference:
 qfactory/qlinear.py:5-145).  Differences, all on purpose:
   * the packed tensors `.w/.s/.z` use the layouts of `convert.py`: `layout='tile'` (every bit
-    width), `layout='fragment'` (4-bit, K % 128 == 0: the tensor-core fragment order) or
-    `layout='auto'` (the default: fragment whenever the shape allows it);
+    width), `layout='fragment'` (2-, 4- and 8-bit, K % 128 == 0: the tensor-core fragment order)
+    or `layout='auto'` (the default: fragment whenever the shape allows it); `state_dict()` carries
+    the layout, and loading packed tensors of the other layout raises;
   * the batch size is a run-time property of `forward`, not a compile-time constant, and
     `x` may have any number of leading dimensions;
   * kernel selection is a static heuristic inside the native library, so `compile_flags`
@@ -62,6 +63,21 @@ class _PackedLinear(torch.nn.Module):
         self._desc = d
         self._lib = L
 
+    # -- the packed layout travels with the checkpoint ------------------------
+    def get_extra_state(self):
+        """[packed layout, library version]: the same bytes mean different codes under the two
+        layouts, so a checkpoint must say which one it holds."""
+        return torch.tensor([int(self.packed_layout), int(_native.version_or_zero())], dtype=torch.int32)
+
+    def set_extra_state(self, state):
+        saved = int(state[0])
+        if saved != int(self.packed_layout):
+            names = {layout.LAYOUT_TILE: "tile", layout.LAYOUT_FRAGMENT: "fragment"}
+            raise RuntimeError(
+                f"packed-layout mismatch: the checkpoint holds the {names.get(saved, saved)} layout, this module "
+                f"expects {names.get(self.packed_layout, self.packed_layout)}; build the module with "
+                f"layout={names.get(saved, saved)!r} or repack the tensors (convert.unpack_params / convert_params)")
+
     def _apply(self, fn, *a, **kw):
         r = super()._apply(fn, *a, **kw)
         self._desc = None  # device pointers changed
@@ -82,11 +98,21 @@ class _PackedLinear(torch.nn.Module):
             out = torch.empty(M, self.out_features, dtype=torch.float16, device=x.device)
         else:
             assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() == M * self.out_features
-        st = self._lib.qfb_linear_forward(
-            ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
-            self._ws.data_ptr(), self._ws_bytes, self.flags,
-            torch.cuda.current_stream(x.device).cuda_stream,
-        )
+        if x.device != self.w.device:
+            raise _native.NativeError(f"activations on {x.device}, packed weights on {self.w.device}")
+        if x.device.index == torch.cuda.current_device():
+            st = self._lib.qfb_linear_forward(
+                ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
+                self._ws.data_ptr(), self._ws_bytes, self.flags,
+                torch.cuda.current_stream(x.device).cuda_stream,
+            )
+        else:  # the launch goes to the current device: make it the tensors' device
+            with torch.cuda.device(x.device):
+                st = self._lib.qfb_linear_forward(
+                    ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
+                    self._ws.data_ptr(), self._ws_bytes, self.flags,
+                    torch.cuda.current_stream(x.device).cuda_stream,
+                )
         if st != 0:
             _native.check(st, "qfb_linear_forward")
         return out.view(*lead, self.out_features)

@@ -1,0 +1,110 @@
+"""The one-shot peer-memory all-reduce fused with the residual add and the RMS norm, on ONE GPU.
+
+The buffers of all ranks are allocated by this process on the same device and the test plays the
+peers' part by hand: it writes their partials into their slots and raises their flags BEFORE the
+kernel of the rank under test is launched (two kernels that wait on each other are never run side
+by side on one GPU).  The bounded wait is exercised with a flag that nothing raises."""
+import pytest
+import torch
+
+from qfactory import _native
+from qfactory.comm import PeerComm
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference(parts, x, w, eps=1e-5):
+    """Sum in rank order in fp32, rounded to fp16; x + s as one fp16 addition; the norm as rmsnorm does."""
+    s = torch.zeros_like(parts[0], dtype=torch.float32)
+    for p in parts:
+        s = s + p.float()
+    row = s.half() if x is None else (x + s.half())
+    if w is None:
+        return row, row
+    f = row.float()
+    n = (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + eps)).half() * w
+    return row, n
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("rows,d", [(1, 8192), (5, 1024), (64, 512), (3, 16384)])
+def test_allreduce_add_rmsnorm_matches_reference_over_two_calls(world, rows, d):
+    g = torch.Generator(device="cuda").manual_seed(world * 100 + rows)
+    rank = world - 1 if rows % 2 else 0
+    comm = PeerComm.local_emulation(rank, world, d, 64)
+    try:
+        x = torch.randn(rows, d, generator=g, device="cuda").half()
+        w = (torch.rand(d, generator=g, device="cuda") + 0.5).half()
+        for call, slot in enumerate((0, 1, 0)):
+            parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
+            for r in range(world):
+                comm.peer_slot(r, slot, rows).copy_(parts[r])
+                if r != rank:
+                    for row in range(rows):
+                        comm.raise_flag(row, r, call + 1)       # peer r has arrived at reduction `call`
+            want_x, want_h = _reference(parts, x, w)
+            h = comm.allreduce_add_rmsnorm(slot, x, w, rows)
+            torch.cuda.synchronize()
+            assert torch.equal(x, want_x)                          # the residual stream, bit for bit
+            assert (h.float() - want_h.float()).abs().max() <= 2e-3 * want_h.float().abs().max()
+            assert comm.read_status() == 0
+    finally:
+        comm.close()
+
+
+def test_plain_sum_without_residual_or_norm():
+    world, rows, d = 4, 7, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    comm = PeerComm.local_emulation(1, world, d, 16)
+    try:
+        parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
+        for r in range(world):
+            comm.peer_slot(r, 0, rows).copy_(parts[r])
+            for row in range(rows):
+                comm.raise_flag(row, r, 1)
+        out = comm.allreduce_add_rmsnorm(0, None, None, rows)
+        torch.cuda.synchronize()
+        assert torch.equal(out, _reference(parts, None, None)[0])
+    finally:
+        comm.close()
+
+
+def test_bounded_wait_runs_out_and_the_next_call_is_correct():
+    world, rows, d = 2, 2, 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    comm = PeerComm.local_emulation(0, world, d, 8)
+    try:
+        comm.set_timeout_us(100)                                  # nothing raises the peer's flag: give up after 100 us
+        x = torch.randn(rows, d, generator=g, device="cuda").half()
+        w = torch.ones(d, dtype=torch.float16, device="cuda")
+        comm.allreduce_add_rmsnorm(0, x.clone(), w, rows)
+        torch.cuda.synchronize()                                  # the kernel returned by itself
+        assert comm.read_status() == 8                            # QFB_ERR_DEVICE_FLAG, reported once
+        assert comm.read_status() == 0
+        # the communicator is still usable: the next reduction (epoch 2, the other slot) is exact
+        parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
+        for r in range(world):
+            comm.peer_slot(r, 1, rows).copy_(parts[r])
+        for row in range(rows):
+            comm.raise_flag(row, 1, 2)
+        want_x, _ = _reference(parts, x, w)
+        comm.allreduce_add_rmsnorm(1, x, w, rows)
+        torch.cuda.synchronize()
+        assert torch.equal(x, want_x) and comm.read_status() == 0
+    finally:
+        comm.close()
+
+
+def test_argument_checks():
+    L = _native.lib()
+    comm = PeerComm.local_emulation(0, 2, 512, 4)
+    try:
+        x = torch.zeros(4, 512, dtype=torch.float16, device="cuda")
+        call = lambda slot, rows, d: L.qfb_allreduce_add_rmsnorm(comm._h, slot, x.data_ptr(), None, None, rows, d, 1e-5, None)
+        assert call(2, 1, 512) == 2          # slot out of range
+        assert call(0, 1, 500) == 2          # d not a multiple of 8
+        assert call(0, 5, 512) == 7          # more rows than the slot holds
+        assert call(0, 0, 512) == 0          # nothing to do
+        assert L.qfb_comm_max_rows() == 64
+    finally:
+        comm.close()

@@ -1,21 +1,36 @@
-"""The quantized decoder against the same network evaluated with dequantised fp32 weights."""
+"""The quantized decoder against the same network evaluated with dequantised fp32 weights: the
+weights the kernels' own decode path yields, and the weights the CPU oracle dequantises from the
+codes, scales and zeros the layers were built from."""
+import numpy as np
 import pytest
 import torch
 import torch.nn.functional as F
 
+from oracle import qf_oracle as O
 from qfactory.decoder import DecoderConfig, QuantDecoder, run_decode
 
 pytestmark = pytest.mark.gpu
 
 
-def _reference_logits(model, tokens):
+def _oracle_weight(t):
+    """fp32 [K, N] on the GPU from (codes, scales, GPTQ zeros), dequantised by the CPU oracle."""
+    q, s, z = (a.cpu() for a in t)
+    return O.dequant_effective(q, s, O.effective_zero(z.numpy(), 4)).float().cuda()
+
+
+def _reference_logits(model, tokens, weights=None):
+    """`weights`: None = each layer's dequantize(); else a function (block index, name) -> fp32 [K, N]."""
     cfg = model.cfg
     B, T = tokens.shape
     pos = torch.arange(T, device=tokens.device)
     x = model.embed[tokens].float()
     rms = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
-    for blk in model.blocks:
-        W = lambda l: l.dequantize().float()       # [K, N] through the kernels' own decode path
+    for bi, blk in enumerate(model.blocks):
+        if weights is None:
+            W = lambda l: l.dequantize().float()       # [K, N] through the kernels' own decode path
+        else:
+            W = lambda l, bi=bi, blk=blk: weights(bi, {id(blk.qkv): "qkv", id(blk.o): "o", id(blk.gate_up): "gate_up",
+                                                        id(blk.down): "down"}[id(l)])
         h = rms(x, blk.norm1)
         qkv = (h.view(B * T, -1) @ W(blk.qkv)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
         q, k, v = qkv[:, :, : blk.hq], qkv[:, :, blk.hq : blk.hq + blk.hkv], qkv[:, :, blk.hq + blk.hkv :]
@@ -28,7 +43,8 @@ def _reference_logits(model, tokens):
         gu = h.view(B * T, -1) @ W(blk.gate_up)
         half = gu.shape[-1] // 2
         x = x + ((F.silu(gu[:, :half]) * gu[:, half:]) @ W(blk.down)).view(B, T, -1)
-    return rms(x[:, -1], model.final_norm) @ model.lm_head.float()
+    head = model.lm_head.dequantize().float() if weights is None else weights(-1, "lm_head")
+    return rms(x[:, -1], model.final_norm) @ head
 
 
 def test_small_decoder_matches_dequantised_reference():
@@ -53,3 +69,32 @@ def test_graph_decode_equals_eager_decode():
     _, ta = run_decode(a, prompt_len=8, steps=6, use_graph=True, seed=3)
     _, tb = run_decode(b, prompt_len=8, steps=6, use_graph=False, seed=3)
     assert torch.equal(ta, tb)
+
+
+def test_seeded_decoder_matches_the_oracle_dequantised_network():
+    """Weights drawn as codes / scales / zeros (the form the tensor-parallel ranks shard): the
+    reference network is built from the ORACLE's dequantisation of those tensors."""
+    cfg = DecoderConfig(layers=2, d_model=512, n_heads=8, n_kv_heads=2, d_ff=1024, vocab=1000, max_len=64)
+    model = QuantDecoder(cfg, world=1, rank=0, device="cuda", seed=4, batch=2, weights="seeded_keep")
+    boost = lambda t: (t[0], (t[1].float() * 40.0).half(), t[2])     # scales large enough for the linears to matter
+    for blk in model.blocks:
+        blk.full = {k: boost(v) for k, v in blk.full.items()}
+        for l in (blk.qkv, blk.o, blk.gate_up, blk.down):
+            l.s.mul_(40.0)
+
+    def weights(bi, name):
+        if name == "lm_head":
+            return _oracle_weight(model.lm_head_full)
+        f = model.blocks[bi].full
+        if name == "qkv":
+            return torch.cat([_oracle_weight(f[n]) for n in ("q", "k", "v")], dim=1)
+        if name == "gate_up":
+            return torch.cat([_oracle_weight(f[n]) for n in ("gate", "up")], dim=1)
+        return _oracle_weight(f[name])
+
+    tokens = torch.randint(0, cfg.vocab, (2, 9), device="cuda")
+    with torch.no_grad():
+        got = model(tokens, torch.arange(9, device="cuda")).float()
+        want = _reference_logits(model, tokens, weights)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() <= 2e-2 * want.abs().max()

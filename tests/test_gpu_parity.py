@@ -125,47 +125,102 @@ def test_clamped_top_zero_follows_packer_semantics():
 
 
 SHAPES_7B = [(12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008)]
+LAYOUTS = ["tile", "fragment"]
 
 
+def _expected_kernel(layout_kind, M):
+    """Kernel id a fragment-layout layer must launch: the mma.sync GEMV up to 16 rows, the
+    tcgen05 kernel above (None: tile-layout layers choose between kernels 1 and 2 by size)."""
+    if layout_kind != "fragment":
+        return None
+    return 3 if M <= 16 else 2
+
+
+@pytest.mark.parametrize("layout_kind", LAYOUTS)
 @pytest.mark.parametrize("N,K", SHAPES_7B)
 @pytest.mark.parametrize("M", [1, 4, 16])
-def test_llama7b_layer_shapes_against_oracle(N, K, M):
-    layer, x, q, s, z = _layer(N, K, 4, 128, False, seed=0, M=M)
+def test_llama7b_layer_shapes_against_oracle(N, K, M, layout_kind):
+    """Every case of the Llama-7B layer sweep (reference: tests/acc_gptq.py:40-72 runs each
+    shape x M x bits against dequantize-then-matmul), on the layout the benchmark launches too."""
+    layer, x, q, s, z = _layer(N, K, 4, 128, False, seed=0, M=M, layout_kind=layout_kind)
     y = layer(x.cuda())
+    want = _expected_kernel(layout_kind, M)
+    if want is not None:
+        assert _native.last_launch()["kernel"] == want
     rel = _check_output(y, x, q, s, z, 4)
     assert rel < TOL
 
 
+@pytest.mark.parametrize("layout_kind", LAYOUTS)
 @pytest.mark.parametrize("bits", [2, 3, 4, 8])
 @pytest.mark.parametrize("sym", [False, True])
-def test_bit_width_sweep_8192(bits, sym):
+def test_bit_width_sweep_8192(bits, sym, layout_kind):
+    if layout_kind == "fragment" and bits == 3:
+        pytest.skip("3-bit layers have no fragment layout")
     N = K = 8192
-    layer, x, q, s, z = _layer(N, K, bits, 128, sym, seed=0, M=1)
+    layer, x, q, s, z = _layer(N, K, bits, 128, sym, seed=0, M=1, layout_kind=layout_kind)
     y = layer(x.cuda())
+    want = _expected_kernel(layout_kind, 1)
+    if want is not None:
+        assert _native.last_launch()["kernel"] == want
     _check_output(y, x, q, s, z, bits)
 
 
-def test_full_size_properties_mlp70b():
-    # (28672, 8192) W4 g128: linearity in x, determinism, and a sampled oracle check
-    N, K, bits, GS = 28672, 8192, 4, 128
-    g = torch.Generator().manual_seed(0)
-    layer = QLinear.empty(1, K, N, bits, GS, sym=False, layout="tile")
+def _random_packed_layer(N, K, bits, GS, M, layout_kind, seed):
+    """A full-size layer of random packed bytes (any byte pattern is a valid packing), its
+    activations, and the codes / scales / zeros of a few sampled output rows recovered by the
+    torch unpackers, for a sampled oracle check where the whole oracle would take minutes."""
+    g = torch.Generator().manual_seed(seed)
+    layer = QLinear.empty(M, K, N, bits, GS, sym=False, layout=layout_kind)
     layer.w.copy_(torch.randint(-128, 128, layer.w.shape, generator=g, dtype=torch.int8))
     layer.s.copy_((torch.rand(layer.s.shape, generator=g) * 0.018 + 0.002).half())
-    layer.z.copy_(torch.randint(0, 16, layer.z.shape, generator=g, dtype=torch.int8))
-    x1 = torch.randn(1, K, generator=g).half().cuda()
+    layer.z.copy_(torch.randint(0, 1 << bits, layer.z.shape, generator=g, dtype=torch.int8))
+    x = torch.randn(M, K, generator=g).half()
+    return layer, x
+
+
+def _sampled_oracle(layer, x, rows):
+    N = layer.out_features
+    q = layer.unpack_codes()[:, rows].cpu()
+    frag = layer.packed_layout == layout.LAYOUT_FRAGMENT
+    s = (layout.unpack_scale_fragment if frag else layout.unpack_scale)(layer.s.cpu(), N)[:, rows]
+    ze = (layout.unpack_zero_fragment if frag else layout.unpack_zero)(layer.z.cpu(), N)[:, rows].numpy()
+    return O.qlinear_exact(x, O.dequant_effective(q, s, ze))
+
+
+@pytest.mark.parametrize("layout_kind", LAYOUTS)
+@pytest.mark.parametrize("N,K", [(28672, 8192), (8192, 28672)])
+@pytest.mark.parametrize("M", [1, 8, 16, 32, 64, 128, 256, 1024])
+def test_llama70b_mlp_shapes_sampled_rows(N, K, M, layout_kind):
+    """Batch sweep on both Llama-70B MLP shapes at full size, built-in kernel choice: sampled
+    output rows against the oracle, crossing from the GEMV kernels to the tcgen05 kernel."""
+    layer, x = _random_packed_layer(N, K, 4, 128, M, layout_kind, seed=M + N)
+    y = layer(x.cuda())
+    want_kernel = _expected_kernel(layout_kind, M)
+    if want_kernel is not None:
+        assert _native.last_launch()["kernel"] == want_kernel
+    rows = torch.tensor([0, 1, 127, 128, N // 2 + 5, N - 1])
+    want = _sampled_oracle(layer, x, rows)
+    got = y[:, rows].float().cpu().numpy()
+    assert np.isfinite(y.float().cpu().numpy()).all()
+    assert np.abs(got - want).max() <= TOL * float(y.float().abs().max())
+
+
+@pytest.mark.parametrize("layout_kind", LAYOUTS)
+@pytest.mark.parametrize("N,K", [(28672, 8192), (8192, 28672)])
+def test_full_size_properties_mlp70b(N, K, layout_kind):
+    # W4 g128 at full size: linearity in x, determinism, and a sampled oracle check
+    layer, x1 = _random_packed_layer(N, K, 4, 128, 1, layout_kind, seed=0)
+    g = torch.Generator().manual_seed(1)
     x2 = torch.randn(1, K, generator=g).half().cuda()
+    x1 = x1.cuda()
     y1, y2 = layer(x1).float(), layer(x2).float()
     y12 = layer((x1.float() + x2.float()).half()).float()
     scale = y12.abs().max()
     assert (y12 - (y1 + y2)).abs().max() <= 2 * TOL * scale
     assert torch.equal(layer(x1), layer(x1))  # split-K reduction order is fixed
-    # rows sampled against the oracle via the kernels' own unpack
-    rows = torch.tensor([0, 1, 127, 128, 5000, 28671])
-    q = layer.unpack_codes()[:, rows].cpu()
-    s = layout.unpack_scale(layer.s.cpu(), N)[:, rows]
-    ze = layout.unpack_zero(layer.z.cpu(), N)[:, rows].numpy()
-    want = O.qlinear_exact(x1.cpu(), O.dequant_effective(q, s, ze))
+    rows = torch.tensor([0, 1, 127, 128, 5000, N - 1])
+    want = _sampled_oracle(layer, x1.cpu(), rows)
     got = layer(x1)[:, rows].float().cpu().numpy()
     assert np.abs(got - want).max() <= TOL * float(scale)
 

@@ -159,7 +159,7 @@ def test_module_refuses_to_run_without_cuda():
 
     q = torch.zeros(128, 8, dtype=torch.int32)
     layer = QLinear.init(1, 128, 8, 4, q, 64, torch.ones(2, 8, dtype=torch.float16), torch.zeros(2, 8, dtype=torch.int32))
-    assert set(layer.state_dict()) == {"w", "s", "z"}
+    assert set(layer.state_dict()) == {"w", "s", "z", "_extra_state"}  # packed tensors + the layout tag
     if not torch.cuda.is_available():
         with pytest.raises(_native.NativeError):
             layer(torch.zeros(1, 128, dtype=torch.float16))

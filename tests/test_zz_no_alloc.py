@@ -3,9 +3,10 @@ memory is owned by another component, or they run inside a fixed schedule or a s
 
 Collected last on purpose.  It drives `qfb_gemv_forward_static` directly through the C ABI,
 twice in a row on the same layer (the second call sees the scratch contents the first one
-left behind), and compares with the regular workspace-based entry point."""
+left behind), and compares with the regular workspace-based entry point and with the CPU oracle."""
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
@@ -32,9 +33,11 @@ def test_static_scratch_entry_matches_regular_entry(M, N, K):
         outs.append(y.float())
     torch.cuda.synchronize()
     scale = want.abs().max()
+    _, yex = O.reference_forward(x, q, s, z, 4)  # the oracle's dequantize-then-matmul
     for y in outs:
         assert torch.isfinite(y).all()
         assert (y - want).abs().max() <= TOL * scale
+        assert np.abs(y.cpu().numpy().astype(np.float64) - yex).max() <= TOL * np.abs(yex).max()
     assert torch.equal(outs[0], outs[1])
 
 
