@@ -165,11 +165,15 @@ int qfb_read_status(const void* workspace, void* stream, unsigned* status_out);
 /* Debug / tuning override of the split-K heuristic of the SIMT kernel: split_k <= 0 and
  * k_ways <= 0 restore the built-in choice.  Process-wide, not thread-safe. */
 void qfb_set_gemv_tuning(int split_k, int k_ways);
-/* Tuning override of the tensor-core kernel's split-K factor for batches <= 64 (0 = built-in). */
+/* Tuning override of the tensor-core kernel's K split (0 = built-in): the split-K factor for batches
+ * <= 64; above 64 rows, values 2..4 cut every (row tile, batch tile) unit into that many K ranges. */
 void qfb_set_tensor_split(int split_k);
+/* Tuning override of the tensor-core kernel's batch tile above 64 rows: 64, 128 or 256 columns
+ * (0 = built-in choice). */
+void qfb_set_tensor_batch_tile(int columns);
 /* Tuning override of the tensor-core kernel's decode groups where it scales in the decode (batches
- * > 32, or groups of 64): 1 = eight decode warps, 2 = two groups of eight that take alternate
- * stages; 0 = built-in choice (2). */
+ * > 32, or groups of 64): 1 = eight decode warps (two CTAs per SM for batch tiles up to 128 columns),
+ * 2 = two groups of eight that take alternate stages (one CTA per SM); 0 = built-in choice. */
 void qfb_set_tensor_decode_groups(int groups);
 /* mma.sync GEMV (fragment layout), how K splits are reduced: 1 (default) lets the cost model
  * choose between a thread-block cluster (distributed shared memory, at most 8 splits) and the

@@ -40,6 +40,7 @@ static int g_tune_split = 0, g_tune_kways = 0;
 static int g_tc_min_m = 2;  // smallest batch routed to the tensor-core kernel
 static int g_tc_split = 0;  // tuning override of the tensor-core split-K factor (0 = built-in)
 static int g_tc_dg = 0;     // tuning override of the tensor-core kernel's decode groups (0 = built-in)
+static int g_tc_nb = 0;     // tuning override of the tensor-core kernel's batch tile above 64 rows (0 = built-in)
 static int g_mma_cluster = 1;  // mma.sync GEMV: reduce up to 8 K splits inside a thread-block cluster
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -114,13 +115,15 @@ static size_t counters_bytes(int tiles) {
 static size_t partial_offset(int tiles) { return kHeaderBytes + counters_bytes(tiles); }
 
 // ---- tensor-core path planning --------------------------------------------------------
-struct TcPlan { int nb, mtiles, split, dg; bool post; };
+struct TcPlan { int nb, mtiles, split, dg; bool post; int tail_split, full_units, tail_units; };
 
 static bool tc_supported(const LayerView& v) { return v.k % 128 == 0; }
 
 static TcPlan plan_tc(const LayerView& v, int m) {
   TcPlan pl;
   pl.split = 1;
+  pl.tail_split = 0;
+  pl.full_units = pl.tail_units = 0;
   // per-stage accumulators need quantisation groups made of whole 128-k stages
   const bool post_ok = v.group_size == -1 || v.group_size % 128 == 0;
   pl.dg = 1;
@@ -146,7 +149,7 @@ static TcPlan plan_tc(const LayerView& v, int m) {
     if (v.tiles > 512) split = 1;  // the counter array holds 512 tiles x 4 row quarters
     pl.split = split;
   } else {
-    // tensor-bound regime: scale in the decode, one accumulator over all of K, no split;
+    // tensor-bound regime: scale in the decode, one accumulator over all of K;
     // pick the widest batch tile that still yields at least one CTA per SM
     pl.post = false;
     pl.nb = 64;
@@ -154,13 +157,44 @@ static TcPlan plan_tc(const LayerView& v, int m) {
       if (m >= nb && (long long)v.tiles * ((m + nb - 1) / nb) >= num_sms()) { pl.nb = nb; break; }
     }
     if (pl.nb == 64 && (long long)v.tiles * ((m + 127) / 128) >= num_sms() / 2) pl.nb = 128;
+    if (g_tc_nb == 64 || g_tc_nb == 128 || g_tc_nb == 256) pl.nb = g_tc_nb;
     pl.mtiles = (m + pl.nb - 1) / pl.nb;
-
+    const int kblocks = v.k / 128;
+    if (g_tc_split > 1) {  // tuning override: every unit is cut
+      pl.tail_split = std::min(g_tc_split, 4);
+    } else if (g_tc_split == 0 && g_tc_nb == 0 && m >= 96 && m <= 512 && kblocks >= 64) {
+      // Few row tiles (N small against the SM count): narrow batch tiles would decode every weight
+      // tile once per batch tile.  Better (measured: (8192,28672) at 128 rows 123 -> 78 us): the
+      // widest tile the batch fills, every unit cut into 2..4 K ranges of one CTA each, fp32
+      // partials summed in range order by the last CTA to arrive.
+      const int nbw = m > 128 ? 256 : 128;
+      const int units = v.tiles * ((m + nbw - 1) / nbw);
+      const int s = std::min(std::min(4, kblocks / 16), num_sms() / std::max(1, units));
+      if (nbw > pl.nb && s >= 2) {
+        pl.nb = nbw;
+        pl.mtiles = (m + nbw - 1) / nbw;
+        pl.tail_split = s;
+      }
+    }
+    if (pl.tail_split > 1) {
+      pl.full_units = 0;
+      pl.tail_units = v.tiles * pl.mtiles;
+    }
   }
-  // scale-in-the-decode mode: two decode groups on alternate stages (the latency of one stage's
-  // decode, not its throughput, bounds the pipeline there: measured +10-15 % at 128..512 rows)
-  if (!pl.post) pl.dg = g_tc_dg > 0 ? std::min(g_tc_dg, 2) : 2;
+  // scale-in-the-decode mode: two decode groups on alternate stages in one CTA per SM (the latency
+  // of one stage's decode, not its throughput, bounds the pipeline there: measured +10-15 % at
+  // 128..512 rows), or, for batch tiles up to 128 columns on layers with more row tiles than SMs, one
+  // decode group and two CTAs per SM (two independent pipelines: measured +5-12 % at 64..128 rows)
+  if (!pl.post) {
+    const bool two_per_sm = pl.nb <= 128 && pl.tail_split <= 1 && (long long)v.tiles * pl.mtiles >= num_sms() * 6 / 5 &&
+                            m <= 128;
+    pl.dg = g_tc_dg > 0 ? std::min(g_tc_dg, 2) : (two_per_sm ? 1 : 2);
+  }
   return pl;
+}
+
+static size_t tc_tail_partial_bytes(const TcPlan& pl) {
+  return (size_t)pl.tail_split * pl.tail_units * pl.nb * kTileRows * sizeof(float);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -215,6 +249,9 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   p.counters = nullptr;
   p.status = nullptr;
   if (workspace && ws_bytes >= kHeaderBytes) p.status = static_cast<unsigned*>(workspace);
+  p.tail_split = 0;
+  p.full_units = p.tail_units = 0;
+  p.mtiles = pl.mtiles;
   if (pl.split > 1) {
     const size_t off = partial_offset(v.tiles);
     const size_t need = off + (size_t)pl.split * m * v.npad * sizeof(float);
@@ -222,10 +259,24 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
     p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
     p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
   }
-  const dim3 grid(v.tiles, pl.mtiles, pl.split);
+  dim3 grid(v.tiles, pl.mtiles, pl.split);
+  if (pl.tail_split > 1) {
+    // the tail split is an optimisation: a workspace too small for its partial sums means the
+    // plain grid, not an error (the counters of tail units sit in the first 2048 slots)
+    const size_t off = partial_offset(v.tiles);
+    const size_t need = off + tc_tail_partial_bytes(pl);
+    if (workspace && ws_bytes >= need && pl.tail_units * 4 <= 2048) {
+      p.tail_split = pl.tail_split;
+      p.full_units = pl.full_units;
+      p.tail_units = pl.tail_units;
+      p.counters = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + kHeaderBytes);
+      p.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + off);
+      grid = dim3(pl.full_units + pl.tail_units * pl.tail_split, 1, 1);
+    }
+  }
   tl_last_launch[0] = 2;
   tl_last_launch[1] = grid.x * grid.y;
-  tl_last_launch[2] = grid.z;
+  tl_last_launch[2] = p.tail_split > 1 ? p.tail_split : grid.z;
   tl_last_launch[3] = 256 + 256 * pl.dg;
   tl_last_launch[4] = pl.nb;
   return check_cuda(launch_gemm_tc(tm, p, v.bits, pl.nb, pl.post, pl.dg, grid, (flags & QFB_FLAG_PDL) != 0, st));
@@ -546,13 +597,14 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
   if (k % 128 == 0) {
     LayerView v = {};
     v.n = n; v.k = k; v.bits = bits; v.npad = npad; v.tiles = tiles;
-    const int probes[] = {16, 32, 64, m_max};
+    const int probes[] = {16, 32, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 4096, m_max};
     for (int gs : {64, 128}) {  // the group size selects between the two accumulation modes
       v.group_size = gs;
       for (int m : probes) {
         if (m > m_max) continue;
         const TcPlan pl = plan_tc(v, m);
         if (pl.split > 1) partial = std::max(partial, (size_t)pl.split * m * npad * sizeof(float));
+        if (pl.tail_split > 1) partial = std::max(partial, tc_tail_partial_bytes(pl));
       }
     }
   }
@@ -598,6 +650,7 @@ void qfb_set_gemv_tuning(int split_k, int k_ways) {
 
 void qfb_set_tensor_split(int split_k) { g_tc_split = split_k > 0 ? split_k : 0; }
 void qfb_set_tensor_decode_groups(int groups) { g_tc_dg = groups > 0 ? groups : 0; }
+void qfb_set_tensor_batch_tile(int columns) { g_tc_nb = columns > 0 ? columns : 0; }
 
 void qfb_set_cluster_reduce(int mode) { g_mma_cluster = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 

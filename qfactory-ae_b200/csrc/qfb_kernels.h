@@ -78,6 +78,11 @@ struct TcParams {
   int halfstages_per_group;  // group_size / 64
   uint32_t zconst;
   int layout;                // QFB_LAYOUT_TILE, or QFB_LAYOUT_FRAGMENT (2-, 4- and 8-bit)
+  // tail-split launches (one-dimensional grid; 0 = the uniform grid (tiles, batch tiles, splits)):
+  int tail_split;            // K ranges each unit of the last, partly filled wave is cut into
+  int full_units;            // (row tile, batch tile) units that run whole, one CTA each
+  int tail_units;            // units that are cut; partial = [tail_split][tail_units][batch tile][128] fp32
+  int mtiles;                // batch tiles per row tile (unit = tile * mtiles + batch tile)
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
 cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,

@@ -24,7 +24,7 @@ EXPORTS = (
     "qfb_packed_weight_bytes", "qfb_packed_scale_bytes", "qfb_packed_zero_bytes",
     "qfb_workspace_bytes", "qfb_workspace_init",
     "qfb_linear_forward", "qfb_linear_forward_host", "qfb_select_kernel",
-    "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_set_tensor_decode_groups", "qfb_set_cluster_reduce", "qfb_read_status",
+    "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_set_tensor_decode_groups", "qfb_set_tensor_batch_tile", "qfb_set_cluster_reduce", "qfb_read_status",
     "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
     "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention",
@@ -94,6 +94,8 @@ def lib() -> ctypes.CDLL:
     L.qfb_set_tensor_split.argtypes = [i32]
     L.qfb_set_tensor_decode_groups.restype = None
     L.qfb_set_tensor_decode_groups.argtypes = [i32]
+    L.qfb_set_tensor_batch_tile.restype = None
+    L.qfb_set_tensor_batch_tile.argtypes = [i32]
     L.qfb_set_cluster_reduce.restype = None
     L.qfb_set_cluster_reduce.argtypes = [i32]
     L.qfb_read_status.restype = i32

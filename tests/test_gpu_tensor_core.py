@@ -160,3 +160,60 @@ def test_one_and_two_decode_groups_give_identical_results(M, GS, bits):
     # 16- and 32-wide batch tiles with per-stage accumulators always run one group
     if info2["block"] == 768:
         assert info1["block"] == 512
+
+
+@pytest.mark.parametrize("M,bits,GS", [(130, 4, 128), (300, 4, 128), (257, 8, 64), (100, 2, -1)])
+@pytest.mark.parametrize("layout_kind", ["tile", "fragment"])
+def test_tail_split_of_wide_batches_agrees_with_the_plain_grid(M, bits, GS, layout_kind):
+    """Above 64 rows the units of a launch's last, partly filled wave are cut along K (2..4 ranges,
+    fp32 partials summed in range order by the last CTA to arrive).  Forced here on every unit and
+    compared with the oracle and with the uncut launch."""
+    L = _native.lib()
+    N, K = 384, 4096
+    x, q, s, z = O.make_case(M, N, K, bits, GS, False, seed=700 + M)
+    if GS == -1:
+        layer = QLinear.init(M, K, N, bits, q.cuda(), layout=layout_kind)
+    else:
+        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda(), layout=layout_kind)
+    layer.flags = _native.FLAG_FORCE_TENSOR
+    layer._prepare()
+    # cutting EVERY unit in four needs more partial-sum space than the built-in plan ever asks for
+    layer._ws = torch.zeros(32 << 20, dtype=torch.uint8, device="cuda")
+    layer._ws_bytes = layer._ws.numel()
+    xs = x.cuda()
+    _, yex = O.reference_forward(x, q, s, z, bits)
+    outs = {}
+    try:
+        for split in (1, 2, 3, 4):
+            L.qfb_set_tensor_split(split)
+            y = layer(xs).clone()
+            info = _native.last_launch()
+            assert info["kernel"] == 2 and info["grid_y"] == split
+            assert np.abs(y.float().cpu().numpy() - yex).max() <= TOL * np.abs(yex).max()
+            assert torch.equal(y, layer(xs))   # fixed summation order: identical between runs
+            outs[split] = y.float()
+    finally:
+        L.qfb_set_tensor_split(0)
+    st = ctypes.c_uint(0)
+    assert L.qfb_read_status(layer._ws.data_ptr(), None, ctypes.byref(st)) == 0 and st.value == 0
+    for split in (2, 3, 4):
+        assert (outs[split] - outs[1]).abs().max() <= 2e-3 * outs[1].abs().max()
+
+
+def test_wide_tile_with_k_split_when_the_row_tiles_leave_most_sms_idle():
+    # 16 row tiles at 128 rows: a 128-column batch tile cut in K ranges instead of two 64-column tiles
+    M, N, K = 128, 2048, 8192
+    x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=41)
+    _, yex = O.reference_forward(x, q, s, z, 4)
+    big = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda())       # workspace sized for 128 rows
+    y = big(x.cuda())
+    info = _native.last_launch()
+    assert info["kernel"] == 2 and info["grid_y"] > 1 and info["smem"] == 128   # (the last field reports the batch tile)
+    assert np.abs(y.float().cpu().numpy() - yex).max() <= TOL * np.abs(yex).max()
+    assert torch.equal(y, big(x.cuda()))
+    # a workspace too small for the partial sums means the plain grid, not an error
+    big._ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    big._ws_bytes = 4096
+    y2 = big(x.cuda())
+    assert _native.last_launch()["grid_y"] == 1
+    assert np.abs(y2.float().cpu().numpy() - yex).max() <= TOL * np.abs(yex).max()
