@@ -608,6 +608,49 @@ def main():
             extras["eager"] = {"layer": "4096x4096 M=1", "host_us_per_call": round(host_s / 400 * 1e6, 2),
                                "us_per_call_with_device": round(total_s / 400 * 1e6, 2)}
             del L
+            # same-box GPU baseline: the reference project's own kernel (its default and its scheduled
+            # design point, compiled ahead of time for sm_100a) on the four layer shapes at M = 1, in the
+            # reference's packed layout, timed by the same graph-replay method over rotating weights
+            from oracle import ref_gpu
+
+            if ref_gpu.available():
+                rows = []
+                for si, (N, K) in enumerate(ref_gpu.SHAPES):
+                    R = max(2, min(48, (400 << 20) // (N * K // 2) + 1))
+                    ws = [torch.randint(-128, 128, (N, K // 2), dtype=torch.int8, device=dev) for _ in range(R)]
+                    sc = (torch.rand(N, K // GS, device=dev) * 0.018 + 0.002).half()
+                    zz = torch.randint(-128, 128, (N, K // GS // 2), dtype=torch.int8, device=dev)
+                    xr = torch.randn(1, K, device=dev).half()
+                    yr = torch.empty(1, N, dtype=torch.float16, device=dev)
+                    row = {"N": N, "K": K, "M": 1}
+                    for sched, key in ((0, "default_us"), (1, "scheduled_us")):
+                        st = torch.cuda.Stream(device=dev)
+                        with torch.cuda.stream(st):
+                            assert ref_gpu.launch(si, sched, xr, ws[0], yr, sc, zz, st.cuda_stream) == 0
+                            torch.cuda.synchronize()
+                            gr = torch.cuda.CUDAGraph()
+                            with torch.cuda.graph(gr, stream=st):
+                                for w in ws:
+                                    ref_gpu.launch(si, sched, xr, w, yr, sc, zz, st.cuda_stream)
+                            for _ in range(3):
+                                gr.replay()
+                            torch.cuda.synchronize()
+                            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            a.record()
+                            for _ in range(10):
+                                gr.replay()
+                            b.record()
+                            torch.cuda.synchronize()
+                        row[key] = round(a.elapsed_time(b) * 1e3 / (10 * R), 2)
+                        del gr
+                    best = min(row["default_us"], row["scheduled_us"])
+                    row["GBps"] = round(algorithmic_bytes(1, N, K) / best / 1e3, 1)
+                    rows.append(row)
+                    del ws
+                    torch.cuda.empty_cache()
+                extras["ref_gpu_kernel"] = {"what": "the reference project's kernel_gptq template (BLOCK_N 1, BLOCK_SIZE 128, NUM_ELM 8, "
+                                            "eager decode; default and scheduled load paths), sm_100a, same box, same timing method",
+                                            "rows": rows}
         except Exception as e:
             extras["error"] = str(e)[:200]
         torch.cuda.empty_cache()

@@ -74,6 +74,14 @@ typedef enum qfb_status {
 #define QFB_FLAG_NO_SYNC 8u      /* qfb_linear_forward_host only: do not synchronise the stream; the
                                     caller queues several layers and synchronises once */
 
+#define QFB_FLAG_TEST_STALLED_WAIT 16u /* test aid for the bounded device-side waits: the kernel's first
+                                    bulk-copy barrier is told to expect 16 bytes that never come and every
+                                    wait gives up after ~100 us instead of ~1 s.  The copies themselves all
+                                    land; the launch returns, the status word of the workspace is set
+                                    (qfb_read_status -> QFB_ERR_DEVICE_FLAG).  The mma.sync GEMV still
+                                    produces the right output; the tcgen05 kernel abandons the launch
+                                    (its output is undefined).  Needs a workspace. */
+
 /* packed layouts */
 #define QFB_LAYOUT_TILE 0      /* tile-128 interleaved: every bit width, every batch size */
 #define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: 2/4/8-bit, K % 128 == 0, group 64 / n*128 / none */
@@ -121,6 +129,18 @@ int qfb_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
  */
 int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y,
                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+
+/*
+ * The down projection of a gated MLP with its activation fused in: y = (silu(gate) * up) . dequant(W)^T
+ * for gate_up fp16 [m, 2k] = [gate | up] as the fused gate/up linear writes it.  The combination
+ * (silu in fp32 rounded to fp16, one fp16 product: the arithmetic of qfb_silu_mul) happens while the
+ * GEMV stages its activations, so the separate element-wise launch of the reference's serving stack
+ * (third_party/vllm-bitblas/vllm/model_executor/models/llama.py:91-96) and its [m, k] tensor go away.
+ * Fragment-layout layers and m <= 16 only (the mma.sync GEMV); otherwise QFB_ERR_UNSUPPORTED and the
+ * caller runs qfb_silu_mul + qfb_linear_forward.  Results are bit-identical to that pair.
+ */
+int qfb_linear_silu_mul_forward(const qfb_layer* layer, const void* gate_up, int m, void* y, void* workspace,
+                                size_t workspace_bytes, unsigned flags, void* stream);
 
 /*
  * Same computation for callers that hold HOST buffers: copies x_host (pinned or pageable)

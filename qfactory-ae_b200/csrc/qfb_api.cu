@@ -252,6 +252,7 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
   p.tail_split = 0;
   p.full_units = p.tail_units = 0;
   p.mtiles = pl.mtiles;
+  p.stall_test = (flags & QFB_FLAG_TEST_STALLED_WAIT) ? 1 : 0;
   if (pl.split > 1) {
     const size_t off = partial_offset(v.tiles);
     const size_t need = off + (size_t)pl.split * m * v.npad * sizeof(float);
@@ -378,8 +379,13 @@ static int mma_cluster_split_cap(int tiles, int batches, int min_block) {
   return std::max(1, std::min(std::min(batches, 8), (slots + tiles - 1) / tiles));
 }
 
-static size_t mma_smem(int rows, int nt, int bpc, int kways) {
-  const size_t stage = (size_t)rows * (bpc * 128 + 16) * 2 + (size_t)bpc * 2 * 8 * nt * sizeof(float);
+// bytes of the staged activation slice and its per-segment sums; a second slice follows them when
+// gate and up slices are combined while they are staged
+static size_t mma_stage_bytes(int rows, int nt, int bpc) {
+  return (size_t)rows * (bpc * 128 + 16) * 2 + (size_t)bpc * 2 * 8 * nt * sizeof(float);
+}
+static size_t mma_smem(int rows, int nt, int bpc, int kways, bool act = false) {
+  const size_t stage = mma_stage_bytes(rows, nt, bpc) + (act ? (size_t)rows * (bpc * 128 + 16) * 2 : 0);
   const size_t red = (size_t)kways * rows * 132 * sizeof(float);  // k-way reduction lines
   return (std::max(stage, red) + 15) / 16 * 16;
 }
@@ -396,7 +402,7 @@ static size_t mma_recv_bytes(int rows, int split) {
 // part that grows with rows x splits, reducing them through the workspace a fixed fence /
 // atomic / re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
 // inside one GPC, so a grid that fits by CTA count may still need a second wave).
-static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits) {
+static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits, bool act) {
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
@@ -414,7 +420,7 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits)
     for (int s = 1; s <= cap; ++s) {
       if (g_tune_split > 0 && s != std::min(g_tune_split, cap)) continue;
       const int bpc = (batches + s - 1) / s;
-      const size_t smem = mma_smem(rows, pl.nt, bpc, kw);
+      const size_t smem = mma_smem(rows, pl.nt, bpc, kw, act);
       if (smem > smem_max && s < cap) continue;
       const int per_kway = (bpc + kw - 1) / kw;
       const double base = 0.05 * s + 0.01 * (kways_max - kw);
@@ -441,7 +447,7 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits)
   // a power of two (the kernel splits a CTA's range among the k-ways with a shift), no more than the batches of a CTA
   pl.kways = best_kw;
   while (pl.kways > 1 && pl.kways > batches / best_s) pl.kways >>= 1;
-  pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways), 16);
+  pl.smem = std::max<size_t>(mma_smem(rows, pl.nt, bpc, pl.kways, act), 16);
   pl.recv_offset = (int)pl.smem;
   if (pl.cluster) pl.smem += mma_recv_bytes(rows, pl.split);
   return pl;
@@ -450,34 +456,38 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits)
 // The search above asks the occupancy API and walks a few hundred candidates: its result is kept
 // per (device, shape, rows, group mode, bit width, tuning overrides), so a repeated call costs a
 // map lookup on the host.
-static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits) {
+static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits, bool act) {
   static std::mutex mu;
   static std::map<std::tuple<int, int, int, int, int, int, int, int, int>, MmaPlan> cache;
   int dev = 0;
   (void)cudaGetDevice(&dev);
-  const auto key = std::make_tuple(dev, tiles, k, rows, (int)seg64, bits, g_tune_split, g_tune_kways, g_mma_cluster);
+  const auto key = std::make_tuple(dev, tiles, k, rows, (int)seg64 + 2 * (int)act, bits, g_tune_split, g_tune_kways, g_mma_cluster);
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
   }
-  const MmaPlan pl = plan_mma_search(tiles, k, rows, seg64, bits);
+  const MmaPlan pl = plan_mma_search(tiles, k, rows, seg64, bits, act);
   std::lock_guard<std::mutex> lock(mu);
   cache[key] = pl;
   return pl;
 }
 
+// `act`: x is a fused gate/up tensor [m, 2k] and the layer's input is silu(gate) * up
 static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
-                   unsigned flags, cudaStream_t st) {
+                   unsigned flags, cudaStream_t st, bool act = false) {
+  const int x_stride = act ? 2 * v.k : v.k;
   for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
     const int rows = std::min(kMaxMmaRows, m - m0);
-    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits);
+    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits, act);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
     MmaParams p;
     p.qw = v.qw;
     p.qs = v.qs;
     p.qz = v.qz;
-    p.x = x + (size_t)m0 * v.k;
+    p.x = x + (size_t)m0 * x_stride;
+    p.x_stride = x_stride;
+    p.act = act ? 1 : 0;
     p.y = y + (size_t)m0 * v.n;
     p.m = rows;
     p.n = v.n;
@@ -488,6 +498,8 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.chunks_per_group = (v.group_size == -1 ? v.k : v.group_size) / 64;
     p.batches = v.k / 128;
     p.batches_per_cta = (p.batches + pl.split - 1) / pl.split;
+    p.act_offset = (int)mma_stage_bytes(rows, pl.nt, p.batches_per_cta);
+    p.stall_test = (flags & QFB_FLAG_TEST_STALLED_WAIT) ? 1 : 0;
     p.batches_div = p.batches / pl.split;
     p.batches_mod = p.batches % pl.split;
     p.zconst = v.zconst;
@@ -681,6 +693,21 @@ int qfb_linear_forward(const qfb_layer* layer, const void* x, int m, void* y, vo
                   static_cast<cudaStream_t>(stream));
   return run_gemv(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                   static_cast<cudaStream_t>(stream));
+}
+
+int qfb_linear_silu_mul_forward(const qfb_layer* layer, const void* gate_up, int m, void* y, void* workspace,
+                                size_t workspace_bytes, unsigned flags, void* stream) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (m < 0) return QFB_ERR_BAD_SHAPE;
+  if (m == 0) return QFB_OK;
+  if (!gate_up || !y) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(gate_up) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  // served by the mma.sync GEMV only, whose activation staging does the combination
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows) return QFB_ERR_UNSUPPORTED;
+  return run_mma(v, static_cast<const __half*>(gate_up), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                 static_cast<cudaStream_t>(stream), true);
 }
 
 int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host, void* x_staging,

@@ -353,6 +353,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   tc_fence_after();
   const uint32_t tmem_base = tmem_holder;
   volatile int* abortp = &abort_flag;
+  const long long wait_limit = p.stall_test ? 200000LL : kWaitLimitCycles;
   grid_launch_dependents();
 
   const bool has_z = p.qz != nullptr;
@@ -371,10 +372,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       const uint32_t ng = hpg == 1 ? 2u : 1u;
       const uint32_t zb = has_z ? ng * 128u : 0u, sb = (!POST && has_s) ? ng * 256u : 0u;
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp, kSleepProducer)) break;
+        if (!mbar_wait(smem_u32(&bar_wempty[s]), ph, abortp, kSleepProducer, wait_limit)) break;
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
-        mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb);
+        mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb + ((p.stall_test && i == 0) ? 16u : 0u));
         if (BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT) {
           // the stage is two runs: 8 k-steps (128 * BITS bytes each) of the upper and of the lower 64 rows
           const uint8_t* f0 = reinterpret_cast<const uint8_t*>(p.qw) +
@@ -401,7 +402,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       int s = 0;
       uint32_t ph = 1;
       for (int i = 0; i < nkb; ++i) {
-        if (!mbar_wait(smem_u32(&bar_xempty[s]), ph, abortp, kSleepProducer)) break;
+        if (!mbar_wait(smem_u32(&bar_xempty[s]), ph, abortp, kSleepProducer, wait_limit)) break;
         const uint32_t bar = smem_u32(&bar_xfull[s]);
         const uint32_t dst = sbase + x_off + s * Cfg::kXBytes;
         mbar_arrive_expect_tx(bar, Cfg::kXBytes);
@@ -421,10 +422,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       for (int i = e; i < nkb; i += Cfg::kIssuers) {
         const int xs = i % NX, r = i % R;
         const uint32_t phx = (uint32_t)(i / NX) & 1u, phr = (uint32_t)(i / R) & 1u;
-        if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp, kSleepMma)) break;
-        if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp, kSleepMma)) break;
+        if (!mbar_wait(smem_u32(&bar_xfull[xs]), phx, abortp, kSleepMma, wait_limit)) break;
+        if (!mbar_wait(smem_u32(&bar_afull[r]), phr, abortp, kSleepMma, wait_limit)) break;
         if (POST) {
-          if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp, kSleepMma)) break;
+          if (!mbar_wait(smem_u32(&bar_dempty[r]), phr ^ 1u, abortp, kSleepMma, wait_limit)) break;
         }
         tc_fence_after();
         const uint32_t a_tmem = tmem_base + r * kAColsPerSlot;
@@ -454,7 +455,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       // ring positions and phases of stage i (NS, R, NX are compile-time constants: multiply-shift, no division)
       const int s = i % NS, r = i % R;
       const uint32_t phs = (uint32_t)(i / NS) & 1u, phr = ((uint32_t)(i / R) & 1u) ^ 1u;
-      if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode)) break;
+      if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode, wait_limit)) break;
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qrow] : p.zconst;
       __half2 d[32];
       if (BITS != 3 && frag) StageDecodeFragment<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
@@ -472,7 +473,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_wempty[s]));
       // slot r was last read by the MMAs of stage i - R
-      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepDecode)) break;
+      if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepDecode, wait_limit)) break;
       // ... and the activation tile of that stage is free as well: tell its producer.  The
       // decode warps cannot fall behind the commits (the MMAs need their stores), so this
       // relay never misses a phase; R <= NX makes it reach every tile that is still needed.
@@ -551,7 +552,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         sc0 = sc1;
         sc1 = scale_at(i + 2, gq);
         if (++gr == stages_per_group) { gr = 0; ++gq; }
-        if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepScale)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&bar_done[r]), phr, abortp, kSleepScale, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + Cfg::kDBase + r * NB;
         constexpr int CH = NB < 32 ? NB : 32;  // columns read back per wait
@@ -578,7 +579,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         finish_split(0u, false);
       }
     } else {
-      ok = mbar_wait(smem_u32(&bar_final), 0, abortp, 500);
+      ok = mbar_wait(smem_u32(&bar_final), 0, abortp, 500, wait_limit) && !*abortp;  // (an abandoned launch stores nothing)
       if (ok) {
         tc_fence_after();
         grid_dependency_wait();
@@ -602,13 +603,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   }
 
   // ------------------------------ teardown ------------------------------------
+  tc_fence_before();
+  __syncthreads();   // every role has left its loop (a role that ran out of work early must not
+                     // look at the abort flag before the others had the chance to raise it)
   if (*abortp) {
     // give bulk copies still in flight time to land before shared memory is released (bounded)
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1u);
   }
-  tc_fence_before();
-  __syncthreads();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);

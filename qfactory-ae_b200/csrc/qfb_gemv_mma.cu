@@ -219,6 +219,10 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   // lane r of warp 0 issues row r; warp 0 waits for the bytes, the barrier below publishes them
   __shared__ __align__(8) uint64_t xbar;
   __shared__ int xabort;
+  // With p.act == 1 the activations are silu(gate) * up of a fused gate/up tensor [m, 2k]: the gate
+  // and the up slices arrive by one bulk copy each and are combined in shared memory, with the
+  // arithmetic of the stand-alone kernel (silu in fp32 rounded to fp16, then one fp16 product).
+  __half* u_s = reinterpret_cast<__half*>(reinterpret_cast<char*>(smem) + p.act_offset);
   if (warp == 0) {
     const uint32_t bar = ptx::smem_u32(&xbar);
     const uint32_t row_bytes = (uint32_t)ncta * 256u;
@@ -226,16 +230,37 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       xabort = 0;
       ptx::mbar_init(bar, 1);
       ptx::fence_barrier_init();
-      ptx::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)p.m);
+      ptx::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)p.m * (p.act ? 2u : 1u) + (p.stall_test ? 16u : 0u));
     }
     __syncwarp();
-    if (lane < p.m)
-      ptx::tma_bulk_g2s(ptx::smem_u32(x_s + (size_t)lane * xstride), p.x + (size_t)lane * p.k + (size_t)bb * 128,
-                        row_bytes, bar);
+    if (lane < p.m) {
+      const __half* src = p.x + (size_t)lane * p.x_stride + (size_t)bb * 128;
+      ptx::tma_bulk_g2s(ptx::smem_u32(x_s + (size_t)lane * xstride), src, row_bytes, bar);
+      if (p.act) ptx::tma_bulk_g2s(ptx::smem_u32(u_s + (size_t)lane * xstride), src + p.k, row_bytes, bar);
+    }
     // bounded: a copy that never lands raises the status word instead of hanging the CTA
-    if (!ptx::mbar_wait(bar, 0, &xabort) && lane == 0 && p.status) atomicExch(p.status, 1u);
+    if (!ptx::mbar_wait(bar, 0, &xabort, 0, p.stall_test ? 200000LL : ptx::kWaitLimitCycles) && lane == 0 && p.status)
+      atomicExch(p.status, 1u);
   }
   __syncthreads();
+  if (p.act) {
+    const int vec_row = ncta * 16;  // 16-byte vectors per row of the slice
+    for (int i = tid; i < p.m * vec_row; i += blockDim.x) {
+      const int r = i / vec_row, j = i - r * vec_row;
+      uint4* gp = reinterpret_cast<uint4*>(x_s + (size_t)r * xstride) + j;
+      const uint4 a = *gp, b = *(reinterpret_cast<const uint4*>(u_s + (size_t)r * xstride) + j);
+      const uint32_t ua[4] = {a.x, a.y, a.z, a.w}, ub[4] = {b.x, b.y, b.z, b.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(as_h2(ua[q]));
+        const __half2 sg = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+        o[q] = as_u32(__hmul2(sg, as_h2(ub[q])));
+      }
+      *gp = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    __syncthreads();
+  }
 
   // activation row each batch tile of this thread reads (rows >= m repeat the last valid row;
   // their output columns are never stored)
@@ -530,7 +555,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // Two register budgets of the same body: CTAs of up to 256 threads with 128 registers per thread
 // (two per SM, 16 warps), and CTAs of up to 128 threads with 96 (five per SM, 20 warps: measured
 // 7-9 % faster on layers with many row tiles, slower as 256-thread CTAs, which fit only twice
-// either way).
+// either way).  Tighter budgets that would leave room for the next launch's CTAs to become
+// resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
+// k-step loop and were 5-70 % slower on every Llama-7B layer shape.
 template <int BITS, int NT, int RB, bool SEG64>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
   gemv_mma_body<BITS, NT, RB, SEG64>(p);

@@ -53,6 +53,11 @@ struct MmaParams {
   int quads_per_owner;   // cluster reduction: ceil(m * 32 / S) quads (4 rows of one batch column) per CTA of the cluster
   uint32_t qper_magic;   // ceil(2^32 / quads_per_owner): q / quads_per_owner = umulhi(q, qper_magic) for q < 2^9
   unsigned* status;      // may be null; set to 1 when a bounded wait ran out
+  int x_stride;          // halfs between activation rows (k, or 2k for a fused gate/up tensor)
+  int act;               // 1: activations = silu(x[:, :k]) * x[:, k:2k], combined while they are staged
+  int act_offset;        // byte offset of the up-slice staging region in dynamic shared memory (act only)
+  int stall_test;        // 1 (QFB_FLAG_TEST_STALLED_WAIT): the activation barrier expects 16 bytes that never
+                         // come and gives up after ~100 us, so that the bounded-wait path can be tested
 };
 // CTAs of the mma.sync GEMV of up to this many threads run the 96-register build (five per SM)
 constexpr int kMmaSmallBlock = 128;
@@ -83,6 +88,8 @@ struct TcParams {
   int full_units;            // (row tile, batch tile) units that run whole, one CTA each
   int tail_units;            // units that are cut; partial = [tail_split][tail_units][batch tile][128] fp32
   int mtiles;                // batch tiles per row tile (unit = tile * mtiles + batch tile)
+  int stall_test;            // 1 (QFB_FLAG_TEST_STALLED_WAIT): the first weight stage's barrier expects 16 bytes
+                             // that never come; every wait gives up after ~100 us (bounded-wait path under test)
 };
 // activations [m, k] fp16 row-major as a 2-D tiled tensor map with boxes of {64, nb}, 128-byte swizzle
 cudaError_t launch_gemm_tc(const CUtensorMap& tmap_x, const TcParams& p, int bits, int nb, bool post, int decode_groups,

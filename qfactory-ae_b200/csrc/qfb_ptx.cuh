@@ -46,7 +46,7 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 // issue slots and ALU-pipe cycles that the decode warps of the same SM need (measured: idle
 // roles polled away more instructions than the decode itself executed).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned backoff_ns = 0) {
+                                          unsigned backoff_ns = 0, long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int it = 0;
@@ -54,7 +54,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((++it & 15) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }

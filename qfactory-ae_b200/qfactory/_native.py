@@ -18,12 +18,13 @@ FLAG_PDL = 1
 FLAG_FORCE_SIMT = 2
 FLAG_FORCE_TENSOR = 4
 FLAG_NO_SYNC = 8
+FLAG_TEST_STALLED_WAIT = 16
 
 EXPORTS = (
     "qfb_version", "qfb_status_string", "qfb_last_cuda_error",
     "qfb_packed_weight_bytes", "qfb_packed_scale_bytes", "qfb_packed_zero_bytes",
     "qfb_workspace_bytes", "qfb_workspace_init",
-    "qfb_linear_forward", "qfb_linear_forward_host", "qfb_select_kernel",
+    "qfb_linear_forward", "qfb_linear_forward_host", "qfb_linear_silu_mul_forward", "qfb_select_kernel",
     "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_set_tensor_decode_groups", "qfb_set_tensor_batch_tile", "qfb_set_cluster_reduce", "qfb_read_status",
     "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
@@ -82,6 +83,8 @@ def lib() -> ctypes.CDLL:
     L.qfb_workspace_init.argtypes = [vp, sz, vp]
     L.qfb_linear_forward.restype = i32
     L.qfb_linear_forward.argtypes = [LP, vp, i32, vp, vp, sz, u32, vp]
+    L.qfb_linear_silu_mul_forward.restype = i32
+    L.qfb_linear_silu_mul_forward.argtypes = [LP, vp, i32, vp, vp, sz, u32, vp]
     L.qfb_linear_forward_host.restype = i32
     L.qfb_linear_forward_host.argtypes = [LP, vp, i32, vp, vp, vp, vp, sz, u32, vp]
     L.qfb_select_kernel.restype = i32

@@ -125,6 +125,7 @@ class QuantDecoder(torch.nn.Module):
                  native_ops: bool = True, weights: str = "packed", collective: str = "auto"):
         super().__init__()
         self.native_ops = native_ops
+        self.fuse_silu = True   # False: SiLU * up as a launch of its own (tests compare the two)
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         assert weights in ("packed", "seeded", "seeded_keep") and collective in ("auto", "nccl", "none")
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
@@ -248,9 +249,16 @@ class QuantDecoder(torch.nn.Module):
                 h = self._add_rms(x, o.view(B, T, -1), blk.norm2)     # x += o, then the norm
             gu = blk.gate_up(h.view(R, -1))
             half = gu.shape[-1] // 2
-            act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
+            # SiLU(gate) * up is combined inside the down projection's activation staging where that
+            # kernel serves the batch (`down` below); otherwise as a launch of its own
+            fuse_act = self.native_ops and self.fuse_silu and blk.down.silu_mul_supported(R)
+            if fuse_act:
+                down = lambda out=None: blk.down.forward_silu_mul(gu, out=out)
+            else:
+                act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
+                down = lambda out=None: blk.down(act, out=out)
             if fused:
-                blk.down(act, out=self.comm.slot(1, R))
+                down(out=self.comm.slot(1, R))
                 last = li + 1 == nblk
                 if not last:
                     h = self.comm.allreduce_add_rmsnorm(1, x2, self.blocks[li + 1].norm1, R)
@@ -261,7 +269,7 @@ class QuantDecoder(torch.nn.Module):
                     h = None
                 pending = None
             else:
-                dn = blk.down(act)
+                dn = down()
                 self._reduce(dn)                                      # row parallel
                 pending = dn.view(B, T, -1)                           # added by the next layer's (or the final) norm
                 h = None

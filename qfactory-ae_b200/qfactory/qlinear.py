@@ -117,6 +117,39 @@ class _PackedLinear(torch.nn.Module):
             _native.check(st, "qfb_linear_forward")
         return out.view(*lead, self.out_features)
 
+    def silu_mul_supported(self, rows: int) -> bool:
+        """True when `forward_silu_mul` runs as ONE kernel for `rows` activation rows."""
+        return self.packed_layout == layout.LAYOUT_FRAGMENT and 0 < rows <= 16
+
+    def forward_silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """(silu(gate) * up) @ dequant(W)^T for gate_up [..., 2 * in_features] = [gate | up], the down
+        projection of a gated MLP with its activation fused in (reference:
+        third_party/vllm-bitblas/vllm/model_executor/models/llama.py:91-96 runs the activation as a
+        launch of its own).  One kernel on fragment-layout layers up to 16 rows; otherwise the
+        element-wise kernel followed by `forward`.  Both give the same bits."""
+        if self._desc is None:
+            self._prepare()
+        assert gate_up.dtype == torch.float16 and gate_up.shape[-1] == 2 * self.in_features
+        g2 = gate_up.reshape(-1, 2 * self.in_features)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        M = g2.shape[0]
+        if not self.silu_mul_supported(M):
+            from . import ops
+
+            return self.forward(ops.silu_mul(g2), out=out)
+        if out is None:
+            out = torch.empty(M, self.out_features, dtype=torch.float16, device=g2.device)
+        else:
+            assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() == M * self.out_features
+        with torch.cuda.device(g2.device):
+            st = self._lib.qfb_linear_silu_mul_forward(
+                ctypes.byref(self._desc), g2.data_ptr(), M, out.data_ptr(), self._ws.data_ptr(), self._ws_bytes, self.flags,
+                torch.cuda.current_stream(g2.device).cuda_stream)
+        if st != 0:
+            _native.check(st, "qfb_linear_silu_mul_forward")
+        return out.view(*gate_up.shape[:-1], self.out_features)
+
     def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor | None = None, sync: bool = True) -> torch.Tensor:
         """Host-buffer entry: `x_host` (CPU fp16, ideally pinned) is copied in, the result is
         copied back into `y_host` (CPU fp16) and the stream is synchronised.  With `sync=False` the

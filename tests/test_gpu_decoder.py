@@ -98,3 +98,14 @@ def test_seeded_decoder_matches_the_oracle_dequantised_network():
         want = _reference_logits(model, tokens, weights)
     assert torch.isfinite(got).all()
     assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+
+
+def test_fused_and_unfused_activation_give_the_same_tokens_and_logits():
+    cfg = DecoderConfig(layers=2, d_model=512, n_heads=8, n_kv_heads=2, d_ff=1024, vocab=1000, max_len=64, scale_boost=40.0)
+    a = QuantDecoder(cfg, device="cuda", seed=5, batch=2, weights="seeded")
+    b = QuantDecoder(cfg, device="cuda", seed=5, batch=2, weights="seeded")
+    b.fuse_silu = False
+    tok = torch.randint(0, cfg.vocab, (2, 1), device="cuda")
+    pos = torch.zeros(1, dtype=torch.long, device="cuda")
+    with torch.no_grad():
+        assert torch.equal(a(tok, pos), b(tok, pos))   # the fused staging computes the same bits

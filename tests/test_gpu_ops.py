@@ -174,3 +174,46 @@ def test_decode_step_with_native_attention_matches_torch_ops():
             ya, yb = a(tok, pos).float(), b(tok, pos).float()
             assert torch.isfinite(ya).all()
             assert (ya - yb).abs().max() <= 5e-3 * yb.abs().max()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K,GS,bits", [(384, 1024, 128, 4), (4096, 11008, 128, 4), (200, 2048, 64, 4), (512, 3584, 128, 8), (256, 1024, -1, 2)])
+def test_down_projection_with_fused_silu_mul(M, N, K, GS, bits):
+    """silu(gate) * up combined inside the GEMV's activation staging: bit-identical to the element-wise
+    kernel followed by the plain forward, and within the parity bar of the oracle applied to the
+    fp16 activation the reference's serving stack would compute."""
+    import numpy as np
+
+    from oracle import qf_oracle as O
+    from qfactory import QLinear, _native, ops
+
+    _, q, s, z = O.make_case(M, N, K, bits, GS, False, seed=M + N)
+    if GS == -1:
+        layer = QLinear.init(M, K, N, bits, q.cuda(), layout="fragment")
+    else:
+        layer = QLinear.init(M, K, N, bits, q.cuda(), GS, s.cuda(), z.cuda(), layout="fragment")
+    g = torch.Generator().manual_seed(M * 7 + K)
+    gu = torch.randn(M, 2 * K, generator=g).half()
+    assert layer.silu_mul_supported(M)
+    y = layer.forward_silu_mul(gu.cuda())
+    assert _native.last_launch()["kernel"] == 3
+    act = ops.silu_mul(gu.cuda())
+    assert torch.equal(y, layer(act))
+    # the oracle on the activation as torch computes it (fp32 silu rounded to fp16, fp16 product)
+    act_ref = torch.nn.functional.silu(gu[:, :K].float()).half() * gu[:, K:]
+    _, yex = O.reference_forward(act_ref, q, s, z, bits)
+    assert np.abs(y.float().cpu().numpy() - yex).max() <= 1e-2 * np.abs(yex).max()
+
+
+def test_fused_silu_mul_falls_back_above_16_rows_and_on_tile_layers():
+    from oracle import qf_oracle as O
+    from qfactory import QLinear, ops
+
+    M, N, K = 20, 256, 1024
+    _, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=3)
+    gu = torch.randn(M, 2 * K, generator=torch.Generator().manual_seed(1)).half().cuda()
+    for lay, rows in (("fragment", 20), ("tile", 4)):
+        layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout=lay)
+        assert not layer.silu_mul_supported(rows)
+        y = layer.forward_silu_mul(gu[:rows])
+        assert torch.equal(y, layer(ops.silu_mul(gu[:rows].contiguous())))
