@@ -605,7 +605,22 @@ def main():
             host_s = time.perf_counter() - t0
             torch.cuda.synchronize()
             total_s = time.perf_counter() - t0
-            extras["eager"] = {"layer": "4096x4096 M=1", "host_us_per_call": round(host_s / 400 * 1e6, 2),
+            # the same through the C ABI alone (ctypes, arguments prepared once): validation, plan lookup, launch
+            import ctypes
+
+            fwd, dref = _native.lib().qfb_linear_forward, ctypes.byref(L._desc)
+            args = (dref, xe.data_ptr(), 1, ye.data_ptr(), L._ws.data_ptr(), L._ws_bytes, flags,
+                    torch.cuda.current_stream(dev).cuda_stream)
+            for _ in range(20):
+                fwd(*args)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(400):
+                fwd(*args)
+            abi_s = time.perf_counter() - t0
+            torch.cuda.synchronize()
+            extras["eager"] = {"layer": "4096x4096 M=1", "module_host_us_per_call": round(host_s / 400 * 1e6, 2),
+                               "abi_host_us_per_call": round(abi_s / 400 * 1e6, 2),
                                "us_per_call_with_device": round(total_s / 400 * 1e6, 2)}
             del L
             # same-box GPU baseline: the reference project's own kernel (its default and its scheduled

@@ -270,6 +270,18 @@ int qfb_silu_mul(const void* gate_up, void* out, int rows, int half, void* strea
  */
 int qfb_decode_attention(const void* qkv, const void* pos, const void* k_cache, const void* v_cache, void* out,
                          int batch, int q_heads, int kv_heads, int head_dim, int max_len, void* stream);
+/*
+ * The same with the single-token work of qfb_rope_cache fused in: qkv holds the UN-rotated queries, key
+ * and value of the new token; the kernel rotates the queries as it stages them, rotates the new key,
+ * attends over the cached keys 0 .. pos[0] - 1 plus the new one, and writes the rotated key and the
+ * value into the caches at position pos[0] (one CTA per batch row and key/value head does the write).
+ * qkv is not modified.  Same arithmetic, bit for bit, as qfb_rope_cache followed by
+ * qfb_decode_attention; one launch less per decoder layer.  cos, sin fp16 [max_len, hd / 2], 8-byte
+ * aligned.  A position outside [0, max_len) is not rotated and not written.
+ */
+int qfb_decode_attention_rope(const void* qkv, const void* cos, const void* sin, const void* pos, void* k_cache,
+                              void* v_cache, void* out, int batch, int q_heads, int kv_heads, int head_dim,
+                              int max_len, void* stream);
 
 /*
  * One-shot all-reduce over peer memory for the row-parallel linears (O and down projections) of a

@@ -229,7 +229,7 @@ static int run_tc(const LayerView& v, const __half* x, int m, __half* y, void* w
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return QFB_ERR_CUDA;
-  TcParams p;
+  TcParams p = {};
   p.qw = v.qw;
   p.qs = v.qs;
   p.qz = v.qz;
@@ -325,7 +325,7 @@ static int run_gemv(const LayerView& v, const __half* x, int m, __half* y, void*
   for (int m0 = 0; m0 < m; m0 += kMaxSimtRows) {
     const int rows = std::min(kMaxSimtRows, m - m0);
     const GemvPlan pl = plan_gemv(v, rows);
-    GemvParams p;
+    GemvParams p = {};
     p.qw = v.qw;
     p.qs = v.qs;
     p.qz = v.qz;
@@ -481,7 +481,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     const int rows = std::min(kMaxMmaRows, m - m0);
     const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits, act);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
-    MmaParams p;
+    MmaParams p = {};
     p.qw = v.qw;
     p.qs = v.qs;
     p.qz = v.qz;
@@ -543,6 +543,24 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
   }
   return QFB_OK;
 }
+
+// Shared with the allocation-free entry point (qfb_static_scratch.cu): the argument checks of
+// qfb_linear_forward without a launch, the recording of a CUDA error for qfb_last_cuda_error, and the
+// bytes at the start of a scratch area that must be zero before a launch (status word + counters).
+int validate_forward_args(const qfb_layer* layer, const void* x, int m, const void* y) {
+  LayerView v;
+  const int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (m < 0) return QFB_ERR_BAD_SHAPE;
+  if (m > 0 && (!x || !y)) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(y) & 1u)) return QFB_ERR_MISALIGNED;
+  return QFB_OK;
+}
+int record_cuda_error(cudaError_t e) {
+  if (e != cudaSuccess) (void)cudaGetLastError();  // clear the runtime's pending error as well
+  return check_cuda(e);
+}
+size_t scratch_clear_bytes(int n) { return partial_offset(padded_rows(n) / kTileRows); }
 
 // Exact scratch need of the CUDA-core split-K kernel for `m` rows under the built-in plan
 // (0 for invalid shapes); used by the allocation-free entry point.
@@ -819,9 +837,27 @@ int qfb_decode_attention(const void* qkv, const void* pos, const void* k_cache, 
   if (!aligned16(qkv) || !aligned16(k_cache) || !aligned16(v_cache) || (reinterpret_cast<uintptr_t>(out) & 1u))
     return QFB_ERR_MISALIGNED;
   if (batch == 0) return QFB_OK;
-  return check_cuda(launch_decode_attention(static_cast<const __half*>(qkv), static_cast<const __half*>(k_cache),
-                                            static_cast<const __half*>(v_cache), static_cast<const long long*>(pos),
+  return check_cuda(launch_decode_attention(static_cast<const __half*>(qkv),
+                                            const_cast<__half*>(static_cast<const __half*>(k_cache)),
+                                            const_cast<__half*>(static_cast<const __half*>(v_cache)),
+                                            static_cast<const long long*>(pos), static_cast<__half*>(out), batch, q_heads,
+                                            kv_heads, max_len, nullptr, nullptr, static_cast<cudaStream_t>(stream)));
+}
+
+int qfb_decode_attention_rope(const void* qkv, const void* cosv, const void* sinv, const void* pos, void* k_cache,
+                              void* v_cache, void* out, int batch, int q_heads, int kv_heads, int head_dim, int max_len,
+                              void* stream) {
+  if (!qkv || !cosv || !sinv || !pos || !k_cache || !v_cache || !out) return QFB_ERR_NULL_POINTER;
+  if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || max_len <= 0) return QFB_ERR_BAD_SHAPE;
+  if (!decode_attention_supported(q_heads, kv_heads, head_dim, max_len)) return QFB_ERR_UNSUPPORTED;
+  if (!aligned16(qkv) || !aligned16(k_cache) || !aligned16(v_cache) || (reinterpret_cast<uintptr_t>(out) & 1u) ||
+      (reinterpret_cast<uintptr_t>(cosv) & 7u) || (reinterpret_cast<uintptr_t>(sinv) & 7u))
+    return QFB_ERR_MISALIGNED;
+  if (batch == 0) return QFB_OK;
+  return check_cuda(launch_decode_attention(static_cast<const __half*>(qkv), static_cast<__half*>(k_cache),
+                                            static_cast<__half*>(v_cache), static_cast<const long long*>(pos),
                                             static_cast<__half*>(out), batch, q_heads, kv_heads, max_len,
+                                            static_cast<const __half*>(cosv), static_cast<const __half*>(sinv),
                                             static_cast<cudaStream_t>(stream)));
 }
 

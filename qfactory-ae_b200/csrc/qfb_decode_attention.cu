@@ -47,12 +47,34 @@ __device__ __forceinline__ void attn_st_cluster(uint32_t local_addr, int rank, f
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-template <int G>
-__global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __restrict__ qkv, const __half* __restrict__ kc,
-                                                               const __half* __restrict__ vc,
+// rotary embedding of one pair (x1, x2) by (c, s): every product and sum an fp16 operation, as
+// rope_cache_kernel computes it (the _rn forms keep the compiler from fusing product and sum)
+__device__ __forceinline__ uint32_t rope_pair(uint32_t x, __half c, __half s) {
+  const __half x1 = __low2half(as_h2(x)), x2 = __high2half(as_h2(x));
+  return as_u32(__halves2half2(__hsub_rn(__hmul_rn(x1, c), __hmul_rn(x2, s)), __hadd_rn(__hmul_rn(x1, s), __hmul_rn(x2, c))));
+}
+// 8 consecutive halfs (4 pairs, frequencies i0 .. i0 + 3) rotated by the angles of one position
+__device__ __forceinline__ uint4 rope_vec(uint4 v, const __half* cosp, const __half* sinp, int i0) {
+  const uint2 c = *reinterpret_cast<const uint2*>(cosp + i0), s = *reinterpret_cast<const uint2*>(sinp + i0);
+  const __half2 c01 = as_h2(c.x), c23 = as_h2(c.y), s01 = as_h2(s.x), s23 = as_h2(s.y);
+  v.x = rope_pair(v.x, __low2half(c01), __low2half(s01));
+  v.y = rope_pair(v.y, __high2half(c01), __high2half(s01));
+  v.z = rope_pair(v.z, __low2half(c23), __low2half(s23));
+  v.w = rope_pair(v.w, __high2half(c23), __high2half(s23));
+  return v;
+}
+
+// ROPE: the kernel also does what rope_cache_kernel does for a single new token: the queries are
+// rotated as they are staged, the new key is rotated and, with the new value, used from shared
+// memory by the CTAs whose key range holds the new position, and ONE CTA of the cluster writes
+// both into the caches for the steps to come.  (qkv itself is left un-rotated.)
+template <int G, bool ROPE>
+__global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __restrict__ qkv, __half* __restrict__ kc,
+                                                               __half* __restrict__ vc,
                                                                const long long* __restrict__ pos, __half* __restrict__ out,
                                                                int hq, int hkv, int max_len, int chunk_max,
-                                                               float scale_log2e) {
+                                                               float scale_log2e, const __half* __restrict__ cosv,
+                                                               const __half* __restrict__ sinv) {
   static_assert(G >= 1 && G <= 8, "one 16-row MMA tile holds the query heads of a group");
   extern __shared__ uint4 smem_raw[];
   __half* q_s = reinterpret_cast<__half*>(smem_raw);                          // [8][kQStride]
@@ -60,6 +82,7 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
   float* stat = s_s + G * chunk_max;                                          // [G] max, [G] sum
   float* pv = stat + 16;                                                      // [4 warps][G][128] partial outputs
   float* recv = pv + 4 * G * kHD;                                             // [NS][G][kRecvStride] (used in the first CTA)
+  __shared__ __align__(16) __half knew_s[kHD], vnew_s[kHD];                   // ROPE: the new token's rotated key, its value
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -70,7 +93,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
   // was the fastest of the four variants measured.)
 
   // this CTA's keys: [k0, k0 + nk) of the n = pos + 1 attended ones, in chunks of a multiple of 8
-  const int n = min((int)pos[0] + 1, max_len);
+  const long long p_new = pos[0];
+  const int n = min((int)p_new + 1, max_len);
   const int chunk = min(chunk_max, (((n + NS - 1) / NS) + 7) & ~7);
   const int k0 = z * chunk;
   const int nk = max(0, min(n, k0 + chunk) - k0);
@@ -82,8 +106,27 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
   for (int i = tid; i < 8 * (kHD / 8); i += blockDim.x) {
     const int r = i / (kHD / 8), c = i % (kHD / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < G) v = *reinterpret_cast<const uint4*>(qkv + ((size_t)b * H + (size_t)kvh * G + r) * kHD + c * 8);
+    if (r < G) {
+      v = *reinterpret_cast<const uint4*>(qkv + ((size_t)b * H + (size_t)kvh * G + r) * kHD + c * 8);
+      if (ROPE && p_new >= 0 && p_new < max_len) v = rope_vec(v, cosv + (size_t)p_new * (kHD / 2), sinv + (size_t)p_new * (kHD / 2), c * 4);
+    }
     *reinterpret_cast<uint4*>(q_s + r * kQStride + c * 8) = v;
+  }
+  // the key position of the new token inside this CTA's range (or -1): taken from shared memory, not from the cache
+  int j_new = -1;
+  if (ROPE && p_new >= 0 && p_new < max_len) {
+    const int pn = (int)p_new;
+    if (pn >= k0 && pn < k0 + nk) j_new = pn - k0;
+    if (j_new >= 0 && tid < 32) {   // 16 threads rotate the key, 16 copy the value
+      const int c = tid & 15;
+      const __half* src = qkv + ((size_t)b * H + hq + (tid < 16 ? 0 : hkv) + kvh) * kHD + c * 8;
+      uint4 v = *reinterpret_cast<const uint4*>(src);
+      if (tid < 16) v = rope_vec(v, cosv + (size_t)pn * (kHD / 2), sinv + (size_t)pn * (kHD / 2), c * 4);
+      *reinterpret_cast<uint4*>((tid < 16 ? knew_s : vnew_s) + c * 8) = v;
+      // the CTA that owns the position also stores both for the steps to come
+      __half* dst = (tid < 16 ? kc : vc) + (((size_t)b * hkv + kvh) * (size_t)max_len + (size_t)pn) * kHD + c * 8;
+      *reinterpret_cast<uint4*>(dst) = v;
+    }
   }
   __syncthreads();
 
@@ -95,7 +138,9 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const int j = rg + 8 * u;
-    v_first[u] = j < nk ? *reinterpret_cast<const uint4*>(vr + (size_t)j * kHD) : make_uint4(0, 0, 0, 0);
+    v_first[u] = j < nk ? (ROPE && j == j_new ? *reinterpret_cast<const uint4*>(vnew_s + cg * 8)
+                                              : *reinterpret_cast<const uint4*>(vr + (size_t)j * kHD))
+                        : make_uint4(0, 0, 0, 0);
   }
 
   // ---- scores: S[head][key] = q . k * scale, 8 keys per MMA tile, the warps take alternate tiles ----
@@ -109,7 +154,7 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
     const int ntiles = (nk + 7) >> 3;
     for (int ti = warp; ti < ntiles; ti += 4) {
       const int key = min(k0 + ti * 8 + g, n - 1);  // (keys past the range are read in bounds and masked below)
-      const __half* kr = kbase + (size_t)key * kHD + 2 * t;
+      const __half* kr = (ROPE && key - k0 == j_new) ? knew_s + 2 * t : kbase + (size_t)key * kHD + 2 * t;
       uint32_t kb[8][2];
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
@@ -169,7 +214,9 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
       for (int u = 0; u < 4; ++u) {
         const int j = j0 + 8 * u;
         if (j0 == rg) v[u] = v_first[u];
-        else v[u] = j < nk ? *reinterpret_cast<const uint4*>(vr + (size_t)j * kHD) : make_uint4(0, 0, 0, 0);
+        else v[u] = j < nk ? (ROPE && j == j_new ? *reinterpret_cast<const uint4*>(vnew_s + cg * 8)
+                                                 : *reinterpret_cast<const uint4*>(vr + (size_t)j * kHD))
+                           : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -243,9 +290,9 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const __half* __r
   }
 }
 
-template <int G>
-cudaError_t launch_g(const __half* qkv, const __half* kc, const __half* vc, const long long* pos, __half* out, int B, int hq,
-                     int hkv, int max_len, cudaStream_t st) {
+template <int G, bool ROPE>
+cudaError_t launch_g(const __half* qkv, __half* kc, __half* vc, const long long* pos, __half* out, int B, int hq,
+                     int hkv, int max_len, const __half* cosv, const __half* sinv, cudaStream_t st) {
   // up to 8 key splits, at least 64 keys of capacity each, no more than fill the device
   // (more CTAs than about four per SM only add launch and merge work: measured at 16 rows);
   // but never so few that the scores of a split outgrow the shared memory of a CTA
@@ -262,7 +309,7 @@ cudaError_t launch_g(const __half* qkv, const __half* kc, const __half* vc, cons
   int chunk_max = 0;
   const size_t smem = smem_for(ns, &chunk_max);
   if (smem > kSmemBudget) return cudaErrorInvalidConfiguration;  // (not reachable for max_len <= 16384)
-  auto kern = decode_attention_kernel<G>;
+  auto kern = decode_attention_kernel<G, ROPE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -280,7 +327,7 @@ cudaError_t launch_g(const __half* qkv, const __half* kc, const __half* vc, cons
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const float scale_log2e = 1.4426950408889634f / sqrtf((float)kHD);
-  return cudaLaunchKernelEx(&cfg, kern, qkv, kc, vc, pos, out, hq, hkv, max_len, chunk_max, scale_log2e);
+  return cudaLaunchKernelEx(&cfg, kern, qkv, kc, vc, pos, out, hq, hkv, max_len, chunk_max, scale_log2e, cosv, sinv);
 }
 
 }  // namespace
@@ -291,15 +338,21 @@ bool decode_attention_supported(int hq, int hkv, int hd, int max_len) {
   return gq == 1 || gq == 2 || gq == 4 || gq == 8;
 }
 
-cudaError_t launch_decode_attention(const __half* qkv, const __half* kc, const __half* vc, const long long* pos, __half* out,
-                                    int B, int hq, int hkv, int max_len, cudaStream_t st) {
+cudaError_t launch_decode_attention(const __half* qkv, __half* kc, __half* vc, const long long* pos, __half* out,
+                                    int B, int hq, int hkv, int max_len, const __half* cosv, const __half* sinv,
+                                    cudaStream_t st) {
+#define QFB_ATTN_CASE(GQ)                                                                                         \
+  case GQ:                                                                                                        \
+    return cosv ? launch_g<GQ, true>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, cosv, sinv, st)                 \
+                : launch_g<GQ, false>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, nullptr, nullptr, st);
   switch (hq / hkv) {
-    case 1: return launch_g<1>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, st);
-    case 2: return launch_g<2>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, st);
-    case 4: return launch_g<4>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, st);
-    case 8: return launch_g<8>(qkv, kc, vc, pos, out, B, hq, hkv, max_len, st);
+    QFB_ATTN_CASE(1)
+    QFB_ATTN_CASE(2)
+    QFB_ATTN_CASE(4)
+    QFB_ATTN_CASE(8)
     default: return cudaErrorInvalidValue;
   }
+#undef QFB_ATTN_CASE
 }
 
 }  // namespace qfb

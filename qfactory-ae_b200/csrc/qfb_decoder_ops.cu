@@ -5,6 +5,8 @@
 // The reference runs these through its serving stack's own kernels
 // (third_party/vllm-bitblas/vllm/model_executor/models/llama.py:60-120, 260-285); they sit on
 // either side of the quantized linears this library replaces.
+#include <algorithm>
+
 #include "qfb_common.cuh"
 #include "qfb_kernels.h"
 
@@ -65,6 +67,79 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* __restrict__ x, co
       o[j] = as_u32(__hmul2(n, as_h2(gw[j])));
     }
     yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// The same norm for rows of up to 16384 features, as a chain of two memory round trips instead of
+// eight: up to 1024 threads hold the whole row in registers (VPT 16-byte vectors each), so the
+// loads of the row, of the residual and of the weight are all in flight together, the sum of
+// squares is one block reduction, and nothing is read twice.  A decode step has one row per batch
+// entry and two norms per layer: with one 256-thread CTA looping over the row the kernel took 7 us,
+// a fixed cost on the critical path between two linears.
+template <int VPT>
+__global__ void __launch_bounds__(1024) rmsnorm_row_kernel(__half* __restrict__ x, const __half* __restrict__ res,
+                                                           const __half* __restrict__ w, __half* __restrict__ y, int d,
+                                                           float eps) {
+  grid_launch_dependents();
+  const int row = blockIdx.x, tid = threadIdx.x, nv = d >> 3;
+  // the norm weight never depends on the preceding kernel: fetched before the wait
+  uint4 g[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * blockDim.x;
+    g[i] = v < nv ? reinterpret_cast<const uint4*>(w)[v] : make_uint4(0, 0, 0, 0);
+  }
+  grid_dependency_wait();
+  uint4* xr = reinterpret_cast<uint4*>(x + (size_t)row * d);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + (size_t)row * d) : nullptr;
+  uint4 xv[VPT], rv[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * blockDim.x;
+    xv[i] = v < nv ? xr[v] : make_uint4(0, 0, 0, 0);
+    rv[i] = (rr && v < nv) ? rr[v] : make_uint4(0, 0, 0, 0);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * blockDim.x;
+    if (rr) {
+      xv[i].x = as_u32(__hadd2(as_h2(xv[i].x), as_h2(rv[i].x)));
+      xv[i].y = as_u32(__hadd2(as_h2(xv[i].y), as_h2(rv[i].y)));
+      xv[i].z = as_u32(__hadd2(as_h2(xv[i].z), as_h2(rv[i].z)));
+      xv[i].w = as_u32(__hadd2(as_h2(xv[i].w), as_h2(rv[i].w)));
+      if (v < nv) xr[v] = xv[i];
+    }
+    const uint32_t u[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(as_h2(u[j]));
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  __shared__ float red[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  for (int i = 0; i < nwarps; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / (float)d + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * d);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * blockDim.x;
+    if (v >= nv) continue;
+    const uint32_t u[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(as_h2(u[j]));
+      const __half2 n = __floats2half2_rn(f.x * rstd, f.y * rstd);
+      o[j] = as_u32(__hmul2(n, as_h2(gw[j])));
+    }
+    yr[v] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -160,6 +235,15 @@ cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sin
 
 cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half* y, int rows, int d, float eps,
                            cudaStream_t st) {
+  const int nv = d >> 3;
+  // few rows (a decode step): one CTA per row holding the row in registers; many rows or very long
+  // rows: the looping kernel, which keeps more CTAs per SM
+  if (rows <= 64 && nv <= 2048) {
+    const int vpt = nv > 1024 ? 2 : 1;
+    const unsigned block = (unsigned)std::min(1024, (((nv + vpt - 1) / vpt + 31) / 32) * 32);
+    if (vpt == 1) return launch_pdl(rmsnorm_row_kernel<1>, (unsigned)rows, block, st, x, res, w, y, d, eps);
+    return launch_pdl(rmsnorm_row_kernel<2>, (unsigned)rows, block, st, x, res, w, y, d, eps);
+  }
   return launch_pdl(rmsnorm_kernel, (unsigned)rows, 256, st, x, res, w, y, d, eps);
 }
 

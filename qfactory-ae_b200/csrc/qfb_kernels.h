@@ -30,6 +30,9 @@ cudaError_t launch_gemv(const GemvParams& p, int bits, int mb, dim3 grid, int bl
 
 // exact scratch bytes the split-K GEMV needs for m rows (0 when the shape is invalid)
 size_t gemv_scratch_bytes(int m, int n, int k, int bits);
+// helpers shared with the allocation-free entry point
+int record_cuda_error(cudaError_t e);
+size_t scratch_clear_bytes(int n);
 
 // mma.sync split-K kernel over the fragment layout (2/4/8-bit, m <= 16 per launch)
 struct MmaParams {
@@ -101,8 +104,11 @@ cudaError_t launch_rmsnorm(__half* x, const __half* res, const __half* w, __half
 cudaError_t launch_silu_mul(const __half* gu, __half* out, int rows, int half, cudaStream_t st);
 // single-query attention over the static cache (qfb_decode_attention.cu)
 bool decode_attention_supported(int hq, int hkv, int hd, int max_len);
-cudaError_t launch_decode_attention(const __half* qkv, const __half* k_cache, const __half* v_cache, const long long* pos,
-                                    __half* out, int B, int hq, int hkv, int max_len, cudaStream_t st);
+// cosv / sinv non-null: the queries and the new key are rotated here and the new key / value are written
+// into the caches (the single-token work of launch_rope_cache, fused)
+cudaError_t launch_decode_attention(const __half* qkv, __half* k_cache, __half* v_cache, const long long* pos,
+                                    __half* out, int B, int hq, int hkv, int max_len, const __half* cosv, const __half* sinv,
+                                    cudaStream_t st);
 cudaError_t launch_rope_cache(__half* qkv, const __half* cosv, const __half* sinv, const long long* pos, __half* k_cache,
                               __half* v_cache, int B, int T, int hq, int hkv, int hd, int max_len, cudaStream_t st);
 

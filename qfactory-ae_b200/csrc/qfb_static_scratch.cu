@@ -12,6 +12,10 @@
 #include "qfb_common.cuh"
 #include "qfb_kernels.h"
 
+namespace qfb {
+int validate_forward_args(const qfb_layer* layer, const void* x, int m, const void* y);  // qfb_api.cu
+}
+
 namespace {
 
 // 8 MiB: enough for the split-K partial sums and counters of every Llama-7B-class layer at up
@@ -27,12 +31,15 @@ void* g_scratch_ptr[kMaxDevices] = {};
 // `g_static_scratch` is only a handle for the runtime, never a pointer a kernel may use.
 int scratch_for_current_device(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return QFB_ERR_CUDA;
+  const cudaError_t ge = cudaGetDevice(&dev);
+  if (ge != cudaSuccess) return qfb::record_cuda_error(ge);
   if (dev < 0 || dev >= kMaxDevices) return QFB_ERR_TOO_LARGE;
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_ptr[dev]) {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) return QFB_ERR_CUDA;
+    const cudaError_t se = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (se != cudaSuccess) return qfb::record_cuda_error(se);  // (readable through qfb_last_cuda_error)
+    if (!p) return QFB_ERR_CUDA;
     g_scratch_ptr[dev] = p;
   }
   *out = g_scratch_ptr[dev];
@@ -50,6 +57,9 @@ int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* 
   if (m < 0) return QFB_ERR_BAD_SHAPE;
   if (m == 0) return QFB_OK;
   if (layer->layout != QFB_LAYOUT_TILE) return QFB_ERR_UNSUPPORTED;  // the CUDA-core kernel reads the tile layout
+  // every argument is checked before the shared array is touched: a rejected call leaves it alone
+  const int va = qfb::validate_forward_args(layer, x, m, y);
+  if (va != QFB_OK) return va;
   // the split-K kernel handles 8 rows per pass and reuses the scratch between passes
   const size_t need = qfb::gemv_scratch_bytes(m, layer->n, layer->k, layer->bits);
   if (need == 0) return QFB_ERR_BAD_SHAPE;
@@ -59,8 +69,8 @@ int qfb_gemv_forward_static(const qfb_layer* layer, const void* x, int m, void* 
   if (st != QFB_OK) return st;
   // The array keeps whatever the previous call left behind.  The kernel needs its status word
   // and arrival counters to start at zero (the partial sums are always written before they are
-  // read), so that prefix is cleared on the caller's stream before the launch.
-  const int sc = qfb_workspace_init(scratch, need, stream);
+  // read), so that prefix, and only it, is cleared on the caller's stream before the launch.
+  const int sc = qfb_workspace_init(scratch, qfb::scratch_clear_bytes(layer->n), stream);
   if (sc != QFB_OK) return sc;
   return qfb_linear_forward(layer, x, m, y, scratch, kStaticScratchBytes,
                             (flags & ~QFB_FLAG_FORCE_TENSOR) | QFB_FLAG_FORCE_SIMT, stream);

@@ -28,7 +28,7 @@ EXPORTS = (
     "qfb_set_gemv_tuning", "qfb_get_last_launch", "qfb_set_tensor_min_batch", "qfb_set_tensor_split", "qfb_set_tensor_decode_groups", "qfb_set_tensor_batch_tile", "qfb_set_cluster_reduce", "qfb_read_status",
     "qfb_pack", "qfb_pack_layout", "qfb_layout_supported", "qfb_unpack_codes", "qfb_dequantize",
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
-    "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention",
+    "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention", "qfb_decode_attention_rope",
     "qfb_comm_buffer_bytes", "qfb_comm_max_rows", "qfb_comm_alloc", "qfb_comm_free", "qfb_comm_open", "qfb_comm_close",
     "qfb_comm_create", "qfb_comm_destroy", "qfb_comm_set_timeout_us", "qfb_comm_slot", "qfb_comm_flag_offset",
     "qfb_allreduce_add_rmsnorm", "qfb_comm_read_status", "qfb_comm_last_cuda_error",
@@ -126,6 +126,8 @@ def lib() -> ctypes.CDLL:
     L.qfb_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]
     L.qfb_decode_attention.restype = i32
     L.qfb_decode_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    L.qfb_decode_attention_rope.restype = i32
+    L.qfb_decode_attention_rope.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     L.qfb_quantize.restype = i32
     L.qfb_quantize.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp, vp]
     L.qfb_silu_mul.restype = i32

@@ -126,6 +126,7 @@ class QuantDecoder(torch.nn.Module):
         super().__init__()
         self.native_ops = native_ops
         self.fuse_silu = True   # False: SiLU * up as a launch of its own (tests compare the two)
+        self.fuse_rope = True   # False: rotary embedding + cache write as a launch of its own before the attention
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         assert weights in ("packed", "seeded", "seeded_keep") and collective in ("auto", "nccl", "none")
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
@@ -223,21 +224,27 @@ class QuantDecoder(torch.nn.Module):
                 h = self._add_rms(x, pending, blk.norm1) if pending is not None else self._rms(x, blk.norm1)
             qkv = blk.qkv(h.view(R, -1)).view(B, T, blk.hq + 2 * blk.hkv, blk.hd)
             q, k, v = qkv[:, :, : blk.hq], qkv[:, :, blk.hq : blk.hq + blk.hkv], qkv[:, :, blk.hq + blk.hkv :]
-            if self.native_ops:
-                ops.rope_cache(qkv, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)
+            native_attn = self.native_ops and T == 1 and ops.decode_attention_supported(blk.hq, blk.hkv, blk.hd, cfg.max_len)
+            if native_attn and self.fuse_rope:
+                # one launch: rotary embedding of the queries and the new key, cache write, attention
+                att2d = ops.decode_attention_rope(qkv, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li],
+                                                  blk.hq, blk.hkv)                                            # [B, hq * hd]
             else:
-                q, k = self._rope(q, pos), self._rope(k, pos)
-                self.k_cache[li].index_copy_(2, pos, k.transpose(1, 2))
-                self.v_cache[li].index_copy_(2, pos, v.transpose(1, 2))
-            if self.native_ops and T == 1 and ops.decode_attention_supported(blk.hq, blk.hkv, blk.hd, cfg.max_len):
-                att2d = ops.decode_attention(qkv, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)   # [B, hq * hd]
-            else:
-                if mask is None:
-                    # causal mask over the whole static cache: key j visible to query i iff j <= pos[i]
-                    mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
-                att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
-                                                     attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
-                att2d = att.transpose(1, 2).reshape(R, -1)
+                if self.native_ops:
+                    ops.rope_cache(qkv, self.cos, self.sin, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)
+                else:
+                    q, k = self._rope(q, pos), self._rope(k, pos)
+                    self.k_cache[li].index_copy_(2, pos, k.transpose(1, 2))
+                    self.v_cache[li].index_copy_(2, pos, v.transpose(1, 2))
+                if native_attn:
+                    att2d = ops.decode_attention(qkv, pos, self.k_cache[li], self.v_cache[li], blk.hq, blk.hkv)   # [B, hq * hd]
+                else:
+                    if mask is None:
+                        # causal mask over the whole static cache: key j visible to query i iff j <= pos[i]
+                        mask = torch.arange(cfg.max_len, device=x.device)[None, :] <= pos[:, None]   # [T, max_len]
+                    att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
+                                                         attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
+                    att2d = att.transpose(1, 2).reshape(R, -1)
             if fused:
                 # row parallel: the partial goes straight into the communicator's slot; ONE launch then
                 # sums it over the ranks, adds it to the residual stream and applies the next norm

@@ -87,3 +87,22 @@ def decode_attention(qkv: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor
                                                      out.data_ptr(), B, q_heads, kv_heads, hd, k_cache.shape[2],
                                                      _stream(qkv)), "qfb_decode_attention")
     return out
+
+
+def decode_attention_rope(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor, k_cache: torch.Tensor,
+                          v_cache: torch.Tensor, q_heads: int, kv_heads: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`rope_cache` and `decode_attention` of ONE new token per batch row in one launch: qkv
+    [B, 1, q_heads + 2 kv_heads, hd] un-rotated (and left so); the rotated key and the value are written
+    into the caches at pos [1]; returns [B, q_heads * hd].  Bit-identical to the two separate calls."""
+    B, T, H, hd = qkv.shape
+    assert T == 1 and H == q_heads + 2 * kv_heads and qkv.is_contiguous() and qkv.dtype == torch.float16
+    assert pos.dtype == torch.int64 and pos.numel() == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape == v_cache.shape == (B, kv_heads, k_cache.shape[2], hd)
+    assert cos.dtype == sin.dtype == torch.float16 and cos.is_contiguous() and sin.is_contiguous()
+    if out is None:
+        out = torch.empty(B, q_heads * hd, dtype=torch.float16, device=qkv.device)
+    _native.check(_native.lib().qfb_decode_attention_rope(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), pos.data_ptr(),
+                                                          k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), B, q_heads,
+                                                          kv_heads, hd, k_cache.shape[2], _stream(qkv)),
+                  "qfb_decode_attention_rope")
+    return out

@@ -47,6 +47,16 @@ class _PackedLinear(torch.nn.Module):
         self._host = None
 
     # -- native plumbing ---------------------------------------------------
+    @property
+    def _ws(self):
+        return self._ws_tensor
+
+    @_ws.setter
+    def _ws(self, t):
+        # the workspace pointer handed to the hot call follows the tensor
+        self._ws_tensor = t
+        self._ws_ptr = t.data_ptr() if t is not None else None
+
     def _prepare(self):
         if not self.w.is_cuda:
             raise _native.NativeError("the quantized linear layer runs on CUDA only (no CPU path); move it with .to('cuda')")
@@ -62,6 +72,9 @@ class _PackedLinear(torch.nn.Module):
         self._ws_bytes = nbytes
         self._desc = d
         self._lib = L
+        # pre-resolved pieces of the hot call
+        self._desc_ref = ctypes.byref(d)
+        self._fwd = L.qfb_linear_forward
 
     # -- the packed layout travels with the checkpoint ------------------------
     def get_extra_state(self):
@@ -87,35 +100,34 @@ class _PackedLinear(torch.nn.Module):
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if self._desc is None:
             self._prepare()
+        K, N = self.in_features, self.out_features
         assert x.dtype == torch.float16, "activations must be fp16"
-        assert x.shape[-1] == self.in_features
-        lead = x.shape[:-1]
-        x2 = x.reshape(-1, self.in_features)
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
-        M = x2.shape[0]
-        if out is None:
-            out = torch.empty(M, self.out_features, dtype=torch.float16, device=x.device)
+        assert x.shape[-1] == K
+        if x.dim() == 2 and x.is_contiguous():   # the common case: no reshape, no view of the result
+            x2, lead = x, None
         else:
-            assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() == M * self.out_features
-        if x.device != self.w.device:
-            raise _native.NativeError(f"activations on {x.device}, packed weights on {self.w.device}")
-        if x.device.index == torch.cuda.current_device():
-            st = self._lib.qfb_linear_forward(
-                ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
-                self._ws.data_ptr(), self._ws_bytes, self.flags,
-                torch.cuda.current_stream(x.device).cuda_stream,
-            )
+            lead = x.shape[:-1]
+            x2 = x.reshape(-1, K)
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+        M = x2.shape[0]
+        dev = x.device
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.float16, device=dev)
+        else:
+            assert out.dtype == torch.float16 and out.is_contiguous() and out.numel() == M * N
+        if dev != self.w.device:
+            raise _native.NativeError(f"activations on {dev}, packed weights on {self.w.device}")
+        if dev.index == torch.cuda.current_device():
+            st = self._fwd(self._desc_ref, x2.data_ptr(), M, out.data_ptr(), self._ws_ptr, self._ws_bytes, self.flags,
+                           torch.cuda.current_stream(dev).cuda_stream)
         else:  # the launch goes to the current device: make it the tensors' device
-            with torch.cuda.device(x.device):
-                st = self._lib.qfb_linear_forward(
-                    ctypes.byref(self._desc), x2.data_ptr(), M, out.data_ptr(),
-                    self._ws.data_ptr(), self._ws_bytes, self.flags,
-                    torch.cuda.current_stream(x.device).cuda_stream,
-                )
+            with torch.cuda.device(dev):
+                st = self._fwd(self._desc_ref, x2.data_ptr(), M, out.data_ptr(), self._ws_ptr, self._ws_bytes, self.flags,
+                               torch.cuda.current_stream(dev).cuda_stream)
         if st != 0:
             _native.check(st, "qfb_linear_forward")
-        return out.view(*lead, self.out_features)
+        return out if lead is None else out.view(*lead, N)
 
     def silu_mul_supported(self, rows: int) -> bool:
         """True when `forward_silu_mul` runs as ONE kernel for `rows` activation rows."""

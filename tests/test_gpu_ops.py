@@ -217,3 +217,47 @@ def test_fused_silu_mul_falls_back_above_16_rows_and_on_tile_layers():
         assert not layer.silu_mul_supported(rows)
         y = layer.forward_silu_mul(gu[:rows])
         assert torch.equal(y, layer(ops.silu_mul(gu[:rows].contiguous())))
+
+
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 2), (64, 8), (8, 1)])
+@pytest.mark.parametrize("B,max_len,p", [(1, 512, 0), (1, 512, 7), (2, 512, 130), (3, 512, 383), (1, 4096, 4095), (2, 2048, 1000)])
+def test_fused_rope_attention_equals_the_two_separate_launches(hq, hkv, B, max_len, p):
+    """Rotary embedding + cache write + attention of one new token in ONE launch: the output, the
+    cache contents at the new position and everything else are bit-identical to `rope_cache`
+    followed by `decode_attention` (whose results are checked against torch elsewhere)."""
+    hd = 128
+    g = torch.Generator(device="cuda").manual_seed(hq * 100 + hkv * 10 + p)
+    qkv = torch.randn(B, 1, hq + 2 * hkv, hd, generator=g, device="cuda").half()
+    kc = torch.randn(B, hkv, max_len, hd, generator=g, device="cuda").half()
+    vc = torch.randn(B, hkv, max_len, hd, generator=g, device="cuda").half()
+    kc[:, :, p:] = 1000.0     # position p itself must come from the new token, later ones must not leak in
+    vc[:, :, p:] = 1000.0
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().half(), ang.sin().half()
+    pos = torch.tensor([p], dtype=torch.int64, device="cuda")
+    # two launches on copies
+    qkv_a, kc_a, vc_a = qkv.clone(), kc.clone(), vc.clone()
+    ops.rope_cache(qkv_a, cos, sin, pos, kc_a, vc_a, hq, hkv)
+    want = ops.decode_attention(qkv_a, pos, kc_a, vc_a, hq, hkv)
+    # one launch
+    qkv_b, kc_b, vc_b = qkv.clone(), kc.clone(), vc.clone()
+    got = ops.decode_attention_rope(qkv_b, cos, sin, pos, kc_b, vc_b, hq, hkv)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert torch.equal(kc_b, kc_a) and torch.equal(vc_b, vc_a)     # the new key / value landed, nothing else changed
+    assert torch.equal(qkv_b, qkv)                                  # the fused kernel leaves qkv alone
+
+
+def test_decoder_with_and_without_fused_rope_gives_the_same_logits():
+    cfg = DecoderConfig(layers=2, d_model=1024, n_heads=8, n_kv_heads=2, d_ff=1024, vocab=1000, max_len=64, scale_boost=40.0)
+    a = QuantDecoder(cfg, device="cuda", seed=6, batch=2, weights="seeded")
+    b = QuantDecoder(cfg, device="cuda", seed=6, batch=2, weights="seeded")
+    b.fuse_rope = False
+    tokens = torch.randint(0, cfg.vocab, (2, 9), device="cuda")
+    with torch.no_grad():
+        assert torch.equal(a(tokens, torch.arange(9, device="cuda")), b(tokens, torch.arange(9, device="cuda")))
+        for step in range(3):
+            tok = torch.randint(0, cfg.vocab, (2, 1), device="cuda")
+            pos = torch.tensor([9 + step], device="cuda")
+            assert torch.equal(a(tok, pos), b(tok, pos))
