@@ -231,6 +231,9 @@ def main():
     ap.add_argument("--case", default="", help="profiling aid: run ONE layer NxKxM a few times (4 weight replicas in "
                     "rotation, so launches stay HBM-cold) and exit; meant to be wrapped in ncu")
     ap.add_argument("--reps", type=int, default=8)
+    ap.add_argument("--decode-case", type=int, default=0, help="profiling aid: the decoder with this many layers of the "
+                    "70B architecture, a 128-token prefill and 6 single-token steps launched one by one (no graph), then "
+                    "exit; meant to be wrapped in a profiler's launch list")
     ap.add_argument("--force", default="", choices=["", "simt", "tensor"])
     ap.add_argument("--host-streams", type=int, default=8, help="streams the end-to-end step spreads its layers over")
     ap.add_argument("--sweep", default="", help="comma-separated sweeps instead of the benchmark, one JSON line each: "
@@ -269,6 +272,14 @@ def main():
     flags = _native.FLAG_PDL if args.pdl else 0
     if args.force:
         flags |= _native.FLAG_FORCE_SIMT if args.force == "simt" else _native.FLAG_FORCE_TENSOR
+
+    if args.decode_case:
+        from qfactory.decoder import DecoderConfig, QuantDecoder, run_decode
+
+        model = QuantDecoder(DecoderConfig(layers=args.decode_case), device=dev, batch=args.decode_batch)
+        sec, _ = run_decode(model, prompt_len=128, steps=6, use_graph=False)
+        print(json.dumps({"decode_case_layers": args.decode_case, "eager_ms_per_step": sec / 6 * 1e3}))
+        return
 
     if args.case:
         N, K, M = (int(v) for v in args.case.lower().split("x"))
@@ -715,6 +726,7 @@ def main():
 
             sec = timed_decode()
             decode.update({"model": "llama2-70b-architecture random init, W4A16 g128 (output projection included)",
+                           "kernels_per_layer": 7 if world > 1 else 8,
                            "tp": world, "batch": args.decode_batch, "prompt": 128, "steps": 256,
                            "tok_per_s": 256 * args.decode_batch / sec, "ms_per_step": sec / 256 * 1e3,
                            "collective": model.collective_name()})

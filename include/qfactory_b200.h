@@ -294,23 +294,30 @@ int qfb_decode_attention_rope(const void* qkv, const void* cos, const void* sin,
  * Set-up (allocates; once per process, not on the hot path): every rank calls qfb_comm_alloc,
  * exchanges the 64-byte handle with its peers by any means (the Python side uses the process
  * group), opens the peers' handles with qfb_comm_open and hands the `world` base pointers, by
- * rank, to qfb_comm_create.  A rank's buffer holds a status word, per-row epochs, a flag table
- * and two data slots of `slot_bytes`.
+ * rank, to qfb_comm_create.  A rank's buffer holds a status word, per-row epochs and two data
+ * slots; a slot is this rank's own partial (plain fp16, `slot_bytes`) followed by one receive
+ * region per source rank (8-byte words {4 data bytes, epoch}: 2 * `slot_bytes` each).
  *
  * Use: the row-parallel linear writes its fp16 partial [rows, d] into the local slot
- * (qfb_comm_slot) and qfb_allreduce_add_rmsnorm then computes, identically on every rank,
- *     s = fp16(sum over ranks of the slots, in rank order, fp32)
+ * (qfb_comm_slot); qfb_allreduce_add_rmsnorm stores it, epoch attached, into this rank's receive
+ * region of every peer's buffer (peer stores), polls its own receive regions in local memory until
+ * every word carries the call's epoch (no flag exchange, no fence: one NVLink one-way latency), and
+ * then computes, identically on every rank,
+ *     s = fp16(sum over ranks of the partials, in rank order, fp32)
  *     x != NULL:  x[r,:] += s (in place, one fp16 addition);  otherwise the row is s itself
  *     w != NULL:  out[r,:] = fp16(row * rsqrt(mean(row^2) + eps)) * w;   w == NULL: out = row (if out)
  * Consecutive reductions on a communicator MUST alternate between slot 0 and slot 1, and every
  * rank must issue the same sequence of calls (rows, slot): that is what makes a slot safe to
  * rewrite.  rows <= qfb_comm_max_rows(), rows * d * 2 <= slot_bytes, d % 8 == 0, d <= 16384,
- * world in {1, 2, 4, 8}.  Peer memory is read with plain loads; no multicast.
+ * world in {1, 2, 4, 8}.  Peer memory is written with plain stores; no multicast.
+ * qfb_comm_region(comm, slot, r) is the receive region of source rank r inside the local slot and
+ * qfb_comm_epoch(comm, row, stream) the epoch the NEXT reduction of a row will use (tests that play
+ * a peer's part write its words there; the call synchronises the stream).
  *
- * Every wait on a peer's flag is bounded (qfb_comm_set_timeout_us, default 5 s): when it runs out
- * the kernel records it and returns normally with whatever the slots held; qfb_comm_read_status
- * then returns QFB_ERR_DEVICE_FLAG once and clears the word.  CUDA-graph safe: flags hold epochs
- * that only grow and live in device memory.
+ * Every wait is bounded (qfb_comm_set_timeout_us, default 5 s): when it runs out the kernel records
+ * it and returns normally with whatever the regions held; qfb_comm_read_status then returns
+ * QFB_ERR_DEVICE_FLAG once and clears the word.  CUDA-graph safe: epochs only grow and live in
+ * device memory.
  */
 typedef struct qfb_comm qfb_comm;
 size_t qfb_comm_buffer_bytes(size_t slot_bytes);
@@ -323,7 +330,8 @@ int qfb_comm_create(int rank, int world, void* const* bases, size_t slot_bytes, 
 void qfb_comm_destroy(qfb_comm* comm);
 void qfb_comm_set_timeout_us(qfb_comm* comm, unsigned microseconds);
 void* qfb_comm_slot(const qfb_comm* comm, int slot);
-size_t qfb_comm_flag_offset(int row, int source_rank);
+void* qfb_comm_region(const qfb_comm* comm, int slot, int source_rank);
+int qfb_comm_epoch(qfb_comm* comm, int row, void* stream, unsigned* epoch_out);
 int qfb_allreduce_add_rmsnorm(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,
                               float eps, void* stream);
 int qfb_comm_read_status(qfb_comm* comm, void* stream, unsigned* status_out);

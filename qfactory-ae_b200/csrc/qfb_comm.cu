@@ -11,24 +11,31 @@
 // their bandwidth, is what matters.
 //
 // Protocol.  Every rank owns one symmetric buffer (same layout on every rank, mapped into every
-// peer): a header, a flag table and two data slots.  The row-parallel GEMV writes its fp16 partial
-// [rows, d] straight into a data slot of its own buffer.  The reduction kernel then runs one CTA
-// per batch row:
-//   1. thread p of the CTA stores this call's epoch into the flag (row, my rank) of PEER p's
-//      table (st.release.sys), and polls the flag (row, p) of its OWN table (ld.acquire.sys)
-//      until it holds that epoch: peer p's partial is complete.  Flags only ever grow, so a
-//      replayed CUDA graph needs no reset; the epoch of a row lives in the local header and is
-//      advanced by the kernel itself.
-//   2. every thread pulls 16 bytes of the row from each rank's slot (plain peer loads, all in
-//      flight together), sums them in rank order in fp32 (bit-identical on every rank), adds the
-//      residual stream, and the CTA applies the RMS norm of the sum.
-// Data slots alternate between consecutive reductions: a rank rewrites a slot only after it
-// has passed the entry flags of the NEXT reduction, which every peer raises after it has finished
-// reading that slot.
+// peer): a header and two data slots; a slot holds this rank's own partial (plain fp16, written by
+// the row-parallel GEMV as its output) and one RECEIVE region per source rank.  The reduction
+// kernel runs one CTA per batch row and needs no flag exchange and no fence: the flag travels
+// inside the data.
+//   1. every thread reads its 16 bytes of the local partial and stores them into this rank's
+//      receive region of every PEER's buffer as four 8-byte words {4 data bytes, epoch} (two
+//      16-byte peer stores per peer; an 8-byte word is written atomically, so a word whose epoch
+//      matches carries valid data).  Fire and forget;
+//   2. the same thread polls the four words it needs of every peer's region of its OWN buffer
+//      (local memory) until all carry this call's epoch: the only latency exposed is one NVLink
+//      one-way trip.  (A first version raised flags and pulled the partials with peer loads: a flag
+//      trip plus a load round trip; a second pushed the data and then a flag with st.release.sys,
+//      which waits for the pushes to be acknowledged: 3.8 us per reduction over the norm alone.)
+//      Epochs only ever grow, so stale words never match and a replayed CUDA graph needs no
+//      reset; the epoch of a row lives in the local header and is advanced by the kernel itself.
+//   3. the thread sums the W partials in rank order in fp32 (bit-identical on every rank), adds
+//      the residual stream, and the CTA applies the RMS norm.
+// Data slots alternate between consecutive reductions.  A peer can run at most one reduction ahead
+// of this rank (its next row-parallel GEMV needs the result of the current reduction, hence this
+// rank's partial of it), so it writes the other slot while this one is still being read.
 //
 // Every wait is bounded (default 5 s, settable): when it runs out the CTA records it in the status
 // word of the local header and carries on with whatever the slots hold; the host reads the word
-// with qfb_comm_read_status.  No multicast, no multimem: plain loads and stores on peer pointers.
+// with qfb_comm_read_status.  No multicast, no multimem: plain stores on peer pointers, polls on local memory.
+#include <algorithm>
 #include <cstdio>
 #include <new>
 
@@ -40,12 +47,15 @@ namespace qfb {
 constexpr int kCommMaxWorld = 8;
 constexpr int kCommMaxRows = 64;       // batch rows one reduction handles (one CTA each)
 constexpr size_t kCommHeaderBytes = 1024;                                         // status word + epochs[kCommMaxRows]
-constexpr size_t kCommFlagBytes = (size_t)kCommMaxRows * kCommMaxWorld * 4;       // flags[row][source rank]
-constexpr size_t kCommDataOffset = kCommHeaderBytes + kCommFlagBytes;             // 3072: 16-byte aligned
+constexpr size_t kCommDataOffset = kCommHeaderBytes;
+// a data slot: [own partial, plain fp16: slot_bytes][receive regions, one per source rank: 2 * slot_bytes each]
 
 struct CommArgs {
   char* base[kCommMaxWorld];   // symmetric buffers, by rank (base[rank] is local)
-  size_t slot_offset;          // byte offset of the data slot used by this call
+  char* local;                 // = base[rank] (kept apart: the kernel never indexes `base` with a run-time value)
+  size_t slot_offset;          // byte offset of the data slot used by this call (its own-partial part)
+  size_t recv_offset;          // byte offset of the slot's receive region of source rank 0
+  size_t region_bytes;         // bytes between the receive regions of consecutive source ranks
   __half* x;                   // residual stream [rows, d], updated in place (null: no residual)
   const __half* w;             // norm weight [d] (null: no norm)
   __half* out;                 // normed row, or the plain sum when w is null
@@ -54,81 +64,96 @@ struct CommArgs {
   unsigned long long timeout_ns;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// 16 bytes of (possibly peer) memory, past the L1 (the line may have been rewritten by its owner)
-__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
+// 16 bytes that a peer may have written: read past the L1
+__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
-// VPT = 16-byte vectors of the row each thread owns (d = 8 * VPT * blockDim.x at most)
-template <int W, int VPT>
-__global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommArgs a) {
+// VPT = 16-byte vectors of the row each thread owns (d = 8 * VPT * blockDim.x at most); MAXT = most
+// threads per CTA (512 for eight ranks: a thread then has the registers to keep the sixteen polled
+// vectors of a pass in flight without spilling)
+template <int W, int VPT, int MAXT>
+__global__ void __launch_bounds__(MAXT) allreduce_add_rmsnorm_kernel(const CommArgs a) {
   grid_launch_dependents();
   grid_dependency_wait();  // the partial in the local slot was written by the preceding kernel
   const int row = blockIdx.x, tid = threadIdx.x;
-  unsigned* status = reinterpret_cast<unsigned*>(a.base[a.rank]);
+  unsigned* status = reinterpret_cast<unsigned*>(a.local);
   unsigned* epochs = status + 1;
-  unsigned* my_flags = reinterpret_cast<unsigned*>(a.base[a.rank] + kCommHeaderBytes) + row * kCommMaxWorld;
   __shared__ float red[32];
+  const unsigned epoch = epochs[row] + 1u;   // (advanced by thread 0 once every thread has read it)
 
-  // ---- entry flags: tell every peer this rank's partial is in place, wait for theirs ----------
-  if (tid < W && tid != a.rank) {
-    const unsigned epoch = epochs[row] + 1u;
-    unsigned* theirs = reinterpret_cast<unsigned*>(a.base[tid] + kCommHeaderBytes) + row * kCommMaxWorld + a.rank;
-    st_release_sys(theirs, epoch);
-    const unsigned long long t0 = global_timer_ns();
-    while ((int)(ld_acquire_sys(my_flags + tid) - epoch) < 0) {
-      if (global_timer_ns() - t0 > a.timeout_ns) {  // bounded: record it and go on
+  // ---- push this rank's partial of the row, epoch attached, into every peer's receive region ------
+  const int nv = a.d >> 3;
+  const size_t own_off = a.slot_offset + (size_t)row * a.d * 2;                                   // plain fp16
+  const size_t recv_row = a.recv_offset + (size_t)row * a.d * 4;                                  // {data, epoch} words
+  uint4 mine[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = tid + i * blockDim.x;
+    mine[i] = make_uint4(0, 0, 0, 0);
+    if (v < nv) {
+      mine[i] = *reinterpret_cast<const uint4*>(a.local + own_off + (size_t)v * 16);   // written by the preceding kernel
+      const size_t off = recv_row + (size_t)a.rank * a.region_bytes + (size_t)v * 32;
+      const uint4 lo = make_uint4(mine[i].x, epoch, mine[i].y, epoch), hi = make_uint4(mine[i].z, epoch, mine[i].w, epoch);
+#pragma unroll
+      for (int r = 0; r < W; ++r)
+        if (r != a.rank) {
+          st_sys_v4(a.base[r] + off, lo);
+          st_sys_v4(a.base[r] + off + 16, hi);
+        }
+    }
+  }
+
+  // ---- poll the peers' words of this thread in local memory until they carry the epoch; every pass
+  // sums what it sees in rank order, the pass that finds every epoch in place is the one that counts ----
+  float acc[VPT][8];
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {   // (one vector at a time: the W - 1 polled vectors of a pass stay in registers)
+    const int v = tid + i * blockDim.x;
+    while (true) {
+      bool pending = false;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        uint4 p4 = mine[i];   // (the own partial: already in registers)
+        if (v < nv && r != a.rank) {
+          const char* src = a.local + recv_row + (size_t)r * a.region_bytes + (size_t)v * 32;
+          const uint4 lo = ld_sys_v4(src), hi = ld_sys_v4(src + 16);
+          if (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) pending = true;
+          p4 = make_uint4(lo.x, lo.z, hi.x, hi.z);
+        }
+        const uint32_t u[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(as_h2(u[j]));
+          acc[i][2 * j] += f.x;
+          acc[i][2 * j + 1] += f.y;
+        }
+      }
+      if (!pending) break;
+      if (global_timer_ns() - t0 > a.timeout_ns) {  // bounded: record it and go on with what is there
         atomicExch(status, 1u);
         break;
       }
     }
-  }
-  __syncthreads();
-  if (tid == 0) epochs[row] += 1u;  // (every reader of epochs[row] is past the barrier)
-
-  // ---- pull the row from every rank, sum in rank order ------------------------------------------
-  const int nv = a.d >> 3;
-  float acc[VPT][8];
-  uint4 part[VPT][W];
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * blockDim.x;
-#pragma unroll
-    for (int r = 0; r < W; ++r)
-      if (v < nv) part[i][r] = ld_peer_v4(a.base[r] + a.slot_offset + ((size_t)row * a.d + (size_t)v * 8) * 2);
   }
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = tid + i * blockDim.x;
     if (v >= nv) continue;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-#pragma unroll
-    for (int r = 0; r < W; ++r) {
-      const uint32_t u[4] = {part[i][r].x, part[i][r].y, part[i][r].z, part[i][r].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __half22float2(as_h2(u[j]));
-        acc[i][2 * j] += f.x;
-        acc[i][2 * j + 1] += f.y;
-      }
-    }
     // the reduced partial is rounded to fp16 (what a collective on fp16 tensors returns), then added
     // to the residual stream with one fp16 addition, as the unfused x + o does
     uint32_t o[4];
@@ -150,6 +175,8 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommA
       ss += f.x * f.x + f.y * f.y;
     }
   }
+  __syncthreads();                     // every thread has read the row's epoch
+  if (tid == 0) epochs[row] = epoch;
   if (!a.w) {  // plain all-reduce (with or without the residual): the sum itself is the output
     if (a.out) {
 #pragma unroll
@@ -192,7 +219,10 @@ __global__ void __launch_bounds__(1024) allreduce_add_rmsnorm_kernel(const CommA
 }
 
 template <int W>
-static cudaError_t launch_w(const CommArgs& a, int rows, int block, int vpt, cudaStream_t st) {
+static cudaError_t launch_w(const CommArgs& a, int rows, int nv, cudaStream_t st) {
+  constexpr int MAXT = W >= 8 ? 512 : 1024;
+  const int vpt = nv <= MAXT ? 1 : (nv <= 2 * MAXT ? 2 : 4);
+  const int block = std::min(MAXT, ((nv + vpt - 1) / vpt + 31) / 32 * 32);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(rows);
   cfg.blockDim = dim3(block);
@@ -203,9 +233,11 @@ static cudaError_t launch_w(const CommArgs& a, int rows, int block, int vpt, cud
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   switch (vpt) {
-    case 1: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 1>, a);
-    case 2: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 2>, a);
-    default: return cudaErrorInvalidValue;
+    case 1: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 1, MAXT>, a);
+    case 2: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 2, MAXT>, a);
+    default:
+      if constexpr (W >= 8) return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 4, MAXT>, a);
+      return cudaErrorInvalidValue;
   }
 }
 
@@ -232,7 +264,10 @@ extern "C" {
 
 int qfb_comm_last_cuda_error(void) { return tl_comm_cuda_error; }
 
-size_t qfb_comm_buffer_bytes(size_t slot_bytes) { return kCommDataOffset + 2 * ((slot_bytes + 255) / 256 * 256); }
+// bytes of one data slot: the own partial + a receive region ({data, epoch} words: twice the size) per source rank
+static size_t comm_slot_span(size_t slot_bytes) { return slot_bytes * (1 + 2 * (size_t)kCommMaxWorld); }
+
+size_t qfb_comm_buffer_bytes(size_t slot_bytes) { return kCommDataOffset + 2 * comm_slot_span((slot_bytes + 255) / 256 * 256); }
 
 int qfb_comm_max_rows(void) { return kCommMaxRows; }
 
@@ -294,14 +329,15 @@ void qfb_comm_set_timeout_us(qfb_comm* c, unsigned microseconds) {
   if (c) c->timeout_ns = (unsigned long long)(microseconds ? microseconds : 1u) * 1000ull;
 }
 
-void* qfb_comm_slot(const qfb_comm* c, int slot) {
+void* qfb_comm_slot(const qfb_comm* c, int slot) {  // this rank's own partial of the local slot (plain fp16)
   if (!c || slot < 0 || slot > 1) return nullptr;
-  return c->base[c->rank] + kCommDataOffset + (size_t)slot * c->slot_bytes;
+  return c->base[c->rank] + kCommDataOffset + (size_t)slot * comm_slot_span(c->slot_bytes);
 }
 
-/* byte offset of flag (row, source rank) inside a symmetric buffer (tests pre-raise flags with it) */
-size_t qfb_comm_flag_offset(int row, int source_rank) {
-  return kCommHeaderBytes + ((size_t)row * kCommMaxWorld + (size_t)source_rank) * 4;
+void* qfb_comm_region(const qfb_comm* c, int slot, int source_rank) {  // receive region: {4 data bytes, epoch} words
+  if (!c || slot < 0 || slot > 1 || source_rank < 0 || source_rank >= c->world) return nullptr;
+  return c->base[c->rank] + kCommDataOffset + (size_t)slot * comm_slot_span(c->slot_bytes) + c->slot_bytes +
+         (size_t)source_rank * 2 * c->slot_bytes;
 }
 
 int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
@@ -316,7 +352,10 @@ int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, voi
     return QFB_ERR_MISALIGNED;
   CommArgs a;
   for (int r = 0; r < kCommMaxWorld; ++r) a.base[r] = c->base[r];
-  a.slot_offset = kCommDataOffset + (size_t)slot * c->slot_bytes;
+  a.local = c->base[c->rank];
+  a.slot_offset = kCommDataOffset + (size_t)slot * comm_slot_span(c->slot_bytes);
+  a.recv_offset = a.slot_offset + c->slot_bytes;
+  a.region_bytes = 2 * c->slot_bytes;
   a.x = static_cast<__half*>(x);
   a.w = static_cast<const __half*>(w);
   a.out = static_cast<__half*>(out);
@@ -325,16 +364,27 @@ int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, voi
   a.eps = eps;
   a.timeout_ns = c->timeout_ns;
   const int nv = d / 8;
-  const int vpt = nv > 1024 ? 2 : 1;
-  const int block = std::min(1024, ((nv + vpt - 1) / vpt + 31) / 32 * 32);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (c->world) {
-    case 1: return comm_check(launch_w<1>(a, rows, block, vpt, st));
-    case 2: return comm_check(launch_w<2>(a, rows, block, vpt, st));
-    case 4: return comm_check(launch_w<4>(a, rows, block, vpt, st));
-    case 8: return comm_check(launch_w<8>(a, rows, block, vpt, st));
+    case 1: return comm_check(launch_w<1>(a, rows, nv, st));
+    case 2: return comm_check(launch_w<2>(a, rows, nv, st));
+    case 4: return comm_check(launch_w<4>(a, rows, nv, st));
+    case 8: return comm_check(launch_w<8>(a, rows, nv, st));
     default: return QFB_ERR_UNSUPPORTED;
   }
+}
+
+int qfb_comm_epoch(qfb_comm* c, int row, void* stream, unsigned* epoch_out) {
+  if (!c || !epoch_out) return QFB_ERR_NULL_POINTER;
+  if (row < 0 || row >= kCommMaxRows) return QFB_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned done = 0;
+  int s = comm_check(cudaMemcpyAsync(&done, c->base[c->rank] + 4 + 4 * (size_t)row, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+  if (s != QFB_OK) return s;
+  s = comm_check(cudaStreamSynchronize(st));
+  if (s != QFB_OK) return s;
+  *epoch_out = done + 1u;
+  return QFB_OK;
 }
 
 int qfb_comm_read_status(qfb_comm* c, void* stream, unsigned* status_out) {

@@ -30,7 +30,7 @@ EXPORTS = (
     "qfb_gemv_forward_static", "qfb_static_scratch_capacity",
     "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention", "qfb_decode_attention_rope",
     "qfb_comm_buffer_bytes", "qfb_comm_max_rows", "qfb_comm_alloc", "qfb_comm_free", "qfb_comm_open", "qfb_comm_close",
-    "qfb_comm_create", "qfb_comm_destroy", "qfb_comm_set_timeout_us", "qfb_comm_slot", "qfb_comm_flag_offset",
+    "qfb_comm_create", "qfb_comm_destroy", "qfb_comm_set_timeout_us", "qfb_comm_slot", "qfb_comm_region", "qfb_comm_epoch",
     "qfb_allreduce_add_rmsnorm", "qfb_comm_read_status", "qfb_comm_last_cuda_error",
 )
 
@@ -151,8 +151,10 @@ def lib() -> ctypes.CDLL:
     L.qfb_comm_set_timeout_us.argtypes = [vp, u32]
     L.qfb_comm_slot.restype = vp
     L.qfb_comm_slot.argtypes = [vp, i32]
-    L.qfb_comm_flag_offset.restype = sz
-    L.qfb_comm_flag_offset.argtypes = [i32, i32]
+    L.qfb_comm_region.restype = vp
+    L.qfb_comm_region.argtypes = [vp, i32, i32]
+    L.qfb_comm_epoch.restype = i32
+    L.qfb_comm_epoch.argtypes = [vp, i32, vp, ctypes.POINTER(u32)]
     L.qfb_allreduce_add_rmsnorm.restype = i32
     L.qfb_allreduce_add_rmsnorm.argtypes = [vp, i32, vp, vp, vp, i32, i32, ctypes.c_float, vp]
     L.qfb_comm_read_status.restype = i32

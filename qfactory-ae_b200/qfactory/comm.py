@@ -1,5 +1,8 @@
 """Peer-memory communicator of the tensor-parallel decoder: one symmetric buffer per rank, mapped
-into every peer, and the fused `all-reduce + residual add + RMS norm` kernel that runs on it
+into every peer (two data slots with one receive region per source rank), and the fused
+`all-reduce + residual add + RMS norm` kernel that runs on it: every rank stores its partial, the
+call's epoch attached to every 4 bytes, into its region of every peer's buffer, polls its own
+regions until the epochs are in place, and reduces from local memory
 (C ABI: the qfb_comm_* entry points of include/qfactory_b200.h).
 
 It takes the place of the collective call after a row-parallel linear in the reference's serving
@@ -35,7 +38,8 @@ class PeerComm:
 
     `PeerComm.from_process_group(d, slot_rows, group)` builds one over the ranks of a process group
     (one process per GPU of one node).  `PeerComm.local_emulation(...)` builds the `world` buffers
-    of all ranks inside ONE process on one GPU, for tests that play a peer's part by hand.
+    of all ranks inside ONE process on one GPU, for tests that play a peer's part by hand
+    (`write_peer_partial`).
     """
 
     def __init__(self, rank, world, bases, d, slot_rows, device, owned=None, opened=()):
@@ -88,9 +92,9 @@ class PeerComm:
     @classmethod
     def local_emulation(cls, rank, world, d, slot_rows, device="cuda"):
         """All `world` buffers allocated by this process on one GPU; returns the communicator of
-        `rank`.  `peer_slot(r, slot)` and `raise_flag(...)` let a test write a peer's partial and
-        raise its flag before the kernel is launched (the kernel of a second rank is never run
-        beside this one on the same GPU: kernels that wait on one another must not share a GPU)."""
+        `rank`.  `write_peer_partial(r, slot, t)` lets a test put a peer's partial in place before
+        the kernel is launched (the kernel of a second rank is never run beside this one on the same
+        GPU: kernels that wait on one another must not share a GPU)."""
         L = _native.lib()
         device = torch.device(device)
         slot_rows = min(slot_rows, L.qfb_comm_max_rows())
@@ -134,16 +138,25 @@ class PeerComm:
         return self._lib.qfb_comm_read_status(self._h, torch.cuda.current_stream(self.device).cuda_stream, ctypes.byref(st))
 
     # -- emulation helpers (tests) ---------------------------------------------------
-    def peer_slot(self, r: int, which: int, rows: int) -> torch.Tensor:
-        off = self._lib.qfb_comm_slot(self._h, which) - self.bases[self.rank]
-        return torch.as_tensor(_DevView(self.bases[r] + off, (self.slot_rows, self.d), self), device=self.device)[:rows]
+    def next_epoch(self, row: int = 0) -> int:
+        """The epoch the next reduction of `row` will use (synchronises the stream)."""
+        e = ctypes.c_uint(0)
+        _native.check(self._lib.qfb_comm_epoch(self._h, row, torch.cuda.current_stream(self.device).cuda_stream,
+                                               ctypes.byref(e)), "qfb_comm_epoch")
+        return e.value
 
-    def raise_flag(self, row: int, source_rank: int, epoch: int) -> None:
-        """Store `epoch` into this rank's flag (row, source_rank), as peer `source_rank` would."""
-        off = self._lib.qfb_comm_flag_offset(row, source_rank)
-        v = _DevView(self.bases[self.rank] + off, (2,), self)   # two halfs = the 32-bit flag
-        t = torch.as_tensor(v, device=self.device).view(torch.int32)
-        t.fill_(epoch)
+    def write_peer_partial(self, r: int, which: int, partial: torch.Tensor, epoch: int | None = None) -> None:
+        """Play peer `r`: put its fp16 partial [rows, d] into THIS rank's receive region of slot `which`
+        as the peer's reduction kernel would, every 4 data bytes followed by the epoch.  `epoch` None:
+        the epoch the next reduction will use (rows of one call share it)."""
+        rows = partial.shape[0]
+        if epoch is None:
+            epoch = self.next_epoch(0)
+        ptr = self._lib.qfb_comm_region(self._h, which, r)
+        words = torch.as_tensor(_DevView(ptr, (self.slot_rows, 2 * self.d), self), device=self.device).view(torch.int32)
+        data = partial.contiguous().view(torch.int32)                      # [rows, d / 2]
+        packed = torch.stack((data, torch.full_like(data, epoch)), dim=-1).reshape(rows, self.d)
+        words[:rows].copy_(packed)
 
     def close(self):
         L = self._lib

@@ -1,9 +1,9 @@
 """The one-shot peer-memory all-reduce fused with the residual add and the RMS norm, on ONE GPU.
 
 The buffers of all ranks are allocated by this process on the same device and the test plays the
-peers' part by hand: it writes their partials into their slots and raises their flags BEFORE the
-kernel of the rank under test is launched (two kernels that wait on each other are never run side
-by side on one GPU).  The bounded wait is exercised with a flag that nothing raises."""
+peers' part by hand: it writes their partials, epoch attached, into the receive regions of the
+rank under test BEFORE its kernel is launched (two kernels that wait on each other are never run
+side by side on one GPU).  The bounded wait is exercised with words that nothing writes."""
 import pytest
 import torch
 
@@ -37,11 +37,12 @@ def test_allreduce_add_rmsnorm_matches_reference_over_two_calls(world, rows, d):
         w = (torch.rand(d, generator=g, device="cuda") + 0.5).half()
         for call, slot in enumerate((0, 1, 0)):
             parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
+            assert comm.next_epoch() == call + 1
             for r in range(world):
-                comm.peer_slot(r, slot, rows).copy_(parts[r])
-                if r != rank:
-                    for row in range(rows):
-                        comm.raise_flag(row, r, call + 1)       # peer r has arrived at reduction `call`
+                if r == rank:
+                    comm.slot(slot, rows).copy_(parts[r])          # what the row-parallel linear writes
+                else:
+                    comm.write_peer_partial(r, slot, parts[r])     # what peer r's reduction kernel stores here
             want_x, want_h = _reference(parts, x, w)
             h = comm.allreduce_add_rmsnorm(slot, x, w, rows)
             torch.cuda.synchronize()
@@ -59,9 +60,10 @@ def test_plain_sum_without_residual_or_norm():
     try:
         parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
         for r in range(world):
-            comm.peer_slot(r, 0, rows).copy_(parts[r])
-            for row in range(rows):
-                comm.raise_flag(row, r, 1)
+            if r == 1:
+                comm.slot(0, rows).copy_(parts[r])
+            else:
+                comm.write_peer_partial(r, 0, parts[r])
         out = comm.allreduce_add_rmsnorm(0, None, None, rows)
         torch.cuda.synchronize()
         assert torch.equal(out, _reference(parts, None, None)[0])
@@ -74,7 +76,7 @@ def test_bounded_wait_runs_out_and_the_next_call_is_correct():
     g = torch.Generator(device="cuda").manual_seed(5)
     comm = PeerComm.local_emulation(0, world, d, 8)
     try:
-        comm.set_timeout_us(100)                                  # nothing raises the peer's flag: give up after 100 us
+        comm.set_timeout_us(100)                                  # nothing writes the peer's words: give up after 100 us
         x = torch.randn(rows, d, generator=g, device="cuda").half()
         w = torch.ones(d, dtype=torch.float16, device="cuda")
         comm.allreduce_add_rmsnorm(0, x.clone(), w, rows)
@@ -83,10 +85,9 @@ def test_bounded_wait_runs_out_and_the_next_call_is_correct():
         assert comm.read_status() == 0
         # the communicator is still usable: the next reduction (epoch 2, the other slot) is exact
         parts = [torch.randn(rows, d, generator=g, device="cuda").half() for _ in range(world)]
-        for r in range(world):
-            comm.peer_slot(r, 1, rows).copy_(parts[r])
-        for row in range(rows):
-            comm.raise_flag(row, 1, 2)
+        assert comm.next_epoch() == 2
+        comm.slot(1, rows).copy_(parts[0])
+        comm.write_peer_partial(1, 1, parts[1])
         want_x, _ = _reference(parts, x, w)
         comm.allreduce_add_rmsnorm(1, x, w, rows)
         torch.cuda.synchronize()
