@@ -314,7 +314,7 @@ int qfb_decode_attention_rope(const void* qkv, const void* cos, const void* sin,
  * qfb_comm_epoch(comm, row, stream) the epoch the NEXT reduction of a row will use (tests that play
  * a peer's part write its words there; the call synchronises the stream).
  *
- * Every wait is bounded (qfb_comm_set_timeout_us, default 5 s): when it runs out the kernel records
+ * Every wait is bounded (qfb_comm_set_timeout_us, default 2 s): when it runs out the kernel records
  * it and returns normally with whatever the regions held; qfb_comm_read_status then returns
  * QFB_ERR_DEVICE_FLAG once and clears the word.  CUDA-graph safe: epochs only grow and live in
  * device memory.

@@ -32,7 +32,7 @@
 // of this rank (its next row-parallel GEMV needs the result of the current reduction, hence this
 // rank's partial of it), so it writes the other slot while this one is still being read.
 //
-// Every wait is bounded (default 5 s, settable): when it runs out the CTA records it in the status
+// Every wait is bounded (default 2 s, settable): when it runs out the CTA records it in the status
 // word of the local header and carries on with whatever the slots hold; the host reads the word
 // with qfb_comm_read_status.  No multicast, no multimem: plain stores on peer pointers, polls on local memory.
 #include <algorithm>
@@ -79,166 +79,178 @@ __device__ __forceinline__ void st_sys_v4(void* p, const uint4& v) {
   asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// VPT = 16-byte vectors of the row each thread owns (d = 8 * VPT * blockDim.x at most); MAXT = most
-// threads per CTA (512 for eight ranks: a thread then has the registers to keep the sixteen polled
-// vectors of a pass in flight without spilling)
-template <int W, int VPT, int MAXT>
-__global__ void __launch_bounds__(MAXT) allreduce_add_rmsnorm_kernel(const CommArgs a) {
+__device__ __forceinline__ void comm_cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void comm_st_cluster_f32(const float* local_addr, int cta_rank, float v) {
+  const uint32_t la = static_cast<uint32_t>(__cvta_generic_to_shared(local_addr));
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta_rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+}
+
+// One batch row = one thread-block cluster of C CTAs (grid (C, rows)), each thread one 16-byte vector
+// of the row: the peer stores and the polls of a row are spread over C SMs (a single SM moving the
+// 2 * 16 KiB * (W - 1) bytes of an 8192-wide row was the long pole at four and eight ranks), and the
+// sum of squares of the norm is combined through distributed shared memory with one cluster barrier.
+template <int W, int C>
+__global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const CommArgs a) {   // (a CTA has at most 256 vectors)
   grid_launch_dependents();
+  // shared memory of another CTA of the cluster may only be written once that CTA runs: every CTA
+  // arrives here and waits for the others just before its first remote store (free by then)
+  if (C > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   grid_dependency_wait();  // the partial in the local slot was written by the preceding kernel
-  const int row = blockIdx.x, tid = threadIdx.x;
+  const int row = blockIdx.y, tid = threadIdx.x, crank = blockIdx.x;
   unsigned* status = reinterpret_cast<unsigned*>(a.local);
   unsigned* epochs = status + 1;
   __shared__ float red[32];
-  const unsigned epoch = epochs[row] + 1u;   // (advanced by thread 0 once every thread has read it)
+  __shared__ float css[8];   // sums of squares of the C CTAs of the row (pushed by every CTA into every CTA)
+  const unsigned epoch = epochs[row] + 1u;   // (advanced by one thread once every CTA of the row has read it)
 
   // ---- push this rank's partial of the row, epoch attached, into every peer's receive region ------
   const int nv = a.d >> 3;
+  const int v = crank * blockDim.x + tid;    // this thread's vector of the row
+  const bool active = v < nv;
   const size_t own_off = a.slot_offset + (size_t)row * a.d * 2;                                   // plain fp16
   const size_t recv_row = a.recv_offset + (size_t)row * a.d * 4;                                  // {data, epoch} words
-  uint4 mine[VPT];
+  uint4 mine = make_uint4(0, 0, 0, 0);
+  if (active) {
+    mine = *reinterpret_cast<const uint4*>(a.local + own_off + (size_t)v * 16);   // written by the preceding kernel
+    const size_t off = recv_row + (size_t)a.rank * a.region_bytes + (size_t)v * 32;
+    const uint4 lo = make_uint4(mine.x, epoch, mine.y, epoch), hi = make_uint4(mine.z, epoch, mine.w, epoch);
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * blockDim.x;
-    mine[i] = make_uint4(0, 0, 0, 0);
-    if (v < nv) {
-      mine[i] = *reinterpret_cast<const uint4*>(a.local + own_off + (size_t)v * 16);   // written by the preceding kernel
-      const size_t off = recv_row + (size_t)a.rank * a.region_bytes + (size_t)v * 32;
-      const uint4 lo = make_uint4(mine[i].x, epoch, mine[i].y, epoch), hi = make_uint4(mine[i].z, epoch, mine[i].w, epoch);
-#pragma unroll
-      for (int r = 0; r < W; ++r)
-        if (r != a.rank) {
-          st_sys_v4(a.base[r] + off, lo);
-          st_sys_v4(a.base[r] + off + 16, hi);
-        }
-    }
+    for (int r = 0; r < W; ++r)
+      if (r != a.rank) {
+        st_sys_v4(a.base[r] + off, lo);
+        st_sys_v4(a.base[r] + off + 16, hi);
+      }
   }
 
   // ---- poll the peers' words of this thread in local memory until they carry the epoch; every pass
   // sums what it sees in rank order, the pass that finds every epoch in place is the one that counts ----
-  float acc[VPT][8];
+  float acc[8];
   const unsigned long long t0 = global_timer_ns();
+  while (true) {
+    bool pending = false;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {   // (one vector at a time: the W - 1 polled vectors of a pass stay in registers)
-    const int v = tid + i * blockDim.x;
-    while (true) {
-      bool pending = false;
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-#pragma unroll
-      for (int r = 0; r < W; ++r) {
-        uint4 p4 = mine[i];   // (the own partial: already in registers)
-        if (v < nv && r != a.rank) {
-          const char* src = a.local + recv_row + (size_t)r * a.region_bytes + (size_t)v * 32;
-          const uint4 lo = ld_sys_v4(src), hi = ld_sys_v4(src + 16);
-          if (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) pending = true;
-          p4 = make_uint4(lo.x, lo.z, hi.x, hi.z);
-        }
-        const uint32_t u[4] = {p4.x, p4.y, p4.z, p4.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __half22float2(as_h2(u[j]));
-          acc[i][2 * j] += f.x;
-          acc[i][2 * j + 1] += f.y;
-        }
+    for (int r = 0; r < W; ++r) {
+      uint4 p4 = mine;   // (the own partial: already in registers)
+      if (active && r != a.rank) {
+        const char* src = a.local + recv_row + (size_t)r * a.region_bytes + (size_t)v * 32;
+        const uint4 lo = ld_sys_v4(src), hi = ld_sys_v4(src + 16);
+        if (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) pending = true;
+        p4 = make_uint4(lo.x, lo.z, hi.x, hi.z);
       }
-      if (!pending) break;
-      if (global_timer_ns() - t0 > a.timeout_ns) {  // bounded: record it and go on with what is there
-        atomicExch(status, 1u);
-        break;
+      const uint32_t u[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(as_h2(u[j]));
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
       }
     }
+    if (!pending) break;
+    if (global_timer_ns() - t0 > a.timeout_ns) {  // bounded: record it and go on with what is there
+      atomicExch(status, 1u);
+      break;
+    }
   }
+
+  // the reduced partial is rounded to fp16 (what a collective on fp16 tensors returns), then added
+  // to the residual stream with one fp16 addition, as the unfused x + o does
   float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * blockDim.x;
-    if (v >= nv) continue;
-    // the reduced partial is rounded to fp16 (what a collective on fp16 tensors returns), then added
-    // to the residual stream with one fp16 addition, as the unfused x + o does
+  if (active) {
     uint32_t o[4];
     if (a.x) {
       const uint4 xv = *reinterpret_cast<const uint4*>(a.x + (size_t)row * a.d + (size_t)v * 8);
       const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = as_u32(__hadd2(as_h2(xu[j]), __floats2half2_rn(acc[i][2 * j], acc[i][2 * j + 1])));
+      for (int j = 0; j < 4; ++j) o[j] = as_u32(__hadd2(as_h2(xu[j]), __floats2half2_rn(acc[2 * j], acc[2 * j + 1])));
       *reinterpret_cast<uint4*>(a.x + (size_t)row * a.d + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = as_u32(__floats2half2_rn(acc[i][2 * j], acc[i][2 * j + 1]));
+      for (int j = 0; j < 4; ++j) o[j] = as_u32(__floats2half2_rn(acc[2 * j], acc[2 * j + 1]));
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 f = __half22float2(as_h2(o[j]));
-      acc[i][2 * j] = f.x;
-      acc[i][2 * j + 1] = f.y;
+      acc[2 * j] = f.x;
+      acc[2 * j + 1] = f.y;
       ss += f.x * f.x + f.y * f.y;
     }
-  }
-  __syncthreads();                     // every thread has read the row's epoch
-  if (tid == 0) epochs[row] = epoch;
-  if (!a.w) {  // plain all-reduce (with or without the residual): the sum itself is the output
-    if (a.out) {
+    if (!a.w && a.out) {  // plain all-reduce (with or without the residual): the sum itself is the output
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * blockDim.x;
-        if (v < nv) {
-          uint32_t o[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) o[j] = as_u32(__floats2half2_rn(acc[i][2 * j], acc[i][2 * j + 1]));
-          *reinterpret_cast<uint4*>(a.out + (size_t)row * a.d + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-      }
+      for (int j = 0; j < 4; ++j) o[j] = as_u32(__floats2half2_rn(acc[2 * j], acc[2 * j + 1]));
+      *reinterpret_cast<uint4*>(a.out + (size_t)row * a.d + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    return;
   }
-  // ---- RMS norm of the updated row ---------------------------------------------------------------
+
+  // ---- sum of squares of the row: warps -> CTA -> the C CTAs of the cluster, always in the same order ----
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((tid & 31) == 0) red[tid >> 5] = ss;
   __syncthreads();
-  float tot = 0.f;
-  const int nwarps = (blockDim.x + 31) >> 5;
-  for (int i = 0; i < nwarps; ++i) tot += red[i];
-  const float rstd = rsqrtf(tot / (float)a.d + a.eps);
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int v = tid + i * blockDim.x;
-    if (v >= nv) continue;
-    const uint4 g = *reinterpret_cast<const uint4*>(a.w + (size_t)v * 8);
-    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      // the normalised value is rounded to fp16 before the weight multiply, as rmsnorm_kernel does
-      const __half2 n = __floats2half2_rn(acc[i][2 * j] * rstd, acc[i][2 * j + 1] * rstd);
-      o[j] = as_u32(__hmul2(n, as_h2(gw[j])));
-    }
-    *reinterpret_cast<uint4*>(a.out + (size_t)row * a.d + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  if (C > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrive at the start
+  if (tid == 0) {
+    float t = 0.f;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    for (int i = 0; i < nwarps; ++i) t += red[i];
+    if (C == 1) css[0] = t;
+    else
+      for (int c = 0; c < C; ++c) comm_st_cluster_f32(&css[crank], c, t);
   }
+  if (C > 1) comm_cluster_barrier();   // every CTA of the row has read the epoch and pushed its sum
+  else __syncthreads();
+  if (crank == 0 && tid == 0) epochs[row] = epoch;
+  if (!a.w || !active) return;
+  float tot = 0.f;
+#pragma unroll
+  for (int c = 0; c < C; ++c) tot += css[c];
+  const float rstd = rsqrtf(tot / (float)a.d + a.eps);
+  const uint4 g = *reinterpret_cast<const uint4*>(a.w + (size_t)v * 8);
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // the normalised value is rounded to fp16 before the weight multiply, as rmsnorm_kernel does
+    const __half2 n = __floats2half2_rn(acc[2 * j] * rstd, acc[2 * j + 1] * rstd);
+    o[j] = as_u32(__hmul2(n, as_h2(gw[j])));
+  }
+  *reinterpret_cast<uint4*>(a.out + (size_t)row * a.d + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <int W>
-static cudaError_t launch_w(const CommArgs& a, int rows, int nv, cudaStream_t st) {
-  constexpr int MAXT = W >= 8 ? 512 : 1024;
-  const int vpt = nv <= MAXT ? 1 : (nv <= 2 * MAXT ? 2 : 4);
-  const int block = std::min(MAXT, ((nv + vpt - 1) / vpt + 31) / 32 * 32);
+template <int W, int C>
+static cudaError_t launch_wc(const CommArgs& a, int rows, int nv, cudaStream_t st) {
+  const int block = std::min(256, ((nv + C - 1) / C + 31) / 32 * 32);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(rows);
+  cfg.gridDim = dim3(C, rows);
   cfg.blockDim = dim3(block);
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  switch (vpt) {
-    case 1: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 1, MAXT>, a);
-    case 2: return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 2, MAXT>, a);
-    default:
-      if constexpr (W >= 8) return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, 4, MAXT>, a);
-      return cudaErrorInvalidValue;
+  int na = 1;
+  if (C > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = C;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
   }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, allreduce_add_rmsnorm_kernel<W, C>, a);
+}
+
+// CTAs per row: enough that a CTA has at most 256 vectors (4 KiB of the row), at most 8
+template <int W>
+static cudaError_t launch_w(const CommArgs& a, int rows, int nv, cudaStream_t st) {
+  if (nv > 1024) return launch_wc<W, 8>(a, rows, nv, st);
+  if (nv > 256) return launch_wc<W, 4>(a, rows, nv, st);
+  return launch_wc<W, 1>(a, rows, nv, st);
 }
 
 }  // namespace qfb
@@ -318,7 +330,7 @@ int qfb_comm_create(int rank, int world, void* const* bases, size_t slot_bytes, 
   (void)cudaGetDevice(&c->device);
   c->slot_bytes = (slot_bytes + 255) / 256 * 256;
   for (int r = 0; r < kCommMaxWorld; ++r) c->base[r] = r < world ? static_cast<char*>(bases[r]) : nullptr;
-  c->timeout_ns = 5000000000ull;
+  c->timeout_ns = 2000000000ull;
   *out = c;
   return QFB_OK;
 }
