@@ -13,8 +13,8 @@
 // Protocol.  Every rank owns one symmetric buffer (same layout on every rank, mapped into every
 // peer): a header and two data slots; a slot holds this rank's own partial (plain fp16, written by
 // the row-parallel GEMV as its output) and one RECEIVE region per source rank.  The reduction
-// kernel runs one CTA per batch row and needs no flag exchange and no fence: the flag travels
-// inside the data.
+// kernel runs one thread-block cluster per batch row (a 16-byte vector of the row per thread) and
+// needs no flag exchange and no fence: the flag travels inside the data.
 //   1. every thread reads its 16 bytes of the local partial and stores them into this rank's
 //      receive region of every PEER's buffer as four 8-byte words {4 data bytes, epoch} (two
 //      16-byte peer stores per peer; an 8-byte word is written atomically, so a word whose epoch
@@ -27,7 +27,7 @@
 //      Epochs only ever grow, so stale words never match and a replayed CUDA graph needs no
 //      reset; the epoch of a row lives in the local header and is advanced by the kernel itself.
 //   3. the thread sums the W partials in rank order in fp32 (bit-identical on every rank), adds
-//      the residual stream, and the CTA applies the RMS norm.
+//      the residual stream, and the cluster applies the RMS norm.
 // Data slots alternate between consecutive reductions.  A peer can run at most one reduction ahead
 // of this rank (its next row-parallel GEMV needs the result of the current reduction, hence this
 // rank's partial of it), so it writes the other slot while this one is still being read.
