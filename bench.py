@@ -620,14 +620,14 @@ def main():
             import ctypes
 
             fwd, dref = _native.lib().qfb_linear_forward, ctypes.byref(L._desc)
-            args = (dref, xe.data_ptr(), 1, ye.data_ptr(), L._ws.data_ptr(), L._ws_bytes, flags,
-                    torch.cuda.current_stream(dev).cuda_stream)
+            call_args = (dref, xe.data_ptr(), 1, ye.data_ptr(), L._ws.data_ptr(), L._ws_bytes, flags,
+                         torch.cuda.current_stream(dev).cuda_stream)
             for _ in range(20):
-                fwd(*args)
+                fwd(*call_args)
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             for _ in range(400):
-                fwd(*args)
+                fwd(*call_args)
             abi_s = time.perf_counter() - t0
             torch.cuda.synchronize()
             extras["eager"] = {"layer": "4096x4096 M=1", "module_host_us_per_call": round(host_s / 400 * 1e6, 2),
