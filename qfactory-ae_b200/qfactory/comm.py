@@ -87,7 +87,38 @@ class PeerComm:
                 opened.append(p.value)
         comm = cls(rank, world, bases, d, slot_rows, device, owned=base, opened=opened)
         dist.barrier(group)   # every rank has mapped every buffer before anyone raises a flag
+        try:
+            comm.self_check(group)
+        except Exception:
+            comm.close()
+            raise
         return comm
+
+    def self_check(self, group=None) -> None:
+        """One reduction per slot on a known pattern with a short wait limit, compared with the sum
+        it must give; every rank raises if any rank saw a wrong sum or a wait that ran out, so that
+        a node whose peer mappings do not carry stores is found at construction, not in the middle
+        of a decode step."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)                      # all ranks enter together: the short limit below is safe
+        rows = min(2, self.slot_rows)
+        self.set_timeout_us(500_000)
+        good = True
+        try:
+            for which in (0, 1):
+                col = torch.arange(self.d, device=self.device, dtype=torch.float32) % 7
+                self.slot(which, rows).copy_(((self.rank + 1) * (col + 1) / 8).half().expand(rows, self.d))
+                got = self.allreduce_add_rmsnorm(which, None, None, rows)
+                want = (self.world * (self.world + 1) / 2 * (col + 1) / 8).half().expand(rows, self.d)
+                torch.cuda.synchronize(self.device)
+                good = good and bool(torch.equal(got, want))
+            good = good and self.read_status() == 0
+        finally:
+            self.set_timeout_us(2_000_000)
+        ok = torch.tensor([1 if good else 0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok[0]) == 0:
+            raise RuntimeError("peer-memory reduction self-check failed" + ("" if good else " on this rank"))
 
     @classmethod
     def local_emulation(cls, rank, world, d, slot_rows, device="cuda"):

@@ -165,6 +165,7 @@ class QuantDecoder(torch.nn.Module):
                     from .comm import PeerComm
 
                     self.comm = PeerComm.from_process_group(cfg.d_model, 64, torch.device(device))
+                    self.comm.set_timeout_us(500_000)   # ranks of one node are never this far apart inside a step
                 except Exception as e:  # peers not mappable (no peer access, IPC closed): NCCL serves every reduction
                     self.comm_error = str(e)[:160]
                 # all ranks must agree, or their call sequences diverge
@@ -321,8 +322,19 @@ def run_decode(model: QuantDecoder, prompt_len: int = 128, steps: int = 256, use
             s = torch.cuda.Stream(device=dev)
             s.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(s):
-                for _ in range(2):                              # warm up outside capture
+                for i in range(2):                              # warm up outside capture
                     model(tok, pos)
+                    if i == 0 and model.comm is not None:
+                        # a wait that ran out in the first step: every rank drops to the process group's
+                        # all-reduce before anything is captured
+                        import torch.distributed as dist
+
+                        torch.cuda.synchronize(dev)
+                        bad = torch.tensor([model.comm.read_status()], device=dev)
+                        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+                        if int(bad[0]) != 0:
+                            model.close()
+                            model.comm_error = "a bounded wait ran out in the warm-up step"
             torch.cuda.current_stream(dev).wait_stream(s)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
