@@ -206,6 +206,28 @@ def test_llama70b_mlp_shapes_sampled_rows(N, K, M, layout_kind):
     assert np.abs(got - want).max() <= TOL * float(y.float().abs().max())
 
 
+# the layer shapes of the other model families the reference sweeps (its size and bit-width figures):
+# each distinct (N, K) once, at full size, on the layout the sweep runs
+_FAMILY_SHAPES = [(5120, 5120), (27648, 5120), (5120, 13824), (15360, 5120), (57344, 8192), (10240, 8192),
+                  (3584, 3584), (37888, 3584), (3584, 18944), (4608, 3584), (55296, 5120), (5120, 27648),
+                  (7168, 5120), (59392, 8192), (8192, 29696), (16384, 16384)]
+
+
+@pytest.mark.parametrize("N,K", _FAMILY_SHAPES)
+@pytest.mark.parametrize("M", [1, 16])
+def test_other_family_shapes_sampled_rows(N, K, M):
+    """K = 3584, 13824, 18944, 27648, 29696 are not powers of two (28 ... 232 batches of 128 k): the
+    split-K ranges are uneven there.  Sampled output rows against the oracle, fragment layout."""
+    layer, x = _random_packed_layer(N, K, 4, 128, M, "fragment", seed=N + K + M)
+    y = layer(x.cuda())
+    assert _native.last_launch()["kernel"] == 3
+    rows = torch.tensor([0, 1, 127, 128, N // 2 + 5, N - 1])
+    want = _sampled_oracle(layer, x, rows)
+    got = y[:, rows].float().cpu().numpy()
+    assert np.isfinite(y.float().cpu().numpy()).all()
+    assert np.abs(got - want).max() <= TOL * float(y.float().abs().max())
+
+
 @pytest.mark.parametrize("layout_kind", LAYOUTS)
 @pytest.mark.parametrize("N,K", [(28672, 8192), (8192, 28672)])
 def test_full_size_properties_mlp70b(N, K, layout_kind):
