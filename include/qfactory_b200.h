@@ -334,6 +334,24 @@ void* qfb_comm_region(const qfb_comm* comm, int slot, int source_rank);
 int qfb_comm_epoch(qfb_comm* comm, int row, void* stream, unsigned* epoch_out);
 int qfb_allreduce_add_rmsnorm(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,
                               float eps, void* stream);
+/* The same reduction when the kernel that wrote the partial has already sent it to the peers
+ * (qfb_linear_forward_reduce below): the launch only collects, sums, adds and normalises. */
+int qfb_allreduce_add_rmsnorm_pushed(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,
+                                     float eps, void* stream);
+/* A row-parallel linear fused with the first half of its reduction (reference: the matmul and the
+ * collective call are separate steps, third_party/vllm-bitblas/vllm/model_executor/layers/linear.py:1100-1124):
+ * y = x . dequant(W)^T is this rank's partial [m, n] of a sum over the ranks; the kernel writes it into
+ * data slot `slot` of the communicator and, as it stores each result, also sends it to every peer (plain
+ * peer stores, the reduction's epoch attached to every 4 bytes).  Follow it with
+ * qfb_allreduce_add_rmsnorm_pushed on the same slot.  Up to 16 rows of a 4-bit fragment-layout layer
+ * (groups of 128 or more, or group-less) whose n is a multiple of 128 and equals the communicator's row
+ * width; otherwise QFB_ERR_UNSUPPORTED (use
+ * qfb_linear_forward with y = qfb_comm_slot(...) and the plain reduction instead).  The second form takes
+ * the fused gate/up tensor of qfb_linear_silu_mul_forward. */
+int qfb_linear_forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot,
+                              void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+int qfb_linear_silu_mul_forward_reduce(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
+                                       void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
 int qfb_comm_read_status(qfb_comm* comm, void* stream, unsigned* status_out);
 int qfb_comm_last_cuda_error(void);
 

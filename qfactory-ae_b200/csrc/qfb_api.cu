@@ -475,7 +475,7 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits, bool a
 
 // `act`: x is a fused gate/up tensor [m, 2k] and the layer's input is silu(gate) * up
 static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
-                   unsigned flags, cudaStream_t st, bool act = false) {
+                   unsigned flags, cudaStream_t st, bool act = false, const PushTarget* push = nullptr) {
   const int x_stride = act ? 2 * v.k : v.k;
   for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
     const int rows = std::min(kMaxMmaRows, m - m0);
@@ -500,6 +500,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.batches_per_cta = (p.batches + pl.split - 1) / pl.split;
     p.act_offset = (int)mma_stage_bytes(rows, pl.nt, p.batches_per_cta);
     p.stall_test = (flags & QFB_FLAG_TEST_STALLED_WAIT) ? 1 : 0;
+    if (push) p.push = *push;   // (callers pass it for single-pass launches only)
     p.batches_div = p.batches / pl.split;
     p.batches_mod = p.batches % pl.split;
     p.zconst = v.zconst;
@@ -726,6 +727,37 @@ int qfb_linear_silu_mul_forward(const qfb_layer* layer, const void* gate_up, int
   if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows) return QFB_ERR_UNSUPPORTED;
   return run_mma(v, static_cast<const __half*>(gate_up), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                  static_cast<cudaStream_t>(stream), true);
+}
+
+// The row-parallel linears of a tensor-parallel decoder: the partial goes into the communicator's data slot
+// AND, in the wire format of the reduction, into this rank's receive region of every peer.
+static int forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, void* workspace,
+                          size_t workspace_bytes, unsigned flags, void* stream, bool act) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (!comm || !x) return QFB_ERR_NULL_POINTER;
+  if (m <= 0) return m == 0 ? QFB_OK : QFB_ERR_BAD_SHAPE;
+  if (!aligned16(x) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
+  // served by the mma.sync GEMV in one pass, on layers whose output rows are whole aligned quads
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows || v.n % 128 != 0) return QFB_ERR_UNSUPPORTED;
+  if (v.bits != 4 || v.group_size == 64) return QFB_ERR_UNSUPPORTED;   // (the sending build exists for these only)
+  PushTarget t;
+  void* own = nullptr;
+  st = comm_push_target(comm, slot, m, v.n, &t, &own);
+  if (st != QFB_OK) return st;
+  return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(own), workspace, workspace_bytes, flags,
+                 static_cast<cudaStream_t>(stream), act, &t);
+}
+
+int qfb_linear_forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, void* workspace,
+                              size_t workspace_bytes, unsigned flags, void* stream) {
+  return forward_reduce(layer, x, m, comm, slot, workspace, workspace_bytes, flags, stream, false);
+}
+
+int qfb_linear_silu_mul_forward_reduce(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
+                                       void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+  return forward_reduce(layer, gate_up, m, comm, slot, workspace, workspace_bytes, flags, stream, true);
 }
 
 int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host, void* x_staging,

@@ -62,6 +62,7 @@ struct CommArgs {
   int rank, d;
   float eps;
   unsigned long long timeout_ns;
+  int pushed;                  // 1: the kernel that wrote the local partial has already sent it to the peers
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -117,14 +118,16 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const CommAr
   uint4 mine = make_uint4(0, 0, 0, 0);
   if (active) {
     mine = *reinterpret_cast<const uint4*>(a.local + own_off + (size_t)v * 16);   // written by the preceding kernel
-    const size_t off = recv_row + (size_t)a.rank * a.region_bytes + (size_t)v * 32;
-    const uint4 lo = make_uint4(mine.x, epoch, mine.y, epoch), hi = make_uint4(mine.z, epoch, mine.w, epoch);
+    if (!a.pushed) {
+      const size_t off = recv_row + (size_t)a.rank * a.region_bytes + (size_t)v * 32;
+      const uint4 lo = make_uint4(mine.x, epoch, mine.y, epoch), hi = make_uint4(mine.z, epoch, mine.w, epoch);
 #pragma unroll
-    for (int r = 0; r < W; ++r)
-      if (r != a.rank) {
-        st_sys_v4(a.base[r] + off, lo);
-        st_sys_v4(a.base[r] + off + 16, hi);
-      }
+      for (int r = 0; r < W; ++r)
+        if (r != a.rank) {
+          st_sys_v4(a.base[r] + off, lo);
+          st_sys_v4(a.base[r] + off + 16, hi);
+        }
+    }
   }
 
   // ---- poll the peers' words of this thread in local memory until they carry the epoch; every pass
@@ -264,6 +267,25 @@ struct qfb_comm {
   unsigned long long timeout_ns;
 };
 
+// bytes of one data slot: the own partial + a receive region ({data, epoch} words: twice the size) per source rank
+static size_t comm_slot_span(size_t slot_bytes) { return slot_bytes * (1 + 2 * (size_t)kCommMaxWorld); }
+
+namespace qfb {
+int comm_push_target(const qfb_comm* c, int slot, int rows, int d, PushTarget* t, void** own_slot) {
+  if (!c || !t || !own_slot) return QFB_ERR_NULL_POINTER;
+  if (slot < 0 || slot > 1 || rows <= 0 || d <= 0 || d % 128 != 0) return QFB_ERR_BAD_SHAPE;
+  if (rows > kCommMaxRows || (size_t)rows * d * 2 > c->slot_bytes) return QFB_ERR_TOO_LARGE;
+  const size_t slot_offset = kCommDataOffset + (size_t)slot * comm_slot_span(c->slot_bytes);
+  for (int r = 0; r < 8; ++r) t->base[r] = r < c->world ? c->base[r] : nullptr;
+  t->world = c->world;
+  t->rank = c->rank;
+  t->recv_offset = slot_offset + c->slot_bytes + (size_t)c->rank * 2 * c->slot_bytes;
+  t->epochs = reinterpret_cast<const unsigned*>(c->base[c->rank]) + 1;
+  *own_slot = c->base[c->rank] + slot_offset;
+  return QFB_OK;
+}
+}  // namespace qfb
+
 static thread_local int tl_comm_cuda_error = 0;
 static int comm_check(cudaError_t e) {
   if (e == cudaSuccess) return QFB_OK;
@@ -275,9 +297,6 @@ static int comm_check(cudaError_t e) {
 extern "C" {
 
 int qfb_comm_last_cuda_error(void) { return tl_comm_cuda_error; }
-
-// bytes of one data slot: the own partial + a receive region ({data, epoch} words: twice the size) per source rank
-static size_t comm_slot_span(size_t slot_bytes) { return slot_bytes * (1 + 2 * (size_t)kCommMaxWorld); }
 
 size_t qfb_comm_buffer_bytes(size_t slot_bytes) { return kCommDataOffset + 2 * comm_slot_span((slot_bytes + 255) / 256 * 256); }
 
@@ -352,8 +371,21 @@ void* qfb_comm_region(const qfb_comm* c, int slot, int source_rank) {  // receiv
          (size_t)source_rank * 2 * c->slot_bytes;
 }
 
+static int allreduce_impl(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
+                          int pushed, void* stream);
+
 int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
                               void* stream) {
+  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 0, stream);
+}
+
+int qfb_allreduce_add_rmsnorm_pushed(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d,
+                                     float eps, void* stream) {
+  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 1, stream);
+}
+
+static int allreduce_impl(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
+                          int pushed, void* stream) {
   if (!c) return QFB_ERR_NULL_POINTER;
   if (slot < 0 || slot > 1 || rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;
   if (rows == 0) return QFB_OK;
@@ -375,6 +407,7 @@ int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, voi
   a.d = d;
   a.eps = eps;
   a.timeout_ns = c->timeout_ns;
+  a.pushed = pushed;
   const int nv = d / 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (c->world) {

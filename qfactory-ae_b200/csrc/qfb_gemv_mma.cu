@@ -143,7 +143,10 @@ template <int RB> struct ScaleZero {
 // SEG64 = quantisation groups of 64 (a segment = 4 k-steps) instead of >= 128 (8 k-steps)
 // A segment is the run of k-steps whose MMA accumulator is folded into the results at once
 // with one scale and zero per row: min(group, 128) k.
-template <int BITS, int NT, int RB, bool SEG64>
+// PUSH  = the results are also sent to the peers of a tensor-parallel group (MmaParams::push); a build of its
+//         own, so that the plain kernel carries none of that code (measured: as a run-time branch in the
+//         store path it cost the 4-us launches of the small layers 0.6 us)
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH>
 __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
@@ -219,6 +222,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   // lane r of warp 0 issues row r; warp 0 waits for the bytes, the barrier below publishes them
   __shared__ __align__(8) uint64_t xbar;
   __shared__ int xabort;
+  __shared__ unsigned push_epoch[16];   // epoch of the reduction this launch feeds, per batch row
   // With p.act == 1 the activations are silu(gate) * up of a fused gate/up tensor [m, 2k]: the gate
   // and the up slices arrive by one bulk copy each and are combined in shared memory, with the
   // arithmetic of the stand-alone kernel (silu in fp32 rounded to fp16, then one fp16 product).
@@ -233,6 +237,8 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       ptx::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)p.m * (p.act ? 2u : 1u) + (p.stall_test ? 16u : 0u));
     }
     __syncwarp();
+    // (the reduction kernel that finished the previous epoch of these rows precedes this launch)
+    if (PUSH && lane < p.m) push_epoch[lane] = __ldcg(p.push.epochs + lane) + 1u;
     if (lane < p.m) {
       const __half* src = p.x + (size_t)lane * p.x_stride + (size_t)bb * 128;
       ptx::tma_bulk_g2s(ptx::smem_u32(x_s + (size_t)lane * xstride), src, row_bytes, bar);
@@ -419,12 +425,24 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     }
     return v;
   };
+  // the four fp16 results of a quad as two {data, epoch} words in this rank's receive region of every peer
+  auto push_quad = [&](int mm, int n, uint32_t lo, uint32_t hi) {
+    const unsigned ep = push_epoch[mm];
+    const size_t off = p.push.recv_offset + (size_t)mm * p.n * 4 + (size_t)(n >> 3) * 32 + (size_t)((n >> 2) & 1) * 16;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)   // (compile-time indices: the pointer array stays in the parameter bank)
+      if (r < p.push.world && r != p.push.rank)
+        asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p.push.base[r] + off), "r"(lo), "r"(ep),
+                     "r"(hi), "r"(ep)
+                     : "memory");
+  };
   auto store_quad = [&](int q, const float4& v) {
     const int mm = q >> 5, n = tile * kTileRows + (q & 31) * 4;
     __half* dst = p.y + (size_t)mm * p.n + n;
     if (n + 3 < p.n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
       const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
       *reinterpret_cast<uint2*>(dst) = make_uint2(as_u32(lo), as_u32(hi));
+      if (PUSH) push_quad(mm, n, as_u32(lo), as_u32(hi));   // (such layers have whole, aligned quads only)
     } else {
       const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -550,6 +568,15 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     if (j < J && i < nout && n < p.n) p.y[(size_t)(i >> 7) * p.n + n] = __float2half_rn(s[j]);
   }
   if (tid == 0) p.counters[tile] = 0u;
+  if (PUSH) {
+    // this path stores single outputs: send the tile's results from where they were just written
+    __syncthreads();
+    for (int q = tid; q < nq; q += blockDim.x) {
+      const int mm = q >> 5, n = tile * kTileRows + (q & 31) * 4;
+      const uint2 yv = __ldcg(reinterpret_cast<const uint2*>(p.y + (size_t)mm * p.n + n));
+      push_quad(mm, n, yv.x, yv.y);
+    }
+  }
 }
 
 // Two register budgets of the same body: CTAs of up to 256 threads with 128 registers per thread
@@ -558,18 +585,25 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // either way).  Tighter budgets that would leave room for the next launch's CTAs to become
 // resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
 // k-step loop and were 5-70 % slower on every Llama-7B layer shape.
-template <int BITS, int NT, int RB, bool SEG64>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH>(p);
 }
-template <int BITS, int NT, int RB, bool SEG64>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false>
 __global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH>(p);
 }
 
 template <int BITS, int NT, int RB, bool SEG64>
 static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
   auto kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64> : gemv_mma_kernel<BITS, NT, RB, SEG64>;
+  if (p.push.world) {
+    // the sending build: 4-bit layers with groups of 128 and more (what the decoder's row-parallel layers are)
+    if constexpr (BITS == 4 && !SEG64)
+      kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, NT, RB, false, true> : gemv_mma_kernel<4, NT, RB, false, true>;
+    else
+      return cudaErrorNotSupported;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(block);

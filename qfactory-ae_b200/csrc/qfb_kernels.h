@@ -35,6 +35,16 @@ int record_cuda_error(cudaError_t e);
 size_t scratch_clear_bytes(int n);
 
 // mma.sync split-K kernel over the fragment layout (2/4/8-bit, m <= 16 per launch)
+// Row-parallel linears of a tensor-parallel decoder: where the result is one rank's PARTIAL of a sum over
+// the ranks, the kernel that stores it also sends it to the peers, in the wire format of the peer-memory
+// reduction (qfb_comm.cu): every 4 data bytes followed by the call's epoch, stored into this rank's
+// receive region of every peer's symmetric buffer.  world == 0: nothing is sent.
+struct PushTarget {
+  char* base[8];           // the ranks' symmetric buffers (entries >= world unused)
+  int world, rank;
+  size_t recv_offset;      // byte offset, inside every buffer, of this rank's receive region of the slot (row 0)
+  const unsigned* epochs;  // local header: epoch of the last finished reduction per batch row
+};
 struct MmaParams {
   const uint4* qw;
   const __half* qs;      // null: scale 1 (group-less)
@@ -61,6 +71,7 @@ struct MmaParams {
   int act_offset;        // byte offset of the up-slice staging region in dynamic shared memory (act only)
   int stall_test;        // 1 (QFB_FLAG_TEST_STALLED_WAIT): the activation barrier expects 16 bytes that never
                          // come and gives up after ~100 us, so that the bounded-wait path can be tested
+  PushTarget push;       // row-parallel layer of a tensor-parallel decoder: y is also sent to the peers
 };
 // CTAs of the mma.sync GEMV of up to this many threads run the 96-register build (five per SM)
 constexpr int kMmaSmallBlock = 128;
@@ -68,6 +79,12 @@ constexpr int kMmaSmallBlock = 128;
 int mma_rows_per_warp(int bits, int nt);
 // clusters of `cluster` CTAs of the mma.sync GEMV the current device holds at once (cached)
 int mma_max_active_clusters(int bits, int nt, bool seg64, int block, size_t smem, int cluster);
+}  // namespace qfb
+struct qfb_comm;
+namespace qfb {
+// Where a row-parallel GEMV that feeds data slot `slot` of a communicator must send its [rows, d] partial
+// (`t`), and the local plain-fp16 copy it must write as its output (`own_slot`).  A status code.
+int comm_push_target(const qfb_comm* c, int slot, int rows, int d, PushTarget* t, void** own_slot);
 cudaError_t launch_gemv_mma(const MmaParams& p, int bits, int nt, dim3 grid, int block, size_t smem, bool pdl,
                             cudaStream_t st);
 

@@ -148,12 +148,42 @@ class PeerComm:
     def fits(self, rows: int, d: int) -> bool:
         return d == self.d and 0 < rows <= self.slot_rows
 
-    def allreduce_add_rmsnorm(self, which, x, weight, rows, eps=1e-5, out=None):
+    def linear_into_slot(self, layer, x, which, rows, silu_mul=False, push=True) -> bool:
+        """Run the row-parallel `layer` on `x` ([rows, k], or the fused gate/up tensor [rows, 2k] with
+        `silu_mul`) with data slot `which` as its output.  Returns True when the kernel also sent the
+        partial to the peers while storing it (one launch for the linear and the first half of the
+        reduction; reference: matmul, then a collective call,
+        third_party/vllm-bitblas/vllm/model_executor/layers/linear.py:1100-1124): the reduction must
+        then be called with `pushed=True`.  Where that kernel does not serve the layer or the batch,
+        the plain forward runs with the slot as `out=` and False is returned."""
+        if push and layer.out_features == self.d and 0 < rows <= 16:
+            if layer._desc is None:
+                layer._prepare()
+            x2 = x.reshape(rows, -1)
+            if not x2.is_contiguous():
+                x2 = x2.contiguous()
+            fn = self._lib.qfb_linear_silu_mul_forward_reduce if silu_mul else self._lib.qfb_linear_forward_reduce
+            if (not silu_mul) or layer.silu_mul_supported(rows):
+                st = fn(layer._desc_ref, x2.data_ptr(), rows, self._h, which, layer._ws_ptr, layer._ws_bytes, layer.flags,
+                        torch.cuda.current_stream(self.device).cuda_stream)
+                if st == 0:
+                    return True
+                if st != 3:   # QFB_ERR_UNSUPPORTED: fall through to the two-step form
+                    _native.check(st, "qfb_linear_forward_reduce")
+        if silu_mul:
+            layer.forward_silu_mul(x, out=self.slot(which, rows))
+        else:
+            layer(x, out=self.slot(which, rows))
+        return False
+
+    def allreduce_add_rmsnorm(self, which, x, weight, rows, eps=1e-5, out=None, pushed=False):
         """Sum slot `which` over the ranks; `x` (fp16 [rows, d], may be None) += the sum in place;
-        returns the RMS norm of the row with `weight` (or the row itself when `weight` is None)."""
+        returns the RMS norm of the row with `weight` (or the row itself when `weight` is None).
+        `pushed`: the partial was already sent to the peers (`linear_into_slot` returned True)."""
         if out is None:
             out = torch.empty(rows, self.d, dtype=torch.float16, device=self.device)
-        st = self._lib.qfb_allreduce_add_rmsnorm(
+        fn = self._lib.qfb_allreduce_add_rmsnorm_pushed if pushed else self._lib.qfb_allreduce_add_rmsnorm
+        st = fn(
             self._h, which, None if x is None else x.data_ptr(), None if weight is None else weight.data_ptr(),
             out.data_ptr(), rows, self.d, eps, torch.cuda.current_stream(self.device).cuda_stream)
         if st != 0:
@@ -188,6 +218,15 @@ class PeerComm:
         data = partial.contiguous().view(torch.int32)                      # [rows, d / 2]
         packed = torch.stack((data, torch.full_like(data, epoch)), dim=-1).reshape(rows, self.d)
         words[:rows].copy_(packed)
+
+    def peer_words(self, r: int, which: int, source: int, rows: int) -> torch.Tensor:
+        """Emulation only: the {data, epoch} words [rows, d] (int32: data words at even positions, epochs
+        at odd ones) that rank `source` has stored into ITS receive region of slot `which` in rank `r`'s buffer."""
+        bases = getattr(self, "_emulated", None)
+        assert bases, "peer buffers are only addressable in the one-GPU emulation"
+        off = self._lib.qfb_comm_region(self._h, which, source) - self.bases[self.rank]
+        t = torch.as_tensor(_DevView(bases[r] + off, (self.slot_rows, 2 * self.d), self), device=self.device)
+        return t.view(torch.int32)[:rows]
 
     def close(self):
         L = self._lib

@@ -127,6 +127,7 @@ class QuantDecoder(torch.nn.Module):
         self.native_ops = native_ops
         self.fuse_silu = True   # False: SiLU * up as a launch of its own (tests compare the two)
         self.fuse_rope = True   # False: rotary embedding + cache write as a launch of its own before the attention
+        self.fuse_push = True   # False: the row-parallel linears only store their partial; the reduction kernel sends it
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         assert weights in ("packed", "seeded", "seeded_keep") and collective in ("auto", "nccl", "none")
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
@@ -249,8 +250,8 @@ class QuantDecoder(torch.nn.Module):
             if fused:
                 # row parallel: the partial goes straight into the communicator's slot; ONE launch then
                 # sums it over the ranks, adds it to the residual stream and applies the next norm
-                blk.o(att2d, out=self.comm.slot(0, R))
-                h = self.comm.allreduce_add_rmsnorm(0, x2, blk.norm2, R)
+                pushed = self.comm.linear_into_slot(blk.o, att2d, 0, R, push=self.fuse_push)
+                h = self.comm.allreduce_add_rmsnorm(0, x2, blk.norm2, R, pushed=pushed)
             else:
                 o = blk.o(att2d)
                 self._reduce(o)                                       # row parallel
@@ -266,14 +267,15 @@ class QuantDecoder(torch.nn.Module):
                 act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
                 down = lambda out=None: blk.down(act, out=out)
             if fused:
-                down(out=self.comm.slot(1, R))
+                pushed = self.comm.linear_into_slot(blk.down, gu if fuse_act else act, 1, R, silu_mul=fuse_act,
+                                                    push=self.fuse_push)
                 last = li + 1 == nblk
                 if not last:
-                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.blocks[li + 1].norm1, R)
+                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.blocks[li + 1].norm1, R, pushed=pushed)
                 elif T == 1:
-                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.final_norm, R)     # the final norm of every row
+                    h = self.comm.allreduce_add_rmsnorm(1, x2, self.final_norm, R, pushed=pushed)   # the final norm of every row
                 else:
-                    self.comm.allreduce_add_rmsnorm(1, x2, None, R, out=x2)            # x += sum; the final norm follows
+                    self.comm.allreduce_add_rmsnorm(1, x2, None, R, out=x2, pushed=pushed)          # x += sum; the final norm follows
                     h = None
                 pending = None
             else:

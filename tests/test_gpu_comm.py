@@ -109,3 +109,96 @@ def test_argument_checks():
         assert L.qfb_comm_max_rows() == 64
     finally:
         comm.close()
+
+
+# ---- the row-parallel GEMV that sends its partial while storing it ---------------------------------
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("M,path", [(1, "plan"), (3, "single"), (5, "cluster"), (16, "workspace"), (9, "plan")])
+def test_row_parallel_gemv_sends_its_partial_in_wire_format(world, M, path):
+    """`qfb_linear_forward_reduce`: the partial lands in the local slot (same bits as the plain forward)
+    AND, epoch attached, in this rank's receive region of every peer's buffer, through each of the
+    kernel's three store paths; the collect-only reduction then gives the reference result."""
+    from oracle import qf_oracle as O
+    from qfactory import QLinear
+
+    N, K, rank = 1024, 2048, 1
+    L = _native.lib()
+    x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=500 + M)
+    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="fragment")
+    xs = x.cuda()
+    comm = PeerComm.local_emulation(rank, world, N, 16)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    try:
+        if path == "single":
+            L.qfb_set_gemv_tuning(1, 2)
+        elif path == "cluster":
+            L.qfb_set_cluster_reduce(2); L.qfb_set_gemv_tuning(4, 1)
+        elif path == "workspace":
+            L.qfb_set_cluster_reduce(0); L.qfb_set_gemv_tuning(4, 1)
+        want = layer(xs).clone()
+        resid = torch.randn(M, N, generator=g, device="cuda").half()
+        w = (torch.rand(N, generator=g, device="cuda") + 0.5).half()
+        for call, slot in enumerate((0, 1, 0)):
+            ep = comm.next_epoch()
+            assert comm.linear_into_slot(layer, xs, slot, M) is True
+            torch.cuda.synchronize()
+            assert _native.last_launch()["kernel"] == 3
+            assert torch.equal(comm.slot(slot, M), want)
+            for r in range(world):
+                if r == rank:
+                    continue
+                words = comm.peer_words(r, slot, rank, M)
+                assert torch.equal(words[:, 0::2], want.view(torch.int32))
+                assert bool((words[:, 1::2] == ep).all())
+            parts = [want if r == rank else torch.randn(M, N, generator=g, device="cuda").half() for r in range(world)]
+            for r in range(world):
+                if r != rank:
+                    comm.write_peer_partial(r, slot, parts[r])
+            want_x, want_h = _reference(parts, resid, w)
+            h = comm.allreduce_add_rmsnorm(slot, resid, w, M, pushed=True)
+            torch.cuda.synchronize()
+            assert torch.equal(resid, want_x)
+            assert (h.float() - want_h.float()).abs().max() <= 2e-3 * want_h.float().abs().max()
+            assert comm.read_status() == 0
+    finally:
+        L.qfb_set_gemv_tuning(0, 0)
+        L.qfb_set_cluster_reduce(1)
+        comm.close()
+
+
+def test_fused_activation_row_parallel_gemv_sends_its_partial():
+    from qfactory import QLinear
+
+    M, N, K, rank, world = 2, 512, 1024, 0, 4
+    layer = QLinear.empty(M, K, N, 4, 128, sym=False, device="cuda", layout="fragment")
+    layer.w.random_(-128, 127); layer.s.uniform_(0.002, 0.02); layer.z.view(torch.uint8).random_(0, 15)
+    gu = torch.randn(M, 2 * K, device="cuda").half()
+    want = layer.forward_silu_mul(gu).clone()
+    comm = PeerComm.local_emulation(rank, world, N, 16)
+    try:
+        ep = comm.next_epoch()
+        assert comm.linear_into_slot(layer, gu, 1, M, silu_mul=True) is True
+        torch.cuda.synchronize()
+        assert torch.equal(comm.slot(1, M), want)
+        for r in range(1, world):
+            words = comm.peer_words(r, 1, rank, M)
+            assert torch.equal(words[:, 0::2], want.view(torch.int32)) and bool((words[:, 1::2] == ep).all())
+    finally:
+        comm.close()
+
+
+def test_layers_the_sending_gemv_does_not_serve_fall_back_to_two_steps():
+    from qfactory import QLinear
+
+    M, N, K = 2, 512, 1024
+    layer = QLinear.empty(M, K, N, 4, 128, sym=False, device="cuda", layout="tile")   # tile layout: not served
+    layer.w.random_(-128, 127); layer.s.uniform_(0.002, 0.02); layer.z.view(torch.uint8).random_(0, 15)
+    x = torch.randn(M, K, device="cuda").half()
+    want = layer(x).clone()
+    comm = PeerComm.local_emulation(0, 2, N, 16)
+    try:
+        assert comm.linear_into_slot(layer, x, 0, M) is False
+        torch.cuda.synchronize()
+        assert torch.equal(comm.slot(0, M), want)
+    finally:
+        comm.close()
