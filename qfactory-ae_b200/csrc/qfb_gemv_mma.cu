@@ -146,7 +146,10 @@ template <int RB> struct ScaleZero {
 // PUSH  = the results are also sent to the peers of a tensor-parallel group (MmaParams::push); a build of its
 //         own, so that the plain kernel carries none of that code (measured: as a run-time branch in the
 //         store path it cost the 4-us launches of the small layers 0.6 us)
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH>
+// LEAN  = a build without the fused-activation staging and without the reduction through the workspace, for
+//         the launches that need neither (measured: 1-3 % faster; the compiler schedules the common path
+//         better when the rare ones are not in the same function)
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN>
 __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
@@ -249,7 +252,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       atomicExch(p.status, 1u);
   }
   __syncthreads();
-  if (p.act) {
+  if (!LEAN && p.act) {
     const int vec_row = ncta * 16;  // 16-byte vectors per row of the slice
     for (int i = tid; i < p.m * vec_row; i += blockDim.x) {
       const int r = i / vec_row, j = i - r * vec_row;
@@ -485,6 +488,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     return;
   }
 
+  if (LEAN) return;  // (the lean build is only launched for S == 1 and in-cluster reductions)
   // split-K through the workspace: publish this CTA's partial, the last CTA of the tile to
   // arrive sums them in split order
   for (int q = tid; q < nq; q += blockDim.x) {
@@ -585,18 +589,21 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // either way).  Tighter budgets that would leave room for the next launch's CTAs to become
 // resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
 // k-step loop and were 5-70 % slower on every Llama-7B layer shape.
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN>(p);
 }
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false>
 __global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN>(p);
 }
 
 template <int BITS, int NT, int RB, bool SEG64>
 static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
   auto kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64> : gemv_mma_kernel<BITS, NT, RB, SEG64>;
+  if (!p.act && (p.cluster || grid.x == 1) && !p.push.world)
+    kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true>
+                                   : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true>;
   if (p.push.world) {
     // the sending build: 4-bit layers with groups of 128 and more (what the decoder's row-parallel layers are)
     if constexpr (BITS == 4 && !SEG64)
