@@ -277,10 +277,13 @@ __device__ __forceinline__ void splitk_reduce(const float* base0, size_t sstride
   }
 }
 
-template <int BITS, int NB, bool POST, int DG>
+// FRAG = the layer is in the fragment layout (a build of its own: with both decoders behind a run-time branch in
+// the decode loop the compiler allots registers for the larger of the two)
+template <int BITS, int NB, bool POST, int DG, bool FRAG>
 __global__ void __launch_bounds__(TcCfg<BITS, NB, POST, DG>::kThreads, (TcCfg<BITS, NB, POST, DG>::kTwoPerSM ? 2 : 1))
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
+  static_assert(!(FRAG && BITS == 3), "no 3-bit fragment layout");
   constexpr int NS = Cfg::kWStages;   // weight ring
   constexpr int NX = Cfg::kXStages;   // activation ring
   constexpr int R = Cfg::kRing;       // tensor-memory slot ring
@@ -376,7 +379,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
         const uint32_t bar = smem_u32(&bar_wfull[s]);
         // zeros / scales of the groups this stage touches: one group, or two when the group is 64
         mbar_arrive_expect_tx(bar, Cfg::kWBytes + zb + sb + ((p.stall_test && i == 0) ? 16u : 0u));
-        if (BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT) {
+        if (FRAG) {
           // the stage is two runs: 8 k-steps (128 * BITS bytes each) of the upper and of the lower 64 rows
           const uint8_t* f0 = reinterpret_cast<const uint8_t*>(p.qw) +
                               (((size_t)tile * 2) * (size_t)(p.kblocks * 8) + (size_t)(kb0 + i) * 8) * (128 * BITS);
@@ -448,7 +451,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
     // with groups of 64 the two halves of a stage belong to different groups: half h reads
     // the second record of the stage's zero / scale slot
     const int qsel = (p.halfstages_per_group == 1 && h == 1) ? kTileRows : 0;
-    const bool frag = BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT;
+    constexpr bool frag = FRAG;
     // position of the row's scale / zero inside the tile's 128 (fragment layers keep them in fragment order)
     const int qrow = qsel + (frag ? frag_pos_of_row(row) : row);
     for (int i = grp; i < nkb; i += DG) {
@@ -458,7 +461,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
       if (!mbar_wait(smem_u32(&bar_wfull[s]), phs, abortp, kSleepDecode, wait_limit)) break;
       const uint32_t z = has_z ? (uint32_t)gbase[z_off + s * Cfg::kZSlot + qrow] : p.zconst;
       __half2 d[32];
-      if (BITS != 3 && frag) StageDecodeFragment<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
+      if constexpr (FRAG) StageDecodeFragment<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
       else StageDecode<BITS>::run(gbase + w_off + s * Cfg::kWBytes, row, h, z, d);
       uint32_t rr[32];
       if (!POST && has_s) {
@@ -536,7 +539,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 #pragma unroll
       for (int j = 0; j < NB; ++j) acc[j] = 0.f;
       const size_t sz_row = (size_t)tile * p.groups * kTileRows +
-                            ((BITS != 3 && p.layout == QFB_LAYOUT_FRAGMENT) ? frag_pos_of_row(row) : row);
+                            (FRAG ? frag_pos_of_row(row) : row);
       const int stages_per_group = p.halfstages_per_group >> 1;  // POST needs groups of whole stages
       int r = 0;
       uint32_t phr = 0;
@@ -620,10 +623,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
+template <int BITS, int NB, bool POST, int DG, bool FRAG>
+static cudaError_t launch_cfg_layout(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st);
+
 template <int BITS, int NB, bool POST, int DG>
 static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
+  if (p.layout == QFB_LAYOUT_FRAGMENT) {
+    if constexpr (BITS != 3) return launch_cfg_layout<BITS, NB, POST, DG, true>(tm, p, grid, pdl, st);
+    else return cudaErrorInvalidValue;
+  }
+  return launch_cfg_layout<BITS, NB, POST, DG, false>(tm, p, grid, pdl, st);
+}
+
+template <int BITS, int NB, bool POST, int DG, bool FRAG>
+static cudaError_t launch_cfg_layout(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
-  auto kern = qgemm_tc_kernel<BITS, NB, POST, DG>;
+  auto kern = qgemm_tc_kernel<BITS, NB, POST, DG, FRAG>;
   // the attribute belongs to the (function, device) pair: set it on every launch, it is cheap
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
