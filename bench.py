@@ -306,7 +306,7 @@ def main():
         R = max(2, min(48, (400 << 20) // (N * K * bits // 8) + 1))
         ls = []
         for _ in range(R):
-            lay = "tile" if (args.layout == "fragment" and bits == 3) else args.layout  # no 3-bit fragment layout
+            lay = args.layout
             L = QLinear.empty(M, K, N, bits, gs, sym=sym, device=dev, layout=lay)
             L.w.random_(-128, 127)
             if L.s is not None:

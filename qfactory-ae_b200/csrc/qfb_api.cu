@@ -33,6 +33,9 @@ static int num_sms() {
 constexpr size_t kCounterAlign = 256;
 constexpr int kMaxSimtRows = 8;  // activation rows one SIMT launch handles
 constexpr int kMaxMmaRows = 16;  // activation rows one mma.sync GEMV launch handles
+// ... except on 3-bit layers, whose only build has one 8-column batch tile (96 bits per lane and k-step leave
+// no registers for a second one): 9..16 rows take two launches
+static int mma_pass_rows(int bits) { return bits == 3 ? 8 : kMaxMmaRows; }
 
 static thread_local int tl_last_cuda_error = 0;
 static thread_local int tl_last_launch[5] = {0, 0, 0, 0, 0};
@@ -67,8 +70,9 @@ static int validate_shape(int n, int k, int bits, int group_size) {
 static int validate_layout(int layout, int k, int bits, int group_size) {
   if (layout == QFB_LAYOUT_TILE) return QFB_OK;
   if (layout != QFB_LAYOUT_FRAGMENT) return QFB_ERR_UNSUPPORTED;
-  if (bits != 4 && bits != 8 && bits != 2) return QFB_ERR_UNSUPPORTED;
+  if (bits != 4 && bits != 8 && bits != 2 && bits != 3) return QFB_ERR_UNSUPPORTED;
   if (group_size != -1 && group_size != 64 && group_size % 128 != 0) return QFB_ERR_BAD_SHAPE;
+  if (bits == 3 && group_size == 64) return QFB_ERR_BAD_SHAPE;   // (3-bit groups are multiples of 128 in both layouts)
   return k % 128 == 0 ? QFB_OK : QFB_ERR_BAD_SHAPE;
 }
 
@@ -477,8 +481,9 @@ static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits, bool a
 static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
                    unsigned flags, cudaStream_t st, bool act = false, const PushTarget* push = nullptr) {
   const int x_stride = act ? 2 * v.k : v.k;
-  for (int m0 = 0; m0 < m; m0 += kMaxMmaRows) {
-    const int rows = std::min(kMaxMmaRows, m - m0);
+  const int pass_rows = mma_pass_rows(v.bits);
+  for (int m0 = 0; m0 < m; m0 += pass_rows) {
+    const int rows = std::min(pass_rows, m - m0);
     const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits, act);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
     MmaParams p = {};
@@ -639,7 +644,7 @@ size_t qfb_workspace_bytes(int m_max, int n, int k, int bits) {
       }
     }
   }
-  if (bits != 3 && k % 128 == 0) {  // fragment-layout layers: the mma.sync GEMV's split bound
+  if (k % 128 == 0) {  // fragment-layout layers: the mma.sync GEMV's split bound
     const size_t rows_mma = (size_t)std::min(m_max, kMaxMmaRows);
     partial = std::max(partial, (size_t)mma_split_cap(tiles, k / 128) * rows_mma * npad * sizeof(float));
   }
@@ -724,7 +729,7 @@ int qfb_linear_silu_mul_forward(const qfb_layer* layer, const void* gate_up, int
   if (!gate_up || !y) return QFB_ERR_NULL_POINTER;
   if (!aligned16(gate_up) || (reinterpret_cast<uintptr_t>(y) & 1u) || !aligned16(workspace)) return QFB_ERR_MISALIGNED;
   // served by the mma.sync GEMV only, whose activation staging does the combination
-  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows) return QFB_ERR_UNSUPPORTED;
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > mma_pass_rows(v.bits)) return QFB_ERR_UNSUPPORTED;
   return run_mma(v, static_cast<const __half*>(gate_up), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                  static_cast<cudaStream_t>(stream), true);
 }

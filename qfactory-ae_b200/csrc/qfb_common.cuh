@@ -210,10 +210,19 @@ __device__ __forceinline__ void frag4_fields(uint32_t w, uint32_t (&a)[4]) {
 //   2-bit: one word per PAIR of row blocks; the 2-bit field of (row block parity p, row half h,
 //          k offset kk) sits at bit 4p + 2h + 16 (kk & 1) + 8 (kk >> 1), so the four fields a row
 //          needs share one bit offset inside a half-word (and one power-of-two scale).
+//   3-bit: three words per lane and k-step for the four row blocks (96 bits = 32 codes), word j of all lanes
+//          a 128-byte plane of the step.  A half-word holds five 3-bit fields (bit offsets 0, 3, 6, 9, 12)
+//          and one spare bit.  Row blocks 0..2 live in word rb: rows g at offset 0 (k 4t, 4t+1 in the
+//          low / high half-word) and 9 (k 4t+2, 4t+3), rows g + 8 at offsets 3 and 12, so that one
+//          shift by 9 brings the second pair of fields onto the first.  Row block 3 takes what is
+//          left: offset 6 of word 0 (rows g, k 4t..), word 1 (rows g, k 4t+2..) and word 2 (rows g + 8,
+//          k 4t..), and for rows g + 8, k 4t+2.. the spare bits: code bit b is bit 15 (31 for the odd k)
+//          of word b.  All its fields are assembled at offset 6.
 // FragCodec<BITS>::decode builds the four A-fragment registers of row block rb from the lane's
 // words of a k-step; shift_lo / shift_hi are the bit offsets of the fields of rows g / g + 8
 // inside a half (the fp16 subnormal they form is q * 2^(shift - 24)).
 // word j of a lane and field position of code (rb, h, kk):
+// (2-, 4- and 8-bit: a code is one contiguous field; see frag_code_bit for the general form)
 __host__ __device__ inline int frag_word_of(int bits, int rb, int h) {
   return bits == 4 ? rb : bits == 8 ? rb * 2 + h : rb >> 1;
 }
@@ -222,7 +231,44 @@ __host__ __device__ inline int frag_bit_of(int bits, int rb, int h, int kk) {
   if (bits == 4) return 4 * ((kk >> 1) * 2 + (kk & 1) * 4 + h);
   return (rb & 1) * 4 + h * 2 + (kk & 1) * 16 + (kk >> 1) * 8;
 }
+// word of the lane and bit inside it that hold bit b of code (rb, h, kk), for every bit width
+__host__ __device__ inline void frag_code_bit(int bits, int rb, int h, int kk, int b, int* word, int* bit) {
+  if (bits != 3) {
+    *word = frag_word_of(bits, rb, h);
+    *bit = frag_bit_of(bits, rb, h, kk) + b;
+    return;
+  }
+  const int half = (kk & 1) * 16, khi = kk >> 1;
+  if (rb < 3) {
+    *word = rb;
+    *bit = half + h * 3 + khi * 9 + b;
+  } else if (h == 1 && khi == 1) {
+    *word = b;
+    *bit = half + 15;
+  } else {
+    *word = h == 1 ? 2 : khi;
+    *bit = half + 6 + b;
+  }
+}
 template <int BITS> struct FragCodec;
+template <> struct FragCodec<3> {
+  __device__ static __forceinline__ void decode(const uint32_t* v, int rb, uint32_t (&a)[4]) {
+    if (rb < 3) {
+      const uint32_t w = v[rb], hi = w >> 9;
+      a[0] = w & 0x00070007u;
+      a[1] = w & 0x00380038u;
+      a[2] = hi & 0x00070007u;
+      a[3] = hi & 0x00380038u;
+    } else {
+      a[0] = v[0] & 0x01C001C0u;
+      a[2] = v[1] & 0x01C001C0u;
+      a[1] = v[2] & 0x01C001C0u;
+      a[3] = ((v[0] >> 9) & 0x00400040u) | ((v[1] >> 8) & 0x00800080u) | ((v[2] >> 7) & 0x01000100u);
+    }
+  }
+  __host__ __device__ static constexpr int shift_lo(int rb) { return rb < 3 ? 0 : 6; }
+  __host__ __device__ static constexpr int shift_hi(int rb) { return rb < 3 ? 3 : 6; }
+};
 template <> struct FragCodec<4> {
   __device__ static __forceinline__ void decode(const uint32_t* v, int rb, uint32_t (&a)[4]) { frag4_fields(v[rb], a); }
   __host__ __device__ static constexpr int shift_lo(int) { return 0; }
@@ -253,6 +299,7 @@ template <> struct FragCodec<2> {
 // byte offset of word j of a lane inside the k-step of a 64-row half, and bytes of a k-step
 __host__ __device__ inline int frag_word_offset(int bits, int lane, int j) {
   if (bits == 8) return (j >> 2) * 512 + lane * 16 + (j & 3) * 4;
+  if (bits == 3) return j * 128 + lane * 4;
   return lane * (4 * bits) + j * 4;
 }
 __host__ __device__ inline int frag_step_bytes(int bits) { return 128 * bits; }

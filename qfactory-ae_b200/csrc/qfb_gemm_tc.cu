@@ -155,8 +155,43 @@ template <> struct StageDecodeFragment<2> {
       }
   }
 };
-template <> struct StageDecodeFragment<3> {  // no 3-bit fragment layout: never reached
-  __device__ static __forceinline__ void run(const uint8_t*, int, int, uint32_t, __half2 (&)[32]) {}
+template <> struct StageDecodeFragment<3> {
+  // word j of lane g*4+t sits in plane j (128 bytes) of the k-step (384 bytes).  Row blocks 0..2: word rb, the
+  // row's fields at bit offset 0 (rows g) or 3 (rows g + 8) for k 4t, 4t+1 and 9 bits higher for k 4t+2, 4t+3.
+  // Row block 3: offset 6 of words 0 / 1 (rows g) and of word 2 (rows g + 8, k 4t, 4t+1); rows g + 8,
+  // k 4t+2, 4t+3 are collected from the spare bits 15 / 31 of the three words.
+  __device__ static __forceinline__ void run(const uint8_t* w, int row, int h, uint32_t z, __half2 (&d)[32]) {
+    const int wt = row >> 6, rb = (row >> 4) & 3, hh = (row >> 3) & 1, g = row & 7;
+    const uint8_t* base = w + wt * 3072 + (4 * h) * 384 + g * 16;
+    if (rb < 3) {
+      // the field as the low mantissa bits of 2^(10 - offset): exact q + 2^(10 - offset), minus the same with z
+      const uint32_t mask = hh ? 0x00380038u : 0x00070007u, magic = hh ? 0x58005800u : 0x64006400u;
+      const __half2 zs = as_h2(magic | ((z << (hh ? 3 : 0)) * 0x00010001u));
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint32_t word = *reinterpret_cast<const uint32_t*>(base + ks * 384 + rb * 128 + t * 4);
+          d[ks * 8 + t * 2] = __hsub2(as_h2(lop3_and_or(word, mask, magic)), zs);
+          d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(lop3_and_or(word >> 9, mask, magic)), zs);
+        }
+    } else {
+      const uint32_t mask = 0x01C001C0u, magic = 0x4C004C00u;
+      const __half2 zs = as_h2(magic | ((z << 6) * 0x00010001u));
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint8_t* p = base + ks * 384 + t * 4;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(p), w1 = *reinterpret_cast<const uint32_t*>(p + 128),
+                         w2 = *reinterpret_cast<const uint32_t*>(p + 256);
+          const uint32_t spare = ((w0 >> 9) & 0x00400040u) | ((w1 >> 8) & 0x00800080u) | ((w2 >> 7) & 0x01000100u);
+          const uint32_t lo = hh ? (w2 & mask) : (w0 & mask), hi = hh ? spare : (w1 & mask);
+          d[ks * 8 + t * 2] = __hsub2(as_h2(lo | magic), zs);
+          d[ks * 8 + t * 2 + 1] = __hsub2(as_h2(hi | magic), zs);
+        }
+    }
+  }
 };
 template <> struct StageDecode<8> {
   // stage = [8 units][128 rows][16 B]; thread owns units 4h .. 4h+3
@@ -283,7 +318,6 @@ template <int BITS, int NB, bool POST, int DG, bool FRAG>
 __global__ void __launch_bounds__(TcCfg<BITS, NB, POST, DG>::kThreads, (TcCfg<BITS, NB, POST, DG>::kTwoPerSM ? 2 : 1))
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
-  static_assert(!(FRAG && BITS == 3), "no 3-bit fragment layout");
   constexpr int NS = Cfg::kWStages;   // weight ring
   constexpr int NX = Cfg::kXStages;   // activation ring
   constexpr int R = Cfg::kRing;       // tensor-memory slot ring
@@ -628,10 +662,7 @@ static cudaError_t launch_cfg_layout(const CUtensorMap& tm, const TcParams& p, d
 
 template <int BITS, int NB, bool POST, int DG>
 static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
-  if (p.layout == QFB_LAYOUT_FRAGMENT) {
-    if constexpr (BITS != 3) return launch_cfg_layout<BITS, NB, POST, DG, true>(tm, p, grid, pdl, st);
-    else return cudaErrorInvalidValue;
-  }
+  if (p.layout == QFB_LAYOUT_FRAGMENT) return launch_cfg_layout<BITS, NB, POST, DG, true>(tm, p, grid, pdl, st);
   return launch_cfg_layout<BITS, NB, POST, DG, false>(tm, p, grid, pdl, st);
 }
 

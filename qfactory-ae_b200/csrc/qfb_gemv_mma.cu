@@ -101,6 +101,22 @@ template <> struct Words<4> {
                  : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]) : "l"(p), "r"(pred));
   }
 };
+template <> struct Words<3> {  // (3-bit: the three words of a lane sit in three 128-byte planes of the k-step)
+  uint32_t v[3];
+  __device__ __forceinline__ void load(const void* p) {
+    const char* c = static_cast<const char*>(p);
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v[0]) : "l"(c));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v[1]) : "l"(c + 128));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v[2]) : "l"(c + 256));
+  }
+  __device__ __forceinline__ void load_if(const void* p, int pred) {
+    const char* c = static_cast<const char*>(p);
+    asm volatile(
+        "{\n.reg .pred q;\nsetp.ne.b32 q, %4, 0;\n@q ld.global.nc.L1::no_allocate.u32 %0, [%3];\n"
+        "@q ld.global.nc.L1::no_allocate.u32 %1, [%3+128];\n@q ld.global.nc.L1::no_allocate.u32 %2, [%3+256];\n}"
+        : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]) : "l"(c), "r"(pred));
+  }
+};
 template <> struct Words<2> {
   uint32_t v[2];
   __device__ __forceinline__ void load(const void* p) {
@@ -155,7 +171,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
   constexpr int NSEG = SEG64 ? 2 : 1;  // segments per 128-k batch
   constexpr int NW = RB * BITS / 4;    // words of a lane and k-step this warp holds
-  constexpr int NSLOT = NW >= 4 ? 1 : 2;  // register buffers of one batch each (32 registers in all, 16 for NW = 1)
+  constexpr int NSLOT = NW >= 3 ? 1 : 2;  // register buffers of one batch each (32 registers in all, 24 for NW = 3, 16 for NW = 1)
   constexpr int WPK = 8 / RB;          // warps per k-way: 128 rows / (16 * RB)
   extern __shared__ uint4 smem[];
 
@@ -675,6 +691,7 @@ static int query_clusters(int block, size_t smem, int cluster) {
     if (bits == 8 && nt == 1) return seg64 ? FN<8, 1, 2, true>(__VA_ARGS__) : FN<8, 1, 2, false>(__VA_ARGS__); \
     if (bits == 8 && nt == 2) return seg64 ? FN<8, 2, 2, true>(__VA_ARGS__) : FN<8, 2, 2, false>(__VA_ARGS__); \
     if (bits == 2 && nt == 1) return seg64 ? FN<2, 1, 4, true>(__VA_ARGS__) : FN<2, 1, 4, false>(__VA_ARGS__); \
+    if (bits == 3 && nt == 1 && !seg64) return FN<3, 1, 4, false>(__VA_ARGS__);                               \
     if (bits == 2 && nt == 2) return seg64 ? FN<2, 2, 2, true>(__VA_ARGS__) : FN<2, 2, 2, false>(__VA_ARGS__); \
   } while (0)
 

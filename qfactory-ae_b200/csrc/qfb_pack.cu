@@ -102,12 +102,20 @@ __global__ void pack_weight_frag_kernel(const PackParams p) {
   uint32_t word = 0;
   for (int rb = 0; rb < 4; ++rb)
     for (int h = 0; h < 2; ++h) {
-      if (frag_word_of(p.bits, rb, h) != j) continue;
       const int n = tile * kTileRows + wt * 64 + rb * 16 + h * 8 + g;
       if (n >= p.n) continue;
+      if (p.bits != 3 && frag_word_of(p.bits, rb, h) != j) continue;
       for (int kk = 0; kk < 4; ++kk) {
         const uint32_t q = (uint32_t)p.codes[(size_t)(k0 + kk) * p.n + n] & ((1u << p.bits) - 1u);
-        word |= q << frag_bit_of(p.bits, rb, h, kk);
+        if (p.bits != 3) {
+          word |= q << frag_bit_of(p.bits, rb, h, kk);
+        } else {  // bit by bit: one of the sixteen field pairs of a lane is spread over the spare bits of its three words
+          for (int b = 0; b < 3; ++b) {
+            int wj, bit;
+            frag_code_bit(3, rb, h, kk, b, &wj, &bit);
+            if (wj == j) word |= ((q >> b) & 1u) << bit;
+          }
+        }
       }
     }
   char* base = reinterpret_cast<char*>(p.qw) + ((size_t)(tile * 2 + wt) * ksteps + ks) * frag_step_bytes(p.bits);
@@ -298,6 +306,7 @@ cudaError_t launch_unpack(const UnpackParams& p, cudaStream_t st) {
     if (p.bits == 4) unpack_frag_kernel<4><<<gridf, block, 0, st>>>(p);
     else if (p.bits == 8) unpack_frag_kernel<8><<<gridf, block, 0, st>>>(p);
     else if (p.bits == 2) unpack_frag_kernel<2><<<gridf, block, 0, st>>>(p);
+    else if (p.bits == 3) unpack_frag_kernel<3><<<gridf, block, 0, st>>>(p);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
   }

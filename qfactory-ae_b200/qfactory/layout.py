@@ -205,26 +205,46 @@ def frag_bit_of(bits: int, rb: int, h: int, kk: int) -> int:
     return (rb & 1) * 4 + h * 2 + (kk & 1) * 16 + (kk >> 1) * 8
 
 
+def frag_code_bit(bits: int, rb: int, h: int, kk: int, b: int):
+    """(word of the lane, bit inside it) that holds bit b of code (rb, h, kk).  2-, 4- and 8-bit codes
+    are contiguous fields.  3-bit: three words per lane; a half-word holds five fields (offsets 0, 3,
+    6, 9, 12) and a spare bit; row blocks 0..2 live in word rb (rows g at offsets 0 / 9, rows g + 8 at
+    3 / 12 for k 4t.. / 4t+2..), row block 3 at offset 6 of words 0, 1 (rows g) and 2 (rows g + 8,
+    k 4t..) and, for rows g + 8, k 4t+2.., in the spare bits: bit b of the code is bit 15 (31) of word b."""
+    if bits != 3:
+        return frag_word_of(bits, rb, h), frag_bit_of(bits, rb, h, kk) + b
+    half, khi = (kk & 1) * 16, kk >> 1
+    if rb < 3:
+        return rb, half + h * 3 + khi * 9 + b
+    if h == 1 and khi == 1:
+        return b, half + 15
+    return (2 if h == 1 else khi), half + 6 + b
+
+
 def frag_word_slot(bits: int, lane: int, j: int) -> int:
     """Index (in 32-bit words) of word j of a lane inside a k-step."""
     if bits == 8:
         return (j >> 2) * 128 + lane * 4 + (j & 3)
+    if bits == 3:
+        return j * 32 + lane
     return lane * bits + j
 
 
 def fragment_supported(N: int, K: int, bits: int, GS: int) -> bool:
+    if bits == 3:
+        return K % 128 == 0 and (GS == -1 or GS % 128 == 0)
     return bits in (2, 4, 8) and K % 128 == 0 and (GS in (-1, 64) or GS % 128 == 0)
 
 
 def resolve_layout(layout, N: int, K: int, bits: int, GS: int, batch_size: int = 1) -> int:
     """'tile' | 'fragment' | 'auto' | 0 | 1 | None -> LAYOUT_*.  'auto' (and None) picks the fragment
-    layout whenever the shape allows it (2/4/8-bit, K % 128 == 0, group 64 or a multiple of 128): it
+    layout whenever the shape allows it (K % 128 == 0, group 64 or a multiple of 128): it
     feeds the fastest kernel up to 16 rows and the tcgen05 kernel within a few percent of the tile
     layout above.  `batch_size` is accepted for the callers' convenience and does not matter."""
     if layout in (LAYOUT_TILE, "tile"):
         return LAYOUT_TILE
     if layout in (LAYOUT_FRAGMENT, "fragment"):
-        assert fragment_supported(N, K, bits, GS), "the fragment layout needs 2/4/8-bit codes and K % 128 == 0"
+        assert fragment_supported(N, K, bits, GS), "the fragment layout needs K % 128 == 0 and groups of 64 (not 3-bit) or multiples of 128"
         return LAYOUT_FRAGMENT
     assert layout in (None, "auto"), f"unknown layout {layout!r}"
     return LAYOUT_FRAGMENT if fragment_supported(N, K, bits, GS) else LAYOUT_TILE
@@ -236,16 +256,18 @@ def frag_row_of_pos(device=None) -> torch.Tensor:
 
 
 def _frag_slots(bits: int, device):
-    """For every (rb, h, g, t, kk): word slot inside the k-step and bit position."""
-    slot = torch.empty(4, 2, 8, 4, 4, dtype=torch.int64)
-    bit = torch.empty(4, 2, 8, 4, 4, dtype=torch.int64)
+    """For every (rb, h, g, t, kk) and code bit b: word slot inside the k-step and bit position."""
+    slot = torch.empty(4, 2, 8, 4, 4, bits, dtype=torch.int64)
+    bit = torch.empty(4, 2, 8, 4, 4, bits, dtype=torch.int64)
     for rb in range(4):
         for h in range(2):
             for g in range(8):
                 for t in range(4):
                     for kk in range(4):
-                        slot[rb, h, g, t, kk] = frag_word_slot(bits, g * 4 + t, frag_word_of(bits, rb, h))
-                        bit[rb, h, g, t, kk] = frag_bit_of(bits, rb, h, kk)
+                        for b in range(bits):
+                            wj, pos = frag_code_bit(bits, rb, h, kk, b)
+                            slot[rb, h, g, t, kk, b] = frag_word_slot(bits, g * 4 + t, wj)
+                            bit[rb, h, g, t, kk, b] = pos
     return slot.to(device), bit.to(device)
 
 
@@ -259,7 +281,9 @@ def pack_weight_fragment(q: torch.Tensor, bits: int = 4) -> torch.Tensor:
     v = blk.view(T, 2, 4, 2, 8, K // 16, 4, 4).permute(0, 1, 5, 2, 3, 4, 6, 7)   # [tile, wt, ks, rb, h, g, t, kk]
     slot, bit = _frag_slots(bits, q.device)
     words = torch.zeros(T, 2, K // 16, 32 * bits, dtype=torch.int64, device=q.device)
-    words.scatter_add_(3, slot.flatten().expand(T, 2, K // 16, -1), (v << bit).reshape(T, 2, K // 16, -1))
+    planes = torch.arange(bits, device=q.device)
+    vbits = ((v.unsqueeze(-1) >> planes) & 1) << bit                                 # every code bit at its place
+    words.scatter_add_(3, slot.flatten().expand(T, 2, K // 16, -1), vbits.reshape(T, 2, K // 16, -1))
     return _words_to_bytes(words).reshape(Np, K * bits // 8).view(torch.int8)
 
 
@@ -268,7 +292,8 @@ def unpack_weight_fragment(w: torch.Tensor, N: int, K: int, bits: int = 4) -> to
     T = Np // TILE
     words = _bytes_to_words(w.contiguous().view(torch.uint8).view(T, 2, K // 16, 32 * bits, 4))
     slot, bit = _frag_slots(bits, w.device)
-    v = (words[..., slot.flatten()] >> bit.flatten()) & ((1 << bits) - 1)           # [tile, wt, ks, rb*h*g*t*kk]
+    vb = (words[..., slot.flatten()] >> bit.flatten()) & 1                           # [tile, wt, ks, rb*h*g*t*kk*b]
+    v = (vb.view(T, 2, K // 16, -1, bits) << torch.arange(bits, device=w.device)).sum(-1)
     v = v.view(T, 2, K // 16, 4, 2, 8, 4, 4).permute(0, 1, 3, 4, 5, 2, 6, 7)        # [tile, wt, rb, h, g, ks, t, kk]
     return v.reshape(Np, K)[:N].t().contiguous().to(torch.int32)
 

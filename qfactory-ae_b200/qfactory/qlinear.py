@@ -131,7 +131,7 @@ class _PackedLinear(torch.nn.Module):
 
     def silu_mul_supported(self, rows: int) -> bool:
         """True when `forward_silu_mul` runs as ONE kernel for `rows` activation rows."""
-        return self.packed_layout == layout.LAYOUT_FRAGMENT and 0 < rows <= 16
+        return self.packed_layout == layout.LAYOUT_FRAGMENT and 0 < rows <= (8 if self.n_bits == 3 else 16)
 
     def forward_silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """(silu(gate) * up) @ dequant(W)^T for gate_up [..., 2 * in_features] = [gate | up], the down

@@ -88,20 +88,52 @@ def test_layout_choice():
     assert R("auto", 4096, 4096, 4, 128, batch_size=512) == layout.LAYOUT_FRAGMENT   # any batch size
     assert R("auto", 4096, 4096, 8, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
     assert R("auto", 4096, 4096, 2, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
-    assert R("auto", 4096, 4096, 3, 128, batch_size=1) == layout.LAYOUT_TILE      # no 3-bit fragment layout
+    assert R("auto", 4096, 4096, 3, 128, batch_size=1) == layout.LAYOUT_FRAGMENT
     assert R("auto", 4096, 4160, 4, 64, batch_size=1) == layout.LAYOUT_TILE       # K % 128 != 0
     assert R("auto", 4096, 4224, 4, 192, batch_size=1) == layout.LAYOUT_TILE      # group neither 64 nor k*128
     assert R("tile", 4096, 4096, 4, 128, batch_size=1) == layout.LAYOUT_TILE
     with pytest.raises(AssertionError):
-        R("fragment", 4096, 4096, 3, 128)
+        R("fragment", 4096, 4096, 3, 64)           # 3-bit groups are multiples of 128 in both layouts
     L = _native.lib()
     assert L.qfb_layout_supported(1, 4096, 4096, 4, 128) == 1
     assert L.qfb_layout_supported(1, 4096, 4096, 8, 128) == 1
     assert L.qfb_layout_supported(1, 4096, 4096, 2, 128) == 1
-    assert L.qfb_layout_supported(1, 4096, 4096, 3, 128) == 0
+    assert L.qfb_layout_supported(1, 4096, 4096, 3, 128) == 1
+    assert L.qfb_layout_supported(1, 4096, 4096, 3, 64) == 0     # 3-bit groups are multiples of 128
     assert L.qfb_layout_supported(1, 4096, 4160, 4, 64) == 0
     assert L.qfb_layout_supported(0, 4096, 4160, 4, 64) == 1
     assert L.qfb_layout_supported(2, 4096, 4096, 4, 128) == 0
+
+
+def test_fragment_packer_three_bits_positions():
+    """3-bit: positions restated from the header, bit by bit (five fields and a spare bit per half-word)."""
+    torch.manual_seed(3)
+    K, N = 256, 200
+    q = torch.randint(0, 8, (K, N), dtype=torch.int32)
+    w = layout.pack_weight_fragment(q, 3)
+    assert w.shape == (256, K * 3 // 8)
+    assert torch.equal(layout.unpack_weight_fragment(w, N, K, 3), q)
+    words = layout._bytes_to_words(w.view(torch.uint8).reshape(-1, 4))
+    rnd = random.Random(3)
+    for _ in range(4000):
+        n, k = rnd.randrange(N), rnd.randrange(K)
+        tile, r = divmod(n, 128)
+        wt, r = divmod(r, 64)
+        rb, r = divmod(r, 16)
+        h, g = divmod(r, 8)
+        ks, kk = divmod(k, 16)
+        t, kk = divmod(kk, 4)
+        lane, half, khi = g * 4 + t, (kk & 1) * 16, kk >> 1
+        base = ((tile * 2 + wt) * (K // 16) + ks) * 96
+        code = int(q[k, n])
+        for b in range(3):
+            if rb < 3:
+                j, bit = rb, half + 3 * h + 9 * khi + b
+            elif h == 1 and khi == 1:
+                j, bit = b, half + 15
+            else:
+                j, bit = (2 if h else khi), half + 6 + b
+            assert (int(words[base + j * 32 + lane]) >> bit) & 1 == (code >> b) & 1
 
 
 @pytest.mark.parametrize("bits", [2, 8])
@@ -271,8 +303,11 @@ def test_fragment_forward_pdl_graph_and_default_layout():
     g.replay()
     torch.cuda.synchronize()
     _check(y, x, q, s, z)
-    other = QLinear.init(64, 2048, 512, 3, q.clamp(max=7).cuda(), 128, s.cuda(), z.clamp(max=7).cuda())  # 3-bit: tile layout
-    assert other.packed_layout == layout.LAYOUT_TILE
+    other = QLinear.init(64, 2048, 512, 3, q.clamp(max=7).cuda(), 128, s.cuda(), z.clamp(max=7).cuda())  # 3-bit too
+    assert other.packed_layout == layout.LAYOUT_FRAGMENT
+    odd = QLinear.init(4, 2048 + 64, 512, 4, torch.cat((q, q[:64])).cuda(), 64, torch.cat((s, s[:1])).repeat_interleave(2, 0)[: (2048 + 64) // 64].cuda(),
+                       torch.cat((z, z[:1])).repeat_interleave(2, 0)[: (2048 + 64) // 64].cuda())     # K % 128 != 0: tile layout
+    assert odd.packed_layout == layout.LAYOUT_TILE
 
 
 @pytest.mark.gpu
@@ -298,8 +333,8 @@ def test_fragment_forward_random_shapes_and_plans():
             K = 128 * rnd.choice([1, 2, 3, 5, 8, 11, 16, 24, 32])
             N = rnd.choice([1, 7, 100, 128, 129, 255, 300, 513, 700])
             M = rnd.randint(1, 16) if case % 4 else rnd.randint(17, 70)   # every fourth case: the tcgen05 kernel
-            bits = rnd.choice([2, 4, 4, 8])
-            gs_ok = [g for g in (64, 128, 256, 384) if K % g == 0] + [-1]
+            bits = rnd.choice([2, 3, 4, 4, 8])
+            gs_ok = [g for g in (64, 128, 256, 384) if K % g == 0 and not (bits == 3 and g == 64)] + [-1]
             GS = rnd.choice(gs_ok)
             sym = GS != -1 and rnd.random() < 0.3
             layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=5000 + case, bits=bits)
@@ -318,9 +353,11 @@ def test_fragment_forward_random_shapes_and_plans():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("bits", [2, 3, 8])
 @pytest.mark.parametrize("N,K,GS,sym", [(128, 128, 128, False), (200, 512, 64, False), (300, 1024, 256, True), (130, 256, -1, False)])
 def test_fragment_other_bit_widths_packer_and_inverse_bit_exact(bits, N, K, GS, sym):
+    if bits == 3 and GS == 64:
+        GS = 128
     layer, x, q, s, z = _frag_layer(1, N, K, GS, sym, seed=N + K + bits, bits=bits)
     assert torch.equal(layer.w.cpu().view(torch.uint8).flatten(),
                        layout.pack_weight_fragment(q, bits).view(torch.uint8).flatten())
@@ -332,10 +369,12 @@ def test_fragment_other_bit_widths_packer_and_inverse_bit_exact(bits, N, K, GS, 
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("bits", [2, 3, 8])
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 21, 40, 70, 130, 300])
 @pytest.mark.parametrize("GS,sym", [(128, False), (64, False), (256, True), (-1, False)])
 def test_fragment_other_bit_widths_forward(bits, M, GS, sym):
+    if bits == 3 and GS == 64:
+        GS = 512
     N, K = 328, 1024
     layer, x, q, s, z = _frag_layer(M, N, K, GS, sym, seed=3000 + 31 * M + bits + (GS % 83), bits=bits)
     y = layer(x.cuda())
@@ -344,7 +383,7 @@ def test_fragment_other_bit_widths_forward(bits, M, GS, sym):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("bits", [2, 8])
+@pytest.mark.parametrize("bits", [2, 3, 8])
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (4, 1000, 11008), (16, 2048, 4096), (1, 8192, 8192)])
 def test_fragment_other_bit_widths_split_k_shapes(bits, M, N, K):
     layer, x, q, s, z = _frag_layer(M, N, K, 128, False, seed=bits + M + N, bits=bits)

@@ -155,8 +155,6 @@ def test_llama7b_layer_shapes_against_oracle(N, K, M, layout_kind):
 @pytest.mark.parametrize("bits", [2, 3, 4, 8])
 @pytest.mark.parametrize("sym", [False, True])
 def test_bit_width_sweep_8192(bits, sym, layout_kind):
-    if layout_kind == "fragment" and bits == 3:
-        pytest.skip("3-bit layers have no fragment layout")
     N = K = 8192
     layer, x, q, s, z = _layer(N, K, bits, 128, sym, seed=0, M=1, layout_kind=layout_kind)
     y = layer(x.cuda())
