@@ -23,12 +23,14 @@
  * Inside a 32-bit word the 2/4-bit fields are pair-interleaved (even elements in the low
  * half-word, odd ones in the high half-word) so that one LOP3 yields an fp16x2 pair.
  *
- * Second packed layout ("fragment", QFB_LAYOUT_FRAGMENT, 2/4/8-bit layers with K % 128 == 0):
+ * Second packed layout ("fragment", QFB_LAYOUT_FRAGMENT, layers with K % 128 == 0):
  * the same bytes permuted so that the words of a lane are the A fragments one thread feeds to the
  * warp-level tensor-core instruction (rows g and g+8 of a 16-row block, four k each):
  *   qweight  [Npad/128][2 x 64 rows][K/16 steps of 128*bits bytes][32 lanes][words of 4 row blocks]
  *            (4-bit: one word per row block; 8-bit: two, in two 512-byte chunks per step;
- *             2-bit: one word per pair of row blocks)
+ *             2-bit: one word per pair of row blocks; 3-bit: three words for the four row blocks,
+ *             word j of all lanes a 128-byte plane of the step, five 3-bit fields and one spare
+ *             bit per half-word, the sixteenth field pair in the spare bits)
  *   scales / zeros  [Npad/128][K/group][128] in fragment row order
  * Batches of at most 16 rows run the mma.sync GEMV on it, larger ones the tcgen05 kernel, which
  * reads the same words; it is the layout of choice whenever the shape allows it.
@@ -84,7 +86,7 @@ typedef enum qfb_status {
 
 /* packed layouts */
 #define QFB_LAYOUT_TILE 0      /* tile-128 interleaved: every bit width, every batch size */
-#define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: 2/4/8-bit, K % 128 == 0, group 64 / n*128 / none */
+#define QFB_LAYOUT_FRAGMENT 1  /* tensor-core fragment order: K % 128 == 0, group 64 (not 3-bit) / n*128 / none */
 
 /* One packed layer.  Plain data; the caller owns the device buffers. */
 typedef struct qfb_layer {

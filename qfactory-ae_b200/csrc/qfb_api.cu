@@ -410,7 +410,7 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits,
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
-  // warps per k-way: 2 x 64 rows (m <= 8, 2- and 4-bit) or 4 x 32 rows; at most 256 threads
+  // warps per k-way: 2 x 64 rows (m <= 8; 2-, 3- and 4-bit) or 4 x 32 rows; at most 256 threads
   const int wpk = kTileRows / mma_rows_per_warp(bits, pl.nt);
   const int kways_max = 8 / wpk;
   const int cap_ws = mma_split_cap(tiles, batches);

@@ -2,7 +2,7 @@
 // tensor-core instruction (mma.sync m16n8k16), reading the "fragment" packed layout.
 //
 // Replaces the reference's kernel_gptq / kernel_gemv templates
-// (qfactory/include/gptq_gemv.h:14-154, qfactory/include/gemv.h:12-94) for 2-, 4- and 8-bit layers.
+// (qfactory/include/gptq_gemv.h:14-154, qfactory/include/gemv.h:12-94) for 2-, 3-, 4- and 8-bit layers.
 //
 // Why a third kernel.  On B200 the fp16x2 CUDA-core instructions and the integer/logic pipe both
 // issue at half rate, so a CUDA-core GEMV that spends LOP3 + HSUB2 + HFMA2 per code pair is
@@ -683,7 +683,7 @@ static int query_clusters(int block, size_t smem, int cluster) {
 }
 
 // one instantiation per (bit width, batch tiles, group mode); RB follows: 64-row warps for one
-// batch tile of 2- and 4-bit layers, 32-row warps otherwise
+// batch tile of 2-, 3- and 4-bit layers, 32-row warps otherwise (3-bit: that one build only)
 #define QFB_MMA_DISPATCH(FN, ...)                                                                     \
   do {                                                                                                \
     if (bits == 4 && nt == 1) return seg64 ? FN<4, 1, 4, true>(__VA_ARGS__) : FN<4, 1, 4, false>(__VA_ARGS__); \

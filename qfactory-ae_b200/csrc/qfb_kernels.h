@@ -34,7 +34,7 @@ size_t gemv_scratch_bytes(int m, int n, int k, int bits);
 int record_cuda_error(cudaError_t e);
 size_t scratch_clear_bytes(int n);
 
-// mma.sync split-K kernel over the fragment layout (2/4/8-bit, m <= 16 per launch)
+// mma.sync split-K kernel over the fragment layout (m <= 16 per launch, 8 for 3-bit layers)
 // Row-parallel linears of a tensor-parallel decoder: where the result is one rank's PARTIAL of a sum over
 // the ranks, the kernel that stores it also sends it to the peers, in the wire format of the peer-memory
 // reduction (qfb_comm.cu): every 4 data bytes followed by the call's epoch, stored into this rank's
@@ -102,7 +102,7 @@ struct TcParams {
   int steps_per_group;       // group_size / 16 MMA k-steps per quantisation group (K / 16 when group-less)
   int halfstages_per_group;  // group_size / 64
   uint32_t zconst;
-  int layout;                // QFB_LAYOUT_TILE, or QFB_LAYOUT_FRAGMENT (2-, 4- and 8-bit)
+  int layout;                // QFB_LAYOUT_TILE or QFB_LAYOUT_FRAGMENT
   // tail-split launches (one-dimensional grid; 0 = the uniform grid (tiles, batch tiles, splits)):
   int tail_split;            // K ranges each unit of the last, partly filled wave is cut into
   int full_units;            // (row tile, batch tile) units that run whole, one CTA each

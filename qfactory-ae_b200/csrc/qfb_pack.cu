@@ -83,7 +83,7 @@ __global__ void pack_scale_zero_kernel(const PackParams p) {
   }
 }
 
-// ---- fragment layouts (2/4/8-bit): one thread per packed word / per scale position ---------
+// ---- fragment layouts: one thread per packed word / per scale position --------------------
 // word j of lane (g, t) at k-step ks of the 64-row half wt of a tile; frag_word_of / frag_bit_of
 // (qfb_common.cuh) say which codes it holds
 __global__ void pack_weight_frag_kernel(const PackParams p) {

@@ -180,12 +180,13 @@ def unpack_zero(z: torch.Tensor, N: int) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------------------
-# Fragment layouts (2/4/8-bit, K % 128 == 0): the same codes permuted so that the words a lane
+# Fragment layouts (K % 128 == 0): the same codes permuted so that the words a lane
 # holds are the A fragments a thread feeds to mma.sync.m16n8k16 (include/qfactory_b200.h and
 # csrc/qfb_common.cuh).  Lane (g = lane // 4, t = lane % 4) of the 64-row half wt of a tile owns,
 # for each of its four row blocks rb, rows g and g + 8 (h = 0, 1) at k = 16*ks + 4*t + kk:
 #   word of the lane that holds code (rb, h, kk):  4-bit rb | 8-bit 2*rb + h | 2-bit rb // 2
 #   bit position inside that word:                 frag_bit_of below
+#   (3-bit: three words per lane, placed bit by bit: frag_code_bit below)
 #   qweight  [tiles][2][K/16] steps of 128*bits bytes: lane-major words (8-bit: two 512-byte chunks,
 #            row blocks 0,1 then 2,3)
 #   scales / zeros  [tiles][K/group][128], position wt*64 + g*8 + rb*2 + h <-> row wt*64 + rb*16 + h*8 + g

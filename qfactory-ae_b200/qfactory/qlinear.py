@@ -4,7 +4,7 @@
 Same names, arguments and error behaviour as the reference (reference:
 qfactory/qlinear.py:5-145).  Differences, all on purpose:
   * the packed tensors `.w/.s/.z` use the layouts of `convert.py`: `layout='tile'` (every bit
-    width), `layout='fragment'` (2-, 4- and 8-bit, K % 128 == 0: the tensor-core fragment order)
+    width), `layout='fragment'` (K % 128 == 0: the tensor-core fragment order)
     or `layout='auto'` (the default: fragment whenever the shape allows it); `state_dict()` carries
     the layout, and loading packed tensors of the other layout raises;
   * the batch size is a run-time property of `forward`, not a compile-time constant, and
