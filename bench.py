@@ -726,7 +726,7 @@ def main():
 
             sec = timed_decode()
             decode.update({"model": "llama2-70b-architecture random init, W4A16 g128 (output projection included)",
-                           "kernels_per_layer": 7 if world > 1 else 8,
+                           "kernels_per_layer": 7,
                            "tp": world, "batch": args.decode_batch, "prompt": 128, "steps": 256,
                            "tok_per_s": 256 * args.decode_batch / sec, "ms_per_step": sec / 256 * 1e3,
                            "collective": model.collective_name()})
