@@ -37,6 +37,23 @@ def test_pack_round_trip_property(bits, n, ku, seed):
     assert torch.equal(layout.unpack_weight(layout.pack_weight(q, bits), n, K, bits), q)
 
 
+@settings(max_examples=20, deadline=None)
+@given(bits=st.sampled_from([2, 3, 4, 8]), n=st.integers(1, 300), ku=st.integers(1, 4), seed=st.integers(0, 2**31 - 1))
+def test_fragment_pack_round_trip_property(bits, n, ku, seed):
+    """The fragment layout of every bit width (3-bit: placed bit by bit, one field pair in the spare
+    bits) holds the same codes: pack -> unpack is the identity, the padded rows are zero, and every
+    byte of the packed tensor is used (packing all-ones codes sets every bit of the real rows)."""
+    K = 128 * ku
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randint(0, 1 << bits, (K, n), generator=g, dtype=torch.int32)
+    w = layout.pack_weight_fragment(q, bits)
+    assert w.dtype == torch.int8 and w.shape == (layout.padded_rows(n), K * bits // 8)
+    assert torch.equal(layout.unpack_weight_fragment(w, n, K, bits), q)
+    ones = layout.pack_weight_fragment(torch.full((K, n), (1 << bits) - 1, dtype=torch.int32), bits)
+    set_bits = int(layout._bytes_to_words(ones.view(torch.uint8).reshape(-1, 4)).to(torch.int64).apply_(lambda v: bin(v & 0xFFFFFFFF).count("1")).sum())
+    assert set_bits == K * n * bits
+
+
 @pytest.mark.parametrize("bits", [2, 4, 8])
 def test_word_field_order_is_the_reference_permutation(bits):
     # one row, one 32-bit word: the word must equal the reference packer's word for the same codes
