@@ -146,6 +146,31 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bind_host_to_gpu(torch, local):
+    """With several ranks on one node every process pins its host staging buffers; a process that runs on
+    the other socket gets them from the far NUMA node and its PCIe copies cross the socket link.  Restrict
+    the process to the CPUs NVML reports as local to its GPU before anything is allocated (read-only NVML
+    queries; nothing of the GPU is changed).  Returns the number of CPUs kept, or 0 when nothing was done."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local).uuid)
+        try:
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        ncpu = os.cpu_count() or 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cpus = {i for i in range(ncpu) if (mask[i // 64] >> (i % 64)) & 1} & os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return 0
+
+
 def use_all_host_threads(torch):
     """The CPU arm uses every host core this process may run on (torchrun exports
     OMP_NUM_THREADS=1 to its workers, which would otherwise leave it on one thread)."""
@@ -242,6 +267,8 @@ def main():
     ap.add_argument("--steps-per-graph", type=int, default=10, help="steps captured in one CUDA graph (a decoder's graph "
                     "holds hundreds of layer launches; a single 12-launch step per graph would time the gap between graph "
                     "launches as much as the kernels)")
+    ap.add_argument("--bind-host", type=int, default=1, help="with more than one rank: keep each process on the CPUs "
+                    "local to its GPU (NUMA-local pinned staging buffers); 0: leave the affinity alone")
     ap.add_argument("--graph", type=int, default=1, help="0: issue the step's launches one by one instead of "
                     "replaying a CUDA graph (for per-launch profiling; not the benchmark configuration)")
     ap.add_argument("--layout", default="auto", choices=["auto", "tile", "fragment"],
@@ -264,6 +291,7 @@ def main():
     _native.lib()  # fail loudly if the native library is missing
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    host_cpus = bind_host_to_gpu(torch, local) if (world > 1 and args.bind_host) else 0
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -786,7 +814,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": bench_config(world),
             "protocol": {"cache": f"inputs larger than L2: {REPL} replicas of all weights ({REPL * sb / 1e6:.0f} MB) alternated between steps",
-                         "graph": bool(args.graph), "steps_per_graph": G, "pdl": bool(args.pdl), "launches_per_step": n_cases,
+                         "graph": bool(args.graph), "steps_per_graph": G, "pdl": bool(args.pdl), "host_cpus_bound": host_cpus, "launches_per_step": n_cases,
                          "timed": f"{len(pass_ms)} passes of {args.steps} steps, CUDA events, max over ranks per pass; value = median pass"},
             "spread": {"passes": len(pass_ms), "ms_per_step_min": srt[0] / args.steps, "ms_per_step_median": ms / args.steps,
                        "ms_per_step_max": srt[-1] / args.steps},
