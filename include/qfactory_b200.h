@@ -336,6 +336,22 @@ void* qfb_comm_region(const qfb_comm* comm, int slot, int source_rank);
 int qfb_comm_epoch(qfb_comm* comm, int row, void* stream, unsigned* epoch_out);
 int qfb_allreduce_add_rmsnorm(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,
                               float eps, void* stream);
+/*
+ * A linear with the residual add and the RMS norm in front of it fused in (reference: separate kernels
+ * around the linears, third_party/vllm-bitblas/vllm/model_executor/models/llama.py:260-285):
+ *   s = x + residual (one fp16 addition per element; residual may be NULL), written to x_out (may be NULL;
+ *   never x or residual themselves: other blocks of the launch still read them);
+ *   y = (rmsnorm(s) * norm_weight) . dequant(W)^T.
+ * The blocks of the GEMV add, weight and square their K slices while staging them; 1 / rms, a scalar per
+ * row, is applied to the result, so the activations are rounded to fp16 once (s * w) instead of twice: y
+ * differs from the three-call form by that rounding (within 2e-3 of max|y| in the tests), x_out is
+ * bit-identical.  Up to 16 rows of a 4-bit fragment-layout layer with groups of 128 or more;
+ * otherwise QFB_ERR_UNSUPPORTED.
+ */
+int qfb_linear_addnorm_forward(const qfb_layer* layer, const void* x, const void* residual, void* x_out,
+                               const void* norm_weight, float eps, int m, void* y, void* workspace,
+                               size_t workspace_bytes, unsigned flags, void* stream);
+
 /* The same reduction when the kernel that wrote the partial has already sent it to the peers
  * (qfb_linear_forward_reduce below): the launch only collects, sums, adds and normalises. */
 int qfb_allreduce_add_rmsnorm_pushed(qfb_comm* comm, int slot, void* x, const void* w, void* out, int rows, int d,

@@ -406,7 +406,7 @@ static size_t mma_recv_bytes(int rows, int split) {
 // part that grows with rows x splits, reducing them through the workspace a fixed fence /
 // atomic / re-read chain.  How many clusters fit at once is asked from the occupancy API (clusters must sit
 // inside one GPC, so a grid that fits by CTA count may still need a second wave).
-static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits, bool act) {
+static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits, bool act, bool no_ws) {
   MmaPlan pl;
   pl.nt = rows <= 8 ? 1 : 2;
   const int batches = k / 128;
@@ -429,7 +429,7 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits,
       const int per_kway = (bpc + kw - 1) / kw;
       const double base = 0.05 * s + 0.01 * (kways_max - kw);
       // through the workspace: the registers (16 or 20 warps per SM) and the shared memory bound the residency
-      if (s <= cap_ws && !(g_mma_cluster == 2 && s > 1 && s <= 8)) {
+      if (s <= cap_ws && !(g_mma_cluster == 2 && s > 1 && s <= 8) && (!no_ws || s == 1)) {
         const int resident = std::max(1, std::min(mma_warps_per_sm(block) / (wpk * kw), (int)((200 * 1024) / (smem + 1024))));
         const int waves = (tiles * s + num_sms() * resident - 1) / (num_sms() * resident);
         const double cost = (double)waves * (per_kway + 1.5) + base + (s > 1 ? 3.0 + 0.02 * rows * s : 0.0);
@@ -460,32 +460,45 @@ static MmaPlan plan_mma_search(int tiles, int k, int rows, bool seg64, int bits,
 // The search above asks the occupancy API and walks a few hundred candidates: its result is kept
 // per (device, shape, rows, group mode, bit width, tuning overrides), so a repeated call costs a
 // map lookup on the host.
-static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits, bool act) {
+// `no_ws`: only plans that reduce the K splits inside a cluster, or do not split (the fused norm needs them)
+static MmaPlan plan_mma(int tiles, int k, int rows, bool seg64, int bits, bool act, bool no_ws = false) {
   static std::mutex mu;
   static std::map<std::tuple<int, int, int, int, int, int, int, int, int>, MmaPlan> cache;
   int dev = 0;
   (void)cudaGetDevice(&dev);
-  const auto key = std::make_tuple(dev, tiles, k, rows, (int)seg64 + 2 * (int)act, bits, g_tune_split, g_tune_kways, g_mma_cluster);
+  const auto key = std::make_tuple(dev, tiles, k, rows, (int)seg64 + 2 * (int)act + 4 * (int)no_ws, bits, g_tune_split, g_tune_kways,
+                                   g_mma_cluster);
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
   }
-  const MmaPlan pl = plan_mma_search(tiles, k, rows, seg64, bits, act);
+  const MmaPlan pl = plan_mma_search(tiles, k, rows, seg64, bits, act, no_ws);
   std::lock_guard<std::mutex> lock(mu);
   cache[key] = pl;
   return pl;
 }
 
 // `act`: x is a fused gate/up tensor [m, 2k] and the layer's input is silu(gate) * up
+// residual add + RMS norm fused in front of the linear (MmaParams::norm_*)
+struct NormArgs {
+  const __half* x;
+  const __half* r;
+  __half* out;
+  const __half* w;
+  float eps;
+};
+
 static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
-                   unsigned flags, cudaStream_t st, bool act = false, const PushTarget* push = nullptr) {
+                   unsigned flags, cudaStream_t st, bool act = false, const PushTarget* push = nullptr,
+                   const NormArgs* norm = nullptr) {
   const int x_stride = act ? 2 * v.k : v.k;
   const int pass_rows = mma_pass_rows(v.bits);
   for (int m0 = 0; m0 < m; m0 += pass_rows) {
     const int rows = std::min(pass_rows, m - m0);
-    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits, act);
+    const MmaPlan pl = plan_mma(v.tiles, v.k, rows, v.group_size == 64, v.bits, act, norm != nullptr);
     if (pl.smem > 200 * 1024) return QFB_ERR_TOO_LARGE;
+    if (norm && pl.split > 1 && !pl.cluster) return QFB_ERR_UNSUPPORTED;   // (no cluster plan fits this device)
     MmaParams p = {};
     p.qw = v.qw;
     p.qs = v.qs;
@@ -506,6 +519,13 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
     p.act_offset = (int)mma_stage_bytes(rows, pl.nt, p.batches_per_cta);
     p.stall_test = (flags & QFB_FLAG_TEST_STALLED_WAIT) ? 1 : 0;
     if (push) p.push = *push;   // (callers pass it for single-pass launches only)
+    if (norm) {
+      p.norm_x = norm->x;
+      p.norm_r = norm->r;
+      p.norm_out = norm->out;
+      p.norm_w = norm->w;
+      p.norm_eps = norm->eps;
+    }
     p.batches_div = p.batches / pl.split;
     p.batches_mod = p.batches % pl.split;
     p.zconst = v.zconst;
@@ -753,6 +773,27 @@ static int forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm
   if (st != QFB_OK) return st;
   return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(own), workspace, workspace_bytes, flags,
                  static_cast<cudaStream_t>(stream), act, &t);
+}
+
+int qfb_linear_addnorm_forward(const qfb_layer* layer, const void* x, const void* residual, void* x_out,
+                               const void* norm_weight, float eps, int m, void* y, void* workspace,
+                               size_t workspace_bytes, unsigned flags, void* stream) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (m < 0) return QFB_ERR_BAD_SHAPE;
+  if (m == 0) return QFB_OK;
+  if (!x || !norm_weight || !y) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(residual) || !aligned16(x_out) || !aligned16(norm_weight) || !aligned16(workspace) ||
+      (reinterpret_cast<uintptr_t>(y) & 1u))
+    return QFB_ERR_MISALIGNED;
+  if (x_out && (x_out == x || x_out == residual)) return QFB_ERR_BAD_SHAPE;   // other CTAs still read the inputs
+  // served by one launch of the mma.sync GEMV's norm build (4-bit, groups of 128 and more)
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows || v.bits != 4 || v.group_size == 64) return QFB_ERR_UNSUPPORTED;
+  const NormArgs na = {static_cast<const __half*>(x), static_cast<const __half*>(residual), static_cast<__half*>(x_out),
+                       static_cast<const __half*>(norm_weight), eps};
+  return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                 static_cast<cudaStream_t>(stream), false, nullptr, &na);
 }
 
 int qfb_linear_forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, void* workspace,

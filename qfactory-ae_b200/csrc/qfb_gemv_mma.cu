@@ -165,7 +165,12 @@ template <int RB> struct ScaleZero {
 // LEAN  = a build without the fused-activation staging and without the reduction through the workspace, for
 //         the launches that need neither (measured: 1-3 % faster; the compiler schedules the common path
 //         better when the rare ones are not in the same function)
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN>
+// NORM  = the activations are rmsnorm(x + r) * w of a residual stream (MmaParams::norm_*), made while they are
+//         staged: every CTA adds and weights its K slice and sums its squares; the sums of a tile's K splits
+//         meet where the partial results meet (in the cluster, or in the one CTA of an unsplit tile), and
+//         1 / rms, a scalar per batch row, is applied to the result instead of to every activation.  A
+//         build of its own; launched with in-cluster reduction or no split only.
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM>
 __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
@@ -242,11 +247,55 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   __shared__ __align__(8) uint64_t xbar;
   __shared__ int xabort;
   __shared__ unsigned push_epoch[16];   // epoch of the reduction this launch feeds, per batch row
+  __shared__ float nss_warp[8][16];     // NORM: per-warp sums of squares of the slice, per batch row
+  __shared__ float nss_recv[8][16];     // NORM: the sums of the K splits of the tile (written by every CTA of the cluster)
+  __shared__ float nrstd[16];           // NORM: 1 / rms per batch row
   // With p.act == 1 the activations are silu(gate) * up of a fused gate/up tensor [m, 2k]: the gate
   // and the up slices arrive by one bulk copy each and are combined in shared memory, with the
   // arithmetic of the stand-alone kernel (silu in fp32 rounded to fp16, then one fp16 product).
   __half* u_s = reinterpret_cast<__half*>(reinterpret_cast<char*>(smem) + p.act_offset);
-  if (warp == 0) {
+  if (NORM) {
+    // x + r (one fp16 addition, as the stand-alone kernel), written back by the CTAs of tile 0 (whose K splits
+    // cover the row once), times the norm weight (one fp16 product) into the slice; squares summed in fp32 per
+    // thread and batch row, then per warp, in a fixed order
+    const int vec_row = ncta * 16;  // 16-byte vectors per row of the slice
+    float ss[8 * NT];
+#pragma unroll
+    for (int r = 0; r < 8 * NT; ++r) ss[r] = 0.f;
+    for (int j = tid; j < vec_row; j += blockDim.x) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + (size_t)bb * 128 + (size_t)j * 8);
+      const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int r = 0; r < 8 * NT; ++r) {
+        if (r < p.m) {
+          const size_t go = (size_t)r * p.k + (size_t)bb * 128 + (size_t)j * 8;
+          uint4 xv = __ldcg(reinterpret_cast<const uint4*>(p.norm_x + go));
+          uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+          if (p.norm_r) {
+            const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.norm_r + go));
+            const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xu[q] = as_u32(__hadd2(as_h2(xu[q]), as_h2(ru[q])));
+          }
+          if (p.norm_out && tile == 0) *reinterpret_cast<uint4*>(p.norm_out + go) = make_uint4(xu[0], xu[1], xu[2], xu[3]);
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(as_h2(xu[q]));
+            ss[r] += f.x * f.x + f.y * f.y;
+            o[q] = as_u32(__hmul2(as_h2(xu[q]), as_h2(wu[q])));
+          }
+          *reinterpret_cast<uint4*>(x_s + (size_t)r * xstride + (size_t)j * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8 * NT; ++r) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
+      if (lane == 0) nss_warp[warp][r] = ss[r];
+    }
+  } else if (warp == 0) {
     const uint32_t bar = ptx::smem_u32(&xbar);
     const uint32_t row_bytes = (uint32_t)ncta * 256u;
     if (lane == 0) {
@@ -455,9 +504,14 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
                      "r"(hi), "r"(ep)
                      : "memory");
   };
-  auto store_quad = [&](int q, const float4& v) {
+  auto store_quad = [&](int q, const float4& v0) {
     const int mm = q >> 5, n = tile * kTileRows + (q & 31) * 4;
     __half* dst = p.y + (size_t)mm * p.n + n;
+    float4 v = v0;
+    if (NORM) {  // the scalar of the norm, applied to the result
+      const float rs = nrstd[mm];
+      v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
+    }
     if (n + 3 < p.n && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
       const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
       *reinterpret_cast<uint2*>(dst) = make_uint2(as_u32(lo), as_u32(hi));
@@ -469,7 +523,17 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
         if (n + i < p.n) dst[i] = __float2half_rn(e[i]);
     }
   };
+  // NORM: this CTA's sum of squares of a batch row (its warps' sums in a fixed order)
+  auto norm_cta_sum = [&](int r) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += nss_warp[w][r];
+    return t;
+  };
   if (S == 1) {
+    if (NORM) {
+      if (tid < p.m) nrstd[tid] = rsqrtf(norm_cta_sum(tid) / (float)p.k + p.norm_eps);
+      __syncthreads();
+    }
     for (int q = tid; q < nq; q += blockDim.x) store_quad(q, kway_sum4(q));
     return;
   }
@@ -484,12 +548,25 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     const uint32_t recv_addr = static_cast<uint32_t>(__cvta_generic_to_shared(recv));
     const int qper = p.quads_per_owner;
     cluster_wait();  // pairs with the arrive at kernel start: every CTA of the cluster runs
+    if (NORM && tid < p.m) {  // every CTA of the tile learns every split's sum of squares
+      const float t = norm_cta_sum(tid);
+      const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(&nss_recv[split][tid]));
+      for (int c = 0; c < S; ++c) st_cluster_f32(a, c, t);
+    }
     for (int q = tid; q < nq; q += blockDim.x) {
       const float4 v = kway_sum4(q);
       const int owner = (int)__umulhi((unsigned)q, p.qper_magic);  // q / qper (q < 2^9, qper <= 2^9)
       st_cluster_v4(recv_addr + (split * qper + (q - owner * qper)) * 16, owner, v);
     }
     cluster_barrier();
+    if (NORM) {
+      if (tid < p.m) {
+        float t = 0.f;
+        for (int u = 0; u < S; ++u) t += nss_recv[u][tid];   // split order: the same bits in every CTA
+        nrstd[tid] = rsqrtf(t / (float)p.k + p.norm_eps);
+      }
+      __syncthreads();
+    }
     for (int j = tid; j < qper; j += blockDim.x) {
       const int q = split * qper + j;
       if (q < nq) {
@@ -605,13 +682,13 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // either way).  Tighter budgets that would leave room for the next launch's CTAs to become
 // resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
 // k-step loop and were 5-70 % slower on every Llama-7B layer shape.
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM>(p);
 }
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false>
 __global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM>(p);
 }
 
 template <int BITS, int NT, int RB, bool SEG64>
@@ -620,6 +697,15 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
   if (!p.act && (p.cluster || grid.x == 1) && !p.push.world)
     kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true>
                                    : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true>;
+  if (p.norm_w) {
+    // the build with the fused residual add + RMS norm: the same layers, in-cluster reduction or no split
+    if (p.push.world || p.act || !(p.cluster || grid.x == 1)) return cudaErrorInvalidValue;
+    if constexpr (BITS == 4 && !SEG64)
+      kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, NT, RB, false, false, true, true>
+                                     : gemv_mma_kernel<4, NT, RB, false, false, true, true>;
+    else
+      return cudaErrorNotSupported;
+  }
   if (p.push.world) {
     // the sending build: 4-bit layers with groups of 128 and more (what the decoder's row-parallel layers are)
     if constexpr (BITS == 4 && !SEG64)

@@ -72,6 +72,14 @@ struct MmaParams {
   int stall_test;        // 1 (QFB_FLAG_TEST_STALLED_WAIT): the activation barrier expects 16 bytes that never
                          // come and gives up after ~100 us, so that the bounded-wait path can be tested
   PushTarget push;       // row-parallel layer of a tensor-parallel decoder: y is also sent to the peers
+  // fused residual add + RMS norm in front of the linear (norm_w != null; x is then unused): the activations
+  // are rmsnorm(norm_x + norm_r) * norm_w.  The sum norm_x + norm_r is also written to norm_out (may be
+  // null; never the same buffer as norm_x or norm_r: other CTAs still read those).
+  const __half* norm_x;  // [m, k] residual stream
+  const __half* norm_r;  // [m, k] addend, or null
+  __half* norm_out;      // [m, k] updated residual stream, or null
+  const __half* norm_w;  // [k] norm weight
+  float norm_eps;
 };
 // CTAs of the mma.sync GEMV of up to this many threads run the 96-register build (five per SM)
 constexpr int kMmaSmallBlock = 128;

@@ -129,6 +129,31 @@ class _PackedLinear(torch.nn.Module):
             _native.check(st, "qfb_linear_forward")
         return out if lead is None else out.view(*lead, N)
 
+    def forward_addnorm(self, x, residual, norm_weight, eps=1e-5, x_out=None, out=None):
+        """y = (rmsnorm(x + residual) * norm_weight) @ dequant(W)^T in ONE kernel (reference: the add, the norm
+        and the linear are separate kernels, third_party/vllm-bitblas/vllm/model_executor/models/llama.py:260-285).
+        `x` [rows, in_features] fp16, `residual` the same shape or None; the sum is written to `x_out` (a
+        buffer other than `x` and `residual`, or None).  Returns y, or None where the fused kernel does not
+        serve the layer or the batch (the caller then runs the three steps)."""
+        if self._desc is None:
+            self._prepare()
+        rows = x.shape[0]
+        if not (self.packed_layout == layout.LAYOUT_FRAGMENT and self.n_bits == 4 and self.group_size != 64 and 0 < rows <= 16
+                and x.dim() == 2 and x.is_contiguous()):
+            return None
+        if out is None:
+            out = torch.empty(rows, self.out_features, dtype=torch.float16, device=x.device)
+        with torch.cuda.device(x.device):
+            st = self._lib.qfb_linear_addnorm_forward(
+                self._desc_ref, x.data_ptr(), None if residual is None else residual.data_ptr(),
+                None if x_out is None else x_out.data_ptr(), norm_weight.data_ptr(), float(eps), rows, out.data_ptr(),
+                self._ws_ptr, self._ws_bytes, self.flags, torch.cuda.current_stream(x.device).cuda_stream)
+        if st == 3:    # QFB_ERR_UNSUPPORTED
+            return None
+        if st != 0:
+            _native.check(st, "qfb_linear_addnorm_forward")
+        return out
+
     def silu_mul_supported(self, rows: int) -> bool:
         """True when `forward_silu_mul` runs as ONE kernel for `rows` activation rows."""
         return self.packed_layout == layout.LAYOUT_FRAGMENT and 0 < rows <= (8 if self.n_bits == 3 else 16)
