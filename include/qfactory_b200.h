@@ -370,6 +370,31 @@ int qfb_linear_forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_
                               void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
 int qfb_linear_silu_mul_forward_reduce(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
                                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+/*
+ * Step numbering: the exchange without a kernel that advances epochs, so that the RECEIVING side can be the
+ * GEMV that consumes the sum.  qfb_comm_step_begin (one tiny launch at the start of a decode step; every
+ * rank) advances a counter in the local buffer that nothing changes during the step; reduction `idx`
+ * (0..255, the same on every rank, slots alternating with it) then uses the epoch 2^31 | step << 8 | idx.
+ *   qfb_linear_forward_reduce_step / qfb_linear_silu_mul_forward_reduce_step: the sending GEMV;
+ *   qfb_linear_collect_addnorm_forward: qfb_linear_addnorm_forward whose addend is the sum over the ranks
+ *     of slot `slot` (own partial + the peers' words, polled while the activations are staged; bounded
+ *     waits, qfb_comm_read_status): y = (rmsnorm(x + sum) * norm_weight) . dequant(W)^T, x + sum -> x_out;
+ *   qfb_allreduce_add_rmsnorm_step: the collecting reduction kernel for the places where no GEMV follows.
+ * Do not mix the two numberings on one slot inside a step.  qfb_linear_addnorm_supported: 1 when the
+ * fused-norm GEMV serves the layer for m rows (4-bit fragment layout, a plan without workspace reduction).
+ */
+int qfb_comm_step_begin(qfb_comm* comm, void* stream);
+int qfb_linear_forward_reduce_step(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, int idx,
+                                   void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+int qfb_linear_silu_mul_forward_reduce_step(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
+                                            int idx, void* workspace, size_t workspace_bytes, unsigned flags,
+                                            void* stream);
+int qfb_linear_collect_addnorm_forward(const qfb_layer* layer, qfb_comm* comm, int slot, int idx, const void* x,
+                                       void* x_out, const void* norm_weight, float eps, int m, void* y,
+                                       void* workspace, size_t workspace_bytes, unsigned flags, void* stream);
+int qfb_allreduce_add_rmsnorm_step(qfb_comm* comm, int slot, int idx, void* x, const void* w, void* out, int rows,
+                                   int d, float eps, void* stream);
+int qfb_linear_addnorm_supported(const qfb_layer* layer, int m);
 int qfb_comm_read_status(qfb_comm* comm, void* stream, unsigned* status_out);
 int qfb_comm_last_cuda_error(void);
 

@@ -487,6 +487,7 @@ struct NormArgs {
   __half* out;
   const __half* w;
   float eps;
+  const CollectSource* collect;   // non-null: the addend is collected from the peers (r unused)
 };
 
 static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* workspace, size_t ws_bytes,
@@ -525,6 +526,7 @@ static int run_mma(const LayerView& v, const __half* x, int m, __half* y, void* 
       p.norm_out = norm->out;
       p.norm_w = norm->w;
       p.norm_eps = norm->eps;
+      if (norm->collect) p.collect = *norm->collect;
     }
     p.batches_div = p.batches / pl.split;
     p.batches_mod = p.batches % pl.split;
@@ -756,7 +758,7 @@ int qfb_linear_silu_mul_forward(const qfb_layer* layer, const void* gate_up, int
 
 // The row-parallel linears of a tensor-parallel decoder: the partial goes into the communicator's data slot
 // AND, in the wire format of the reduction, into this rank's receive region of every peer.
-static int forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, void* workspace,
+static int forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, int idx, void* workspace,
                           size_t workspace_bytes, unsigned flags, void* stream, bool act) {
   LayerView v;
   int st = make_view(layer, &v);
@@ -771,6 +773,8 @@ static int forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm
   void* own = nullptr;
   st = comm_push_target(comm, slot, m, v.n, &t, &own);
   if (st != QFB_OK) return st;
+  if (idx > 255) return QFB_ERR_BAD_SHAPE;
+  t.idx = idx;   // (< 0: per-row epochs, advanced by the reduction kernel)
   return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(own), workspace, workspace_bytes, flags,
                  static_cast<cudaStream_t>(stream), act, &t);
 }
@@ -791,19 +795,63 @@ int qfb_linear_addnorm_forward(const qfb_layer* layer, const void* x, const void
   // served by one launch of the mma.sync GEMV's norm build (4-bit, groups of 128 and more)
   if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows || v.bits != 4 || v.group_size == 64) return QFB_ERR_UNSUPPORTED;
   const NormArgs na = {static_cast<const __half*>(x), static_cast<const __half*>(residual), static_cast<__half*>(x_out),
-                       static_cast<const __half*>(norm_weight), eps};
+                       static_cast<const __half*>(norm_weight), eps, nullptr};
+  return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
+                 static_cast<cudaStream_t>(stream), false, nullptr, &na);
+}
+
+int qfb_linear_addnorm_supported(const qfb_layer* layer, int m) {
+  LayerView v;
+  if (make_view(layer, &v) != QFB_OK || m <= 0) return 0;
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows || v.bits != 4 || v.group_size == 64) return 0;
+  const MmaPlan pl = plan_mma(v.tiles, v.k, m, false, v.bits, false, true);
+  return (pl.smem <= 200 * 1024 && (pl.split == 1 || pl.cluster)) ? 1 : 0;
+}
+
+int qfb_linear_collect_addnorm_forward(const qfb_layer* layer, qfb_comm* comm, int slot, int idx, const void* x,
+                                       void* x_out, const void* norm_weight, float eps, int m, void* y,
+                                       void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+  LayerView v;
+  int st = make_view(layer, &v);
+  if (st != QFB_OK) return st;
+  if (m < 0) return QFB_ERR_BAD_SHAPE;
+  if (m == 0) return QFB_OK;
+  if (!comm || !x || !norm_weight || !y) return QFB_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(x_out) || !aligned16(norm_weight) || !aligned16(workspace) ||
+      (reinterpret_cast<uintptr_t>(y) & 1u))
+    return QFB_ERR_MISALIGNED;
+  if (x_out && x_out == x) return QFB_ERR_BAD_SHAPE;
+  if (v.layout != QFB_LAYOUT_FRAGMENT || m > kMaxMmaRows || v.bits != 4 || v.group_size == 64) return QFB_ERR_UNSUPPORTED;
+  CollectSource cs;
+  st = comm_collect_source(comm, slot, idx, m, v.k, &cs);
+  if (st != QFB_OK) return st;
+  const NormArgs na = {static_cast<const __half*>(x), nullptr, static_cast<__half*>(x_out),
+                       static_cast<const __half*>(norm_weight), eps, &cs};
   return run_mma(v, static_cast<const __half*>(x), m, static_cast<__half*>(y), workspace, workspace_bytes, flags,
                  static_cast<cudaStream_t>(stream), false, nullptr, &na);
 }
 
 int qfb_linear_forward_reduce(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, void* workspace,
                               size_t workspace_bytes, unsigned flags, void* stream) {
-  return forward_reduce(layer, x, m, comm, slot, workspace, workspace_bytes, flags, stream, false);
+  return forward_reduce(layer, x, m, comm, slot, -1, workspace, workspace_bytes, flags, stream, false);
+}
+
+int qfb_linear_forward_reduce_step(const qfb_layer* layer, const void* x, int m, qfb_comm* comm, int slot, int idx,
+                                   void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
+  if (idx < 0) return QFB_ERR_BAD_SHAPE;
+  return forward_reduce(layer, x, m, comm, slot, idx, workspace, workspace_bytes, flags, stream, false);
+}
+
+int qfb_linear_silu_mul_forward_reduce_step(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
+                                            int idx, void* workspace, size_t workspace_bytes, unsigned flags,
+                                            void* stream) {
+  if (idx < 0) return QFB_ERR_BAD_SHAPE;
+  return forward_reduce(layer, gate_up, m, comm, slot, idx, workspace, workspace_bytes, flags, stream, true);
 }
 
 int qfb_linear_silu_mul_forward_reduce(const qfb_layer* layer, const void* gate_up, int m, qfb_comm* comm, int slot,
                                        void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
-  return forward_reduce(layer, gate_up, m, comm, slot, workspace, workspace_bytes, flags, stream, true);
+  return forward_reduce(layer, gate_up, m, comm, slot, -1, workspace, workspace_bytes, flags, stream, true);
 }
 
 int qfb_linear_forward_host(const qfb_layer* layer, const void* x_host, int m, void* y_host, void* x_staging,

@@ -46,7 +46,8 @@ namespace qfb {
 
 constexpr int kCommMaxWorld = 8;
 constexpr int kCommMaxRows = 64;       // batch rows one reduction handles (one CTA each)
-constexpr size_t kCommHeaderBytes = 1024;                                         // status word + epochs[kCommMaxRows]
+constexpr size_t kCommHeaderBytes = 1024;                                         // status word + epochs[kCommMaxRows] + step counter
+constexpr int kCommStepWord = 1 + kCommMaxRows;                                   // header word of the step counter
 constexpr size_t kCommDataOffset = kCommHeaderBytes;
 // a data slot: [own partial, plain fp16: slot_bytes][receive regions, one per source rank: 2 * slot_bytes each]
 
@@ -63,6 +64,7 @@ struct CommArgs {
   float eps;
   unsigned long long timeout_ns;
   int pushed;                  // 1: the kernel that wrote the local partial has already sent it to the peers
+  int idx;                     // >= 0: step numbering (the epoch is 2^31 | step << 8 | idx, nothing is advanced here)
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -107,7 +109,8 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const CommAr
   unsigned* epochs = status + 1;
   __shared__ float red[32];
   __shared__ float css[8];   // sums of squares of the C CTAs of the row (pushed by every CTA into every CTA)
-  const unsigned epoch = epochs[row] + 1u;   // (advanced by one thread once every CTA of the row has read it)
+  // (per-row numbering: advanced by one thread once every CTA of the row has read it)
+  const unsigned epoch = a.idx >= 0 ? (0x80000000u | (status[kCommStepWord] << 8) | (unsigned)a.idx) : epochs[row] + 1u;
 
   // ---- push this rank's partial of the row, epoch attached, into every peer's receive region ------
   const int nv = a.d >> 3;
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(256) allreduce_add_rmsnorm_kernel(const CommAr
   }
   if (C > 1) comm_cluster_barrier();   // every CTA of the row has read the epoch and pushed its sum
   else __syncthreads();
-  if (crank == 0 && tid == 0) epochs[row] = epoch;
+  if (crank == 0 && tid == 0 && a.idx < 0) epochs[row] = epoch;
   if (!a.w || !active) return;
   float tot = 0.f;
 #pragma unroll
@@ -271,6 +274,23 @@ struct qfb_comm {
 static size_t comm_slot_span(size_t slot_bytes) { return slot_bytes * (1 + 2 * (size_t)kCommMaxWorld); }
 
 namespace qfb {
+int comm_collect_source(const qfb_comm* c, int slot, int idx, int rows, int d, CollectSource* s) {
+  if (!c || !s) return QFB_ERR_NULL_POINTER;
+  if (slot < 0 || slot > 1 || idx < 0 || idx > 255 || rows <= 0 || d <= 0 || d % 128 != 0) return QFB_ERR_BAD_SHAPE;
+  if (rows > kCommMaxRows || (size_t)rows * d * 2 > c->slot_bytes) return QFB_ERR_TOO_LARGE;
+  const size_t slot_offset = kCommDataOffset + (size_t)slot * comm_slot_span(c->slot_bytes);
+  s->local = c->base[c->rank];
+  s->own_offset = slot_offset;
+  s->recv_offset = slot_offset + c->slot_bytes;
+  s->region_bytes = 2 * c->slot_bytes;
+  s->world = c->world;
+  s->rank = c->rank;
+  s->step = reinterpret_cast<const unsigned*>(c->base[c->rank]) + kCommStepWord;
+  s->idx = (unsigned)idx;
+  s->timeout_ns = c->timeout_ns;
+  s->status = reinterpret_cast<unsigned*>(c->base[c->rank]);
+  return QFB_OK;
+}
 int comm_push_target(const qfb_comm* c, int slot, int rows, int d, PushTarget* t, void** own_slot) {
   if (!c || !t || !own_slot) return QFB_ERR_NULL_POINTER;
   if (slot < 0 || slot > 1 || rows <= 0 || d <= 0 || d % 128 != 0) return QFB_ERR_BAD_SHAPE;
@@ -281,6 +301,8 @@ int comm_push_target(const qfb_comm* c, int slot, int rows, int d, PushTarget* t
   t->rank = c->rank;
   t->recv_offset = slot_offset + c->slot_bytes + (size_t)c->rank * 2 * c->slot_bytes;
   t->epochs = reinterpret_cast<const unsigned*>(c->base[c->rank]) + 1;
+  t->step = reinterpret_cast<const unsigned*>(c->base[c->rank]) + kCommStepWord;
+  t->idx = -1;
   *own_slot = c->base[c->rank] + slot_offset;
   return QFB_OK;
 }
@@ -372,20 +394,34 @@ void* qfb_comm_region(const qfb_comm* c, int slot, int source_rank) {  // receiv
 }
 
 static int allreduce_impl(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
-                          int pushed, void* stream);
+                          int pushed, int idx, void* stream);
 
 int qfb_allreduce_add_rmsnorm(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
                               void* stream) {
-  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 0, stream);
+  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 0, -1, stream);
 }
 
 int qfb_allreduce_add_rmsnorm_pushed(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d,
                                      float eps, void* stream) {
-  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 1, stream);
+  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 1, -1, stream);
+}
+
+int qfb_allreduce_add_rmsnorm_step(qfb_comm* c, int slot, int idx, void* x, const void* w, void* out, int rows, int d,
+                                   float eps, void* stream) {
+  if (idx < 0 || idx > 255) return QFB_ERR_BAD_SHAPE;
+  return allreduce_impl(c, slot, x, w, out, rows, d, eps, 1, idx, stream);
+}
+
+static __global__ void comm_step_kernel(unsigned* header) { header[kCommStepWord] += 1u; }
+
+int qfb_comm_step_begin(qfb_comm* c, void* stream) {
+  if (!c) return QFB_ERR_NULL_POINTER;
+  comm_step_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<unsigned*>(c->base[c->rank]));
+  return comm_check(cudaGetLastError());
 }
 
 static int allreduce_impl(qfb_comm* c, int slot, void* x, const void* w, void* out, int rows, int d, float eps,
-                          int pushed, void* stream) {
+                          int pushed, int idx, void* stream) {
   if (!c) return QFB_ERR_NULL_POINTER;
   if (slot < 0 || slot > 1 || rows < 0 || d <= 0 || d % 8 != 0) return QFB_ERR_BAD_SHAPE;
   if (rows == 0) return QFB_OK;
@@ -408,6 +444,7 @@ static int allreduce_impl(qfb_comm* c, int slot, void* x, const void* w, void* o
   a.eps = eps;
   a.timeout_ns = c->timeout_ns;
   a.pushed = pushed;
+  a.idx = idx;
   const int nv = d / 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (c->world) {

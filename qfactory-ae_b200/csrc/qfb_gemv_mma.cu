@@ -262,6 +262,8 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     float ss[8 * NT];
 #pragma unroll
     for (int r = 0; r < 8 * NT; ++r) ss[r] = 0.f;
+    const bool collect = p.collect.local != nullptr;
+    const unsigned cep = collect ? (0x80000000u | (__ldcg(p.collect.step) << 8) | p.collect.idx) : 0u;
     for (int j = tid; j < vec_row; j += blockDim.x) {
       const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + (size_t)bb * 128 + (size_t)j * 8);
       const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -271,7 +273,48 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
           const size_t go = (size_t)r * p.k + (size_t)bb * 128 + (size_t)j * 8;
           uint4 xv = __ldcg(reinterpret_cast<const uint4*>(p.norm_x + go));
           uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
-          if (p.norm_r) {
+          if (collect) {
+            // the addend: the partials of all ranks summed in rank order in fp32 and rounded to fp16 (what the
+            // reduction kernel computes, bit for bit); a peer's words are polled until they carry the epoch
+            float acc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < 8; ++rk) {
+              if (rk < p.collect.world) {
+                uint4 p4;
+                if (rk == p.collect.rank) {
+                  p4 = __ldcg(reinterpret_cast<const uint4*>(p.collect.local + p.collect.own_offset + go * 2));
+                } else {
+                  const char* src = p.collect.local + p.collect.recv_offset + (size_t)rk * p.collect.region_bytes + go * 4;
+                  uint4 lo, hi;
+                  unsigned long long t0 = 0;
+                  while (true) {
+                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w) : "l"(src) : "memory");
+                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(src + 16) : "memory");
+                    if (lo.y == cep && lo.w == cep && hi.y == cep && hi.w == cep) break;
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > p.collect.timeout_ns) {   // bounded: record it and go on with what is there
+                      atomicExch(p.collect.status, 1u);
+                      break;
+                    }
+                  }
+                  p4 = make_uint4(lo.x, lo.z, hi.x, hi.z);
+                }
+                const uint32_t pu[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 f = __half22float2(as_h2(pu[q]));
+                  acc[2 * q] += f.x;
+                  acc[2 * q + 1] += f.y;
+                }
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) xu[q] = as_u32(__hadd2(as_h2(xu[q]), __floats2half2_rn(acc[2 * q], acc[2 * q + 1])));
+          } else if (p.norm_r) {
             const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(p.norm_r + go));
             const uint32_t ru[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
@@ -306,7 +349,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
     }
     __syncwarp();
     // (the reduction kernel that finished the previous epoch of these rows precedes this launch)
-    if (PUSH && lane < p.m) push_epoch[lane] = __ldcg(p.push.epochs + lane) + 1u;
+    if (PUSH && lane < p.m)
+      push_epoch[lane] = p.push.idx >= 0 ? (0x80000000u | (__ldcg(p.push.step) << 8) | (unsigned)p.push.idx)
+                                         : __ldcg(p.push.epochs + lane) + 1u;
     if (lane < p.m) {
       const __half* src = p.x + (size_t)lane * p.x_stride + (size_t)bb * 128;
       ptx::tma_bulk_g2s(ptx::smem_u32(x_s + (size_t)lane * xstride), src, row_bytes, bar);

@@ -44,6 +44,26 @@ struct PushTarget {
   int world, rank;
   size_t recv_offset;      // byte offset, inside every buffer, of this rank's receive region of the slot (row 0)
   const unsigned* epochs;  // local header: epoch of the last finished reduction per batch row
+  // Step numbering (idx >= 0): the epoch is 2^31 | step << 8 | idx, with `step` a counter in the local header
+  // that one small launch advances at the start of a decode step and nothing changes during it, and idx the
+  // number of the reduction inside the step.  No kernel has to advance an epoch, so the receiving side can
+  // be any kernel: the reduction kernel, or the GEMV that consumes the sum (CollectSource).
+  const unsigned* step;
+  int idx;
+};
+// The other half of that exchange inside a GEMV (norm build): the addend of the fused residual add is the sum
+// over the ranks of a row-parallel linear's partials, collected from this rank's own buffer while the
+// activations are staged: the own partial (plain fp16) and, per peer, the {data, epoch} words it sent.
+struct CollectSource {
+  const char* local;       // this rank's symmetric buffer (null: no collection; the addend is MmaParams::norm_r)
+  size_t own_offset;       // the slot's own partial
+  size_t recv_offset;      // the slot's receive region of source rank 0
+  size_t region_bytes;     // bytes between the receive regions of consecutive source ranks
+  int world, rank;
+  const unsigned* step;    // local header: step counter
+  unsigned idx;            // number of the reduction inside the step
+  unsigned long long timeout_ns;   // bound of every wait; when it runs out `status` is set and the kernel goes on
+  unsigned* status;
 };
 struct MmaParams {
   const uint4* qw;
@@ -80,6 +100,7 @@ struct MmaParams {
   __half* norm_out;      // [m, k] updated residual stream, or null
   const __half* norm_w;  // [k] norm weight
   float norm_eps;
+  CollectSource collect; // norm build: the addend comes from the peers (norm_r is then unused)
 };
 // CTAs of the mma.sync GEMV of up to this many threads run the 96-register build (five per SM)
 constexpr int kMmaSmallBlock = 128;
@@ -93,6 +114,8 @@ namespace qfb {
 // Where a row-parallel GEMV that feeds data slot `slot` of a communicator must send its [rows, d] partial
 // (`t`), and the local plain-fp16 copy it must write as its output (`own_slot`).  A status code.
 int comm_push_target(const qfb_comm* c, int slot, int rows, int d, PushTarget* t, void** own_slot);
+// Where a GEMV that consumes the sum of data slot `slot` finds the partials (reduction `idx` of the step).
+int comm_collect_source(const qfb_comm* c, int slot, int idx, int rows, int d, CollectSource* s);
 cudaError_t launch_gemv_mma(const MmaParams& p, int bits, int nt, dim3 grid, int block, size_t smem, bool pdl,
                             cudaStream_t st);
 

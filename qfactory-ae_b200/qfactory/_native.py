@@ -31,7 +31,9 @@ EXPORTS = (
     "qfb_rmsnorm", "qfb_add_rmsnorm", "qfb_silu_mul", "qfb_rope_cache", "qfb_quantize", "qfb_decode_attention", "qfb_decode_attention_rope",
     "qfb_comm_buffer_bytes", "qfb_comm_max_rows", "qfb_comm_alloc", "qfb_comm_free", "qfb_comm_open", "qfb_comm_close",
     "qfb_comm_create", "qfb_comm_destroy", "qfb_comm_set_timeout_us", "qfb_comm_slot", "qfb_comm_region", "qfb_comm_epoch",
-    "qfb_allreduce_add_rmsnorm", "qfb_allreduce_add_rmsnorm_pushed", "qfb_linear_forward_reduce", "qfb_linear_addnorm_forward",
+    "qfb_allreduce_add_rmsnorm", "qfb_allreduce_add_rmsnorm_pushed", "qfb_linear_forward_reduce", "qfb_linear_addnorm_forward", "qfb_comm_step_begin", "qfb_linear_forward_reduce_step",
+    "qfb_linear_silu_mul_forward_reduce_step", "qfb_linear_collect_addnorm_forward", "qfb_allreduce_add_rmsnorm_step",
+    "qfb_linear_addnorm_supported",
     "qfb_linear_silu_mul_forward_reduce", "qfb_comm_read_status", "qfb_comm_last_cuda_error",
 )
 
@@ -160,6 +162,18 @@ def lib() -> ctypes.CDLL:
     L.qfb_allreduce_add_rmsnorm.argtypes = [vp, i32, vp, vp, vp, i32, i32, ctypes.c_float, vp]
     L.qfb_allreduce_add_rmsnorm_pushed.restype = i32
     L.qfb_allreduce_add_rmsnorm_pushed.argtypes = [vp, i32, vp, vp, vp, i32, i32, ctypes.c_float, vp]
+    L.qfb_comm_step_begin.restype = i32
+    L.qfb_comm_step_begin.argtypes = [vp, vp]
+    L.qfb_linear_forward_reduce_step.restype = i32
+    L.qfb_linear_forward_reduce_step.argtypes = [LP, vp, i32, vp, i32, i32, vp, sz, u32, vp]
+    L.qfb_linear_silu_mul_forward_reduce_step.restype = i32
+    L.qfb_linear_silu_mul_forward_reduce_step.argtypes = [LP, vp, i32, vp, i32, i32, vp, sz, u32, vp]
+    L.qfb_linear_collect_addnorm_forward.restype = i32
+    L.qfb_linear_collect_addnorm_forward.argtypes = [LP, vp, i32, i32, vp, vp, vp, ctypes.c_float, i32, vp, vp, sz, u32, vp]
+    L.qfb_allreduce_add_rmsnorm_step.restype = i32
+    L.qfb_allreduce_add_rmsnorm_step.argtypes = [vp, i32, i32, vp, vp, vp, i32, i32, ctypes.c_float, vp]
+    L.qfb_linear_addnorm_supported.restype = i32
+    L.qfb_linear_addnorm_supported.argtypes = [LP, i32]
     L.qfb_linear_addnorm_forward.restype = i32
     L.qfb_linear_addnorm_forward.argtypes = [LP, vp, vp, vp, vp, ctypes.c_float, i32, vp, vp, sz, u32, vp]
     L.qfb_linear_forward_reduce.restype = i32

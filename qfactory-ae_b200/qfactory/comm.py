@@ -148,7 +148,52 @@ class PeerComm:
     def fits(self, rows: int, d: int) -> bool:
         return d == self.d and 0 < rows <= self.slot_rows
 
-    def linear_into_slot(self, layer, x, which, rows, silu_mul=False, push=True) -> bool:
+    # -- step numbering: the exchange whose receiving side may be the GEMV that consumes the sum -------------
+    def step_begin(self) -> None:
+        """Advance the step counter (one tiny launch; every rank, once per decode step, before its first
+        reduction).  Reduction `idx` of the step then carries the epoch 2^31 | step << 8 | idx."""
+        _native.check(self._lib.qfb_comm_step_begin(self._h, torch.cuda.current_stream(self.device).cuda_stream),
+                      "qfb_comm_step_begin")
+
+    def step_epoch(self, idx: int) -> int:
+        """The epoch reduction `idx` of the current step uses (synchronises; tests)."""
+        torch.cuda.synchronize(self.device)
+        words = torch.as_tensor(_DevView(self.bases[self.rank], (1, 512), self), device=self.device).view(torch.int32)
+        return (0x80000000 | ((int(words[0, 65]) & 0x7FFFFF) << 8) | idx) & 0xFFFFFFFF
+
+    def collect_norm_linear(self, layer, which, idx, x, x_out, norm_weight, rows, eps=1e-5, out=None):
+        """y = (rmsnorm(x + sum over the ranks of slot `which`) * norm_weight) @ dequant(W)^T in ONE kernel: the
+        GEMV collects the partials (its own from the slot, the peers' from what they sent for reduction `idx`
+        of this step) while it stages its activations; x + sum goes to `x_out` (another buffer than `x`)."""
+        if out is None:
+            out = torch.empty(rows, layer.out_features, dtype=torch.float16, device=self.device)
+        if layer._desc is None:
+            layer._prepare()
+        st = self._lib.qfb_linear_collect_addnorm_forward(
+            layer._desc_ref, self._h, which, idx, x.data_ptr(), None if x_out is None else x_out.data_ptr(),
+            norm_weight.data_ptr(), float(eps), rows, out.data_ptr(), layer._ws_ptr, layer._ws_bytes, layer.flags,
+            torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(st, "qfb_linear_collect_addnorm_forward")
+        return out
+
+    def collect_supported(self, sender, receiver, rows: int) -> bool:
+        """True when `sender` (a row-parallel layer) can send its partial itself and `receiver` (the layer that
+        consumes the normed sum; None: the reduction kernel) can collect it, for `rows` batch rows."""
+        from . import layout as _layout
+
+        def ok4(l):
+            return l.packed_layout == _layout.LAYOUT_FRAGMENT and l.n_bits == 4 and l.group_size != 64
+        if not (0 < rows <= 16 and ok4(sender) and sender.out_features == self.d and self.d % 128 == 0):
+            return False
+        if receiver is None:
+            return True
+        if not (ok4(receiver) and receiver.in_features == self.d):
+            return False
+        if receiver._desc is None:
+            receiver._prepare()
+        return bool(self._lib.qfb_linear_addnorm_supported(receiver._desc_ref, rows))
+
+    def linear_into_slot(self, layer, x, which, rows, silu_mul=False, push=True, idx=None) -> bool:
         """Run the row-parallel `layer` on `x` ([rows, k], or the fused gate/up tensor [rows, 2k] with
         `silu_mul`) with data slot `which` as its output.  Returns True when the kernel also sent the
         partial to the peers while storing it (one launch for the linear and the first half of the
@@ -162,26 +207,41 @@ class PeerComm:
             x2 = x.reshape(rows, -1)
             if not x2.is_contiguous():
                 x2 = x2.contiguous()
-            fn = self._lib.qfb_linear_silu_mul_forward_reduce if silu_mul else self._lib.qfb_linear_forward_reduce
             if (not silu_mul) or layer.silu_mul_supported(rows):
-                st = fn(layer._desc_ref, x2.data_ptr(), rows, self._h, which, layer._ws_ptr, layer._ws_bytes, layer.flags,
-                        torch.cuda.current_stream(self.device).cuda_stream)
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+                if idx is None:
+                    fn = self._lib.qfb_linear_silu_mul_forward_reduce if silu_mul else self._lib.qfb_linear_forward_reduce
+                    st = fn(layer._desc_ref, x2.data_ptr(), rows, self._h, which, layer._ws_ptr, layer._ws_bytes, layer.flags, stream)
+                else:   # step numbering: the receiver waits for exactly this epoch, so there is no fallback
+                    fn = (self._lib.qfb_linear_silu_mul_forward_reduce_step if silu_mul
+                          else self._lib.qfb_linear_forward_reduce_step)
+                    st = fn(layer._desc_ref, x2.data_ptr(), rows, self._h, which, idx, layer._ws_ptr, layer._ws_bytes,
+                            layer.flags, stream)
+                    _native.check(st, "qfb_linear_forward_reduce_step")
                 if st == 0:
                     return True
                 if st != 3:   # QFB_ERR_UNSUPPORTED: fall through to the two-step form
                     _native.check(st, "qfb_linear_forward_reduce")
+        assert idx is None, "a step-numbered reduction needs the sending GEMV (collect_supported says when it serves)"
         if silu_mul:
             layer.forward_silu_mul(x, out=self.slot(which, rows))
         else:
             layer(x, out=self.slot(which, rows))
         return False
 
-    def allreduce_add_rmsnorm(self, which, x, weight, rows, eps=1e-5, out=None, pushed=False):
+    def allreduce_add_rmsnorm(self, which, x, weight, rows, eps=1e-5, out=None, pushed=False, idx=None):
         """Sum slot `which` over the ranks; `x` (fp16 [rows, d], may be None) += the sum in place;
         returns the RMS norm of the row with `weight` (or the row itself when `weight` is None).
         `pushed`: the partial was already sent to the peers (`linear_into_slot` returned True)."""
         if out is None:
             out = torch.empty(rows, self.d, dtype=torch.float16, device=self.device)
+        if idx is not None:   # step numbering: collects what the sending GEMVs stamped with reduction `idx` of this step
+            st = self._lib.qfb_allreduce_add_rmsnorm_step(
+                self._h, which, idx, None if x is None else x.data_ptr(), None if weight is None else weight.data_ptr(),
+                out.data_ptr(), rows, self.d, eps, torch.cuda.current_stream(self.device).cuda_stream)
+            if st != 0:
+                _native.check(st, "qfb_allreduce_add_rmsnorm_step")
+            return out
         fn = self._lib.qfb_allreduce_add_rmsnorm_pushed if pushed else self._lib.qfb_allreduce_add_rmsnorm
         st = fn(
             self._h, which, None if x is None else x.data_ptr(), None if weight is None else weight.data_ptr(),
@@ -216,6 +276,9 @@ class PeerComm:
         ptr = self._lib.qfb_comm_region(self._h, which, r)
         words = torch.as_tensor(_DevView(ptr, (self.slot_rows, 2 * self.d), self), device=self.device).view(torch.int32)
         data = partial.contiguous().view(torch.int32)                      # [rows, d / 2]
+        epoch &= 0xFFFFFFFF
+        if epoch >= 1 << 31:
+            epoch -= 1 << 32                                              # the same 32 bits as a signed word
         packed = torch.stack((data, torch.full_like(data, epoch)), dim=-1).reshape(rows, self.d)
         words[:rows].copy_(packed)
 

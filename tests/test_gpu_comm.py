@@ -202,3 +202,122 @@ def test_layers_the_sending_gemv_does_not_serve_fall_back_to_two_steps():
         assert torch.equal(comm.slot(0, M), want)
     finally:
         comm.close()
+
+
+# ---- step numbering: the receiving side inside the GEMV that consumes the sum ------------------------
+def _sum_ref(parts):
+    s = torch.zeros_like(parts[0], dtype=torch.float32)
+    for p in parts:
+        s = s + p.float()
+    return s.half()
+
+
+@pytest.mark.parametrize("world,rank", [(2, 0), (4, 3), (8, 5)])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_gemv_collects_the_partials_adds_and_norms_while_staging(world, rank, M):
+    """`qfb_linear_collect_addnorm_forward`: own partial from the slot, the peers' from the words they sent
+    (written by hand here) for reduction idx of the current step; the new residual stream is bit-identical to
+    sum-in-rank-order + one fp16 add, the output agrees with norm-then-linear within one rounding."""
+    from oracle import qf_oracle as O
+    from qfactory import QLinear
+
+    N, K = 640, 2048
+    x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=900 + M + world)
+    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="fragment")
+    comm = PeerComm.local_emulation(rank, world, K, 16)
+    g = torch.Generator(device="cuda").manual_seed(world * 10 + M)
+    try:
+        resid = x.cuda()
+        w = (torch.rand(K, generator=g, device="cuda") + 0.5).half()
+        for step in range(2):
+            comm.step_begin()
+            for idx, slot in ((4, 0), (5, 1), (250, 0)):
+                assert comm.collect_supported(layer, layer, M) in (True, False)
+                ep = comm.step_epoch(idx)
+                parts = [torch.randn(M, K, generator=g, device="cuda").half() for _ in range(world)]
+                comm.slot(slot, M).copy_(parts[rank])
+                for r in range(world):
+                    if r != rank:
+                        comm.write_peer_partial(r, slot, parts[r], epoch=ep)
+                x_out = torch.full_like(resid, float("nan"))
+                y = comm.collect_norm_linear(layer, slot, idx, resid, x_out, w, M)
+                torch.cuda.synchronize()
+                want_x = resid + _sum_ref(parts)
+                assert torch.equal(x_out, want_x)
+                f = want_x.float()
+                h = (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + 1e-5)).half() * w
+                y_ref = layer(h)
+                assert float((y.float() - y_ref.float()).abs().max()) <= 3e-3 * float(y_ref.float().abs().max())
+                assert comm.read_status() == 0
+                resid = want_x
+    finally:
+        comm.close()
+
+
+def test_step_numbered_sender_and_reduction_kernel():
+    """The sending GEMV stamps reduction idx of the current step; the collecting reduction kernel accepts
+    exactly that epoch and advances nothing."""
+    from oracle import qf_oracle as O
+    from qfactory import QLinear
+
+    M, N, K, rank, world = 3, 1024, 2048, 1, 4
+    x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=77)
+    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="fragment")
+    xs = x.cuda()
+    want = layer(xs).clone()
+    comm = PeerComm.local_emulation(rank, world, N, 16)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    try:
+        before = comm.next_epoch()
+        comm.step_begin()
+        for idx, slot in ((0, 0), (1, 1), (2, 0)):
+            ep = comm.step_epoch(idx)
+            assert comm.linear_into_slot(layer, xs, slot, M, idx=idx) is True
+            torch.cuda.synchronize()
+            for r in range(world):
+                if r != rank:
+                    words = comm.peer_words(r, slot, rank, M)
+                    assert torch.equal(words[:, 0::2], want.view(torch.int32))
+                    assert bool(((words[:, 1::2].to(torch.int64) & 0xFFFFFFFF) == ep).all())
+            parts = [want if r == rank else torch.randn(M, N, generator=g, device="cuda").half() for r in range(world)]
+            for r in range(world):
+                if r != rank:
+                    comm.write_peer_partial(r, slot, parts[r], epoch=ep)
+            resid = torch.randn(M, N, generator=g, device="cuda").half()
+            w = (torch.rand(N, generator=g, device="cuda") + 0.5).half()
+            want_x, want_h = _reference(parts, resid, w)
+            h = comm.allreduce_add_rmsnorm(slot, resid, w, M, idx=idx)
+            torch.cuda.synchronize()
+            assert torch.equal(resid, want_x)
+            assert (h.float() - want_h.float()).abs().max() <= 2e-3 * want_h.float().abs().max()
+        assert comm.next_epoch() == before and comm.read_status() == 0     # the per-row epochs did not move
+    finally:
+        comm.close()
+
+
+def test_collecting_gemv_gives_up_on_words_that_never_come():
+    from oracle import qf_oracle as O
+    from qfactory import QLinear
+
+    M, N, K = 2, 256, 1024
+    x, q, s, z = O.make_case(M, N, K, 4, 128, False, seed=5)
+    layer = QLinear.init(M, K, N, 4, q.cuda(), 128, s.cuda(), z.cuda(), layout="fragment")
+    comm = PeerComm.local_emulation(0, 2, K, 8)
+    try:
+        comm.set_timeout_us(100)                                  # nothing writes the peer's words
+        comm.step_begin()
+        w = torch.ones(K, dtype=torch.float16, device="cuda")
+        comm.slot(0, M).zero_()
+        comm.collect_norm_linear(layer, 0, 0, x.cuda(), None, w, M)
+        torch.cuda.synchronize()                                  # the launch ended by itself
+        assert comm.read_status() == 8                            # QFB_ERR_DEVICE_FLAG
+        ep = comm.step_epoch(1)
+        part = torch.randn(M, K, device="cuda").half()
+        comm.slot(1, M).copy_(part)
+        comm.write_peer_partial(1, 1, part, epoch=ep)
+        x_out = torch.empty(M, K, dtype=torch.float16, device="cuda")
+        comm.collect_norm_linear(layer, 1, 1, x.cuda(), x_out, w, M)
+        torch.cuda.synchronize()
+        assert torch.equal(x_out, x.cuda() + (part.float() * 2).half()) and comm.read_status() == 0
+    finally:
+        comm.close()
