@@ -133,6 +133,14 @@ class QuantDecoder(torch.nn.Module):
         # linear's weight prefetch (programmatic dependent launch), and the fused staging was measured 2 % slower
         # per token (9.23 against 9.05 ms); it pays where launches are issued one by one.
         self.fuse_norm = False
+        # True (tensor-parallel decode steps): no reduction kernel between a row-parallel linear and the linear that
+        # consumes its sum: O / down send their partials themselves, and gate+up / the next QKV collect them, add
+        # them to the residual stream and apply the norm while they stage their activations (step-numbered
+        # epochs, PeerComm.step_begin).  Only the last reduction of a step (final norm) is a launch of its own.
+        # Off: measured 10 % slower per token at two ranks (6.49 against 5.84-5.90 ms): every CTA of the consuming
+        # GEMV polls and sums its slice (the work of one small kernel repeated per row tile, on the GEMV's own
+        # latency chain), which costs more than the launch it saves.
+        self.fuse_collect = False
         assert cfg.n_kv_heads % world == 0 and cfg.d_ff % (world * cfg.group_size) == 0
         assert weights in ("packed", "seeded", "seeded_keep") and collective in ("auto", "nccl", "none")
         self.cfg, self.world, self.rank, self.batch = cfg, world, rank, batch
@@ -239,10 +247,24 @@ class QuantDecoder(torch.nn.Module):
         pending = None   # output of the previous down projection, not yet added to the residual stream
         h = None         # fused path: the normed input of the next layer, made by the reduction kernel
         nblk = len(self.blocks)
-        # without the communicator the residual stream lives in two buffers used in turn (see _norm_linear)
-        cur, spare = x2, (None if fused else torch.empty_like(x2))
+        # the collecting form of the communicator path: every reduction of the step but the last is received by the
+        # GEMV that consumes it
+        blk0 = self.blocks[0]
+        collect = (fused and self.fuse_collect and self.fuse_push and T == 1 and 2 * nblk <= 256
+                   and self.comm.collect_supported(blk0.o, blk0.gate_up, R) and self.comm.collect_supported(blk0.down, blk0.qkv, R)
+                   and (not self.fuse_silu or blk0.down.silu_mul_supported(R)))
+        if collect:
+            self.comm.step_begin()
+        # without the reduction kernel the residual stream lives in two buffers used in turn (see _norm_linear)
+        cur, spare = x2, (torch.empty_like(x2) if (collect or not fused) else None)
         for li, blk in enumerate(self.blocks):
-            if fused:
+            if collect:
+                if li == 0:
+                    qkv2d = blk.qkv(self._rms(x2, blk.norm1))
+                else:   # residual += sum of the previous down projection's partials (slot 1), norm 1, QKV: one launch
+                    qkv2d = self.comm.collect_norm_linear(blk.qkv, 1, 2 * li - 1, cur, spare, blk.norm1, R)
+                    cur, spare = spare, cur
+            elif fused:
                 if h is None:
                     h = self._rms(x2, blk.norm1)          # first layer; afterwards the reduction kernel makes it
                 qkv2d = blk.qkv(h.view(R, -1))
@@ -271,7 +293,12 @@ class QuantDecoder(torch.nn.Module):
                     att = F.scaled_dot_product_attention(q.transpose(1, 2), self.k_cache[li], self.v_cache[li],
                                                          attn_mask=mask[None, None], enable_gqa=True)   # [B, hq, T, hd]
                     att2d = att.transpose(1, 2).reshape(R, -1)
-            if fused:
+            if collect:
+                # O sends its partial (reduction 2 li, slot 0); gate+up collects it: residual += sum, norm 2, gate/up
+                self.comm.linear_into_slot(blk.o, att2d, 0, R, idx=2 * li)
+                gu = self.comm.collect_norm_linear(blk.gate_up, 0, 2 * li, cur, spare, blk.norm2, R)
+                cur, spare = spare, cur
+            elif fused:
                 # row parallel: the partial goes straight into the communicator's slot; ONE launch then
                 # sums it over the ranks, adds it to the residual stream and applies the next norm
                 pushed = self.comm.linear_into_slot(blk.o, att2d, 0, R, push=self.fuse_push)
@@ -290,7 +317,13 @@ class QuantDecoder(torch.nn.Module):
             else:
                 act = ops.silu_mul(gu) if self.native_ops else F.silu(gu[:, :half]) * gu[:, half:]
                 down = lambda out=None: blk.down(act, out=out)
-            if fused:
+            if collect:
+                # down sends its partial (reduction 2 li + 1, slot 1); the next layer's QKV collects it, or, after
+                # the last layer, the reduction kernel with the final norm
+                self.comm.linear_into_slot(blk.down, gu if fuse_act else act, 1, R, silu_mul=fuse_act, idx=2 * li + 1)
+                if li + 1 == nblk:
+                    h = self.comm.allreduce_add_rmsnorm(1, cur, self.final_norm, R, idx=2 * li + 1)
+            elif fused:
                 pushed = self.comm.linear_into_slot(blk.down, gu if fuse_act else act, 1, R, silu_mul=fuse_act,
                                                     push=self.fuse_push)
                 last = li + 1 == nblk

@@ -87,11 +87,16 @@ def _worker(rank, world, port, ret):
         tp = QuantDecoder(cfg, world=world, rank=rank, device=dev, seed=11, batch=2, weights="seeded")
         got = teacher_forced_logits(tp, toks, prompt_len=80).float()
         fused = tp.comm is not None
+        # the same steps with the reductions received inside the consuming GEMVs (step-numbered exchange)
+        tp.fuse_collect = True
+        got_c = teacher_forced_logits(tp, toks, prompt_len=80).float()
+        status_c = tp.comm.read_status() if tp.comm is not None else -1
         tp.close()
         one = QuantDecoder(cfg, world=1, rank=0, device=dev, seed=11, batch=2, weights="seeded")
         want = teacher_forced_logits(one, toks, prompt_len=80).float()
         rel = float((got - want).abs().max() / want.abs().max())
-        ret[rank] = (ok, status, rel, fused)
+        rel_c = float((got_c - want).abs().max() / want.abs().max())
+        ret[rank] = (ok, status, rel, fused, rel_c, status_c)
     finally:
         dist.destroy_process_group()
 
@@ -111,7 +116,8 @@ def test_peer_memory_allreduce_and_tensor_parallel_decoder_between_real_ranks():
         p.join(300)
         assert p.exitcode == 0
     for r in range(world):
-        ok, status, rel, fused = ret[r]
+        ok, status, rel, fused, rel_c, status_c = ret[r]
         assert ok and status == 0
         assert fused, "the peer buffers could not be mapped: the decoder fell back to NCCL"
         assert rel <= 2e-2
+        assert rel_c <= 2e-2 and status_c == 0
