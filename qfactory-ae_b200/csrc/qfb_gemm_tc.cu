@@ -314,7 +314,9 @@ __device__ __forceinline__ void splitk_reduce(const float* base0, size_t sstride
 
 // FRAG = the layer is in the fragment layout (a build of its own: with both decoders behind a run-time branch in
 // the decode loop the compiler allots registers for the larger of the two)
-template <int BITS, int NB, bool POST, int DG, bool FRAG>
+// ASYM = the layer has scales AND zero points (the common case; a build of its own for the same reason; used
+// where the scale is applied in the decode)
+template <int BITS, int NB, bool POST, int DG, bool FRAG, bool ASYM>
 __global__ void __launch_bounds__(TcCfg<BITS, NB, POST, DG>::kThreads, (TcCfg<BITS, NB, POST, DG>::kTwoPerSM ? 2 : 1))
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
@@ -393,8 +395,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const TcParams p) {
   const long long wait_limit = p.stall_test ? 200000LL : kWaitLimitCycles;
   grid_launch_dependents();
 
-  const bool has_z = p.qz != nullptr;
-  const bool has_s = p.qs != nullptr;
+  const bool has_z = ASYM || p.qz != nullptr;
+  const bool has_s = ASYM || p.qs != nullptr;
 
   if (warp == 0) {
     // ------------------------------ weight producer ---------------------------
@@ -669,7 +671,12 @@ static cudaError_t launch_cfg(const CUtensorMap& tm, const TcParams& p, dim3 gri
 template <int BITS, int NB, bool POST, int DG, bool FRAG>
 static cudaError_t launch_cfg_layout(const CUtensorMap& tm, const TcParams& p, dim3 grid, bool pdl, cudaStream_t st) {
   using Cfg = TcCfg<BITS, NB, POST, DG>;
-  auto kern = qgemm_tc_kernel<BITS, NB, POST, DG, FRAG>;
+  auto kern = qgemm_tc_kernel<BITS, NB, POST, DG, FRAG, false>;
+  // scale-in-the-decode mode: the common case of scales and zero points present has a build of its own (measured:
+  // 2-6 % faster from 64 rows up; with per-stage accumulators the same specialisation was 3 % slower, not used)
+  if constexpr (!POST) {
+    if (p.qz && p.qs) kern = qgemm_tc_kernel<BITS, NB, POST, DG, FRAG, true>;
+  }
   // the attribute belongs to the (function, device) pair: set it on every launch, it is cheap
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes);
   if (e != cudaSuccess) return e;
