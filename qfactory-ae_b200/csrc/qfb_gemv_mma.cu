@@ -170,7 +170,9 @@ template <int RB> struct ScaleZero {
 //         meet where the partial results meet (in the cluster, or in the one CTA of an unsplit tile), and
 //         1 / rms, a scalar per batch row, is applied to the result instead of to every activation.  A
 //         build of its own; launched with in-cluster reduction or no split only.
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM>
+// ASYM  = the layer is known to have scales and zero points (the common case: their null checks and the
+//         symmetric / group-less fold leave the loop)
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM, bool ASYM>
 __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
@@ -482,9 +484,9 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) {
           float2 sf = make_float2(1.f, 1.f);
-          if (p.qs) sf = __half22float2(as_h2(sz_cur.s[rb]));
+          if (ASYM || p.qs) sf = __half22float2(as_h2(sz_cur.s[rb]));
           float z0 = zc, z1 = zc;
-          if (p.qz) {
+          if (ASYM || p.qz) {
             const uint32_t zb = sz_cur.z[rb >> 1] >> ((rb & 1) * 16);
             z0 = (float)(zb & 0xffu);
             z1 = (float)((zb >> 8) & 0xffu);
@@ -727,21 +729,28 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // either way).  Tighter budgets that would leave room for the next launch's CTAs to become
 // resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
 // k-step loop and were 5-70 % slower on every Llama-7B layer shape.
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM>(p);
 }
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false>
 __global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM>(p);
 }
 
 template <int BITS, int NT, int RB, bool SEG64>
 static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t smem, bool pdl, cudaStream_t st) {
   auto kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64> : gemv_mma_kernel<BITS, NT, RB, SEG64>;
-  if (!p.act && (p.cluster || grid.x == 1) && !p.push.world)
+  if (!p.act && (p.cluster || grid.x == 1) && !p.push.world) {
     kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true>
                                    : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true>;
+    // (measured: 1-2 % faster with one batch tile, 2-5 % slower with two, where it is not used)
+    if constexpr (NT == 1) {
+      if (p.qs && p.qz)
+        kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, true>
+                                       : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, true>;
+    }
+  }
   if (p.norm_w) {
     // the build with the fused residual add + RMS norm: the same layers, in-cluster reduction or no split
     if (p.push.world || p.act || !(p.cluster || grid.x == 1)) return cudaErrorInvalidValue;
