@@ -172,7 +172,10 @@ template <int RB> struct ScaleZero {
 //         build of its own; launched with in-cluster reduction or no split only.
 // ASYM  = the layer is known to have scales and zero points (the common case: their null checks and the
 //         symmetric / group-less fold leave the loop)
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM, bool ASYM>
+// ONE   = one activation row (m = 1; a lean build with scales and zero points): the threads fetch the slice with
+//         plain loads and sum it on the way in (one barrier and one pass less than the bulk copy + all-ones MMA
+//         that serve every m), and only batch column 0 is folded and reduced
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM, bool ASYM, bool ONE>
 __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   using FC = FragCodec<BITS>;
   constexpr int KS = SEG64 ? 4 : 8;    // k-steps per segment
@@ -256,6 +259,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   // and the up slices arrive by one bulk copy each and are combined in shared memory, with the
   // arithmetic of the stand-alone kernel (silu in fp32 rounded to fp16, then one fp16 product).
   __half* u_s = reinterpret_cast<__half*>(reinterpret_cast<char*>(smem) + p.act_offset);
+  constexpr bool direct = ONE;
   if (NORM) {
     // x + r (one fp16 addition, as the stand-alone kernel), written back by the CTAs of tile 0 (whose K splits
     // cover the row once), times the norm weight (one fp16 product) into the slice; squares summed in fp32 per
@@ -340,6 +344,42 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       for (int o = 16; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
       if (lane == 0) nss_warp[warp][r] = ss[r];
     }
+  } else if (direct) {
+    // one activation row: every thread fetches 16 bytes of the slice itself, stores them and adds them up; the 16
+    // (8) lanes that hold a 128-k (64-k) segment combine their sums with shuffles and one of them writes the
+    // segment's sum.  One barrier instead of two and no pass over the staged slice.
+    constexpr int SEGL = SEG64 ? 8 : 16;  // lanes (16-byte vectors) per segment
+    const int nvec = ncta * 16;
+    float* xs_sum = reinterpret_cast<float*>(x_s + xstride);
+    const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)bb * 128);
+    if (PUSH && tid == 0)
+      push_epoch[0] = p.push.idx >= 0 ? (0x80000000u | (__ldcg(p.push.step) << 8) | (unsigned)p.push.idx)
+                                      : __ldcg(p.push.epochs) + 1u;
+    for (int base = 0; base < nvec; base += (int)blockDim.x) {  // (nvec is a multiple of 16: a segment's lanes agree)
+      const int j = base + tid;
+      uint4 v = j < nvec ? __ldcg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+      if (!LEAN && p.act) {  // silu(gate) * up, the arithmetic of the pass over the staged slices below
+        const uint4 up = j < nvec ? __ldcg(src + (p.k >> 3) + j) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t ua[4] = {v.x, v.y, v.z, v.w}, ub[4] = {up.x, up.y, up.z, up.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(as_h2(ua[q]));
+          const __half2 sg = __floats2half2_rn(f.x / (1.f + __expf(-f.x)), f.y / (1.f + __expf(-f.y)));
+          o[q] = as_u32(__hmul2(sg, as_h2(ub[q])));
+        }
+        v = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      const float2 f0 = __half22float2(as_h2(v.x)), f1 = __half22float2(as_h2(v.y));
+      const float2 f2 = __half22float2(as_h2(v.z)), f3 = __half22float2(as_h2(v.w));
+      float sum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+      for (int o = SEGL / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (j < nvec) {
+        *(reinterpret_cast<uint4*>(x_s) + j) = v;
+        if ((j & (SEGL - 1)) == 0) xs_sum[(j / SEGL) * (8 * NT)] = sum;
+      }
+    }
   } else if (warp == 0) {
     const uint32_t bar = ptx::smem_u32(&xbar);
     const uint32_t row_bytes = (uint32_t)ncta * 256u;
@@ -364,7 +404,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       atomicExch(p.status, 1u);
   }
   __syncthreads();
-  if (!LEAN && p.act) {
+  if (!LEAN && !direct && p.act) {
     const int vec_row = ncta * 16;  // 16-byte vectors per row of the slice
     for (int i = tid; i < p.m * vec_row; i += blockDim.x) {
       const int r = i / vec_row, j = i - r * vec_row;
@@ -392,7 +432,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
   // ---- sum of the activations over every segment of the slice: an MMA whose A fragment is all
   // ones yields, in every row, the column sums of the B fragment.  The warps share the segments.
   float* xsum_s = reinterpret_cast<float*>(x_s + (size_t)p.m * xstride);  // [segments][8 * NT]
-  {
+  if (!direct) {
     const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};  // fp16 1.0
     const int nwarps = blockDim.x >> 5;
     // two segments per pass and two accumulators per segment (even / odd k-steps): independent
@@ -426,8 +466,8 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
         }
       }
     }
+    __syncthreads();
   }
-  __syncthreads();
 
   float acc[RB][NT][4];
 #pragma unroll
@@ -497,9 +537,11 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             acc[rb][nt][0] = fmaf(b0, dx[nt][0], fmaf(a0, d[rb][nt][0], acc[rb][nt][0]));
-            acc[rb][nt][1] = fmaf(b0, dx[nt][1], fmaf(a0, d[rb][nt][1], acc[rb][nt][1]));
             acc[rb][nt][2] = fmaf(b1, dx[nt][0], fmaf(a1, d[rb][nt][2], acc[rb][nt][2]));
-            acc[rb][nt][3] = fmaf(b1, dx[nt][1], fmaf(a1, d[rb][nt][3], acc[rb][nt][3]));
+            if (!ONE) {  // (one activation row: only batch column 0 is stored)
+              acc[rb][nt][1] = fmaf(b0, dx[nt][1], fmaf(a0, d[rb][nt][1], acc[rb][nt][1]));
+              acc[rb][nt][3] = fmaf(b1, dx[nt][1], fmaf(a1, d[rb][nt][3], acc[rb][nt][3]));
+            }
           }
         }
         if (++gpos == segs_per_group) {  // the next segment starts a new group
@@ -523,6 +565,7 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
       for (int i = 0; i < 4; ++i) {
         const int mm = nt * 8 + 2 * t + (i & 1);
         const int r = wt * 64 + (sub * RB + rb) * 16 + (i >> 1) * 8 + g;
+        if (ONE && (i & 1)) continue;
         if (mm < p.m) red[(kw * p.m + mm) * kRedStride + r] = acc[rb][nt][i];
       }
   __syncthreads();
@@ -729,13 +772,15 @@ __device__ __forceinline__ void gemv_mma_body(const MmaParams& p) {
 // either way).  Tighter budgets that would leave room for the next launch's CTAs to become
 // resident early (three CTAs of 256 threads at 80 registers, six of 128 at 80) spill inside the
 // k-step loop and were 5-70 % slower on every Llama-7B layer shape.
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false,
+          bool ONE = false>
 __global__ void __launch_bounds__(256, 2) gemv_mma_kernel(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM, ONE>(p);
 }
-template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false>
+template <int BITS, int NT, int RB, bool SEG64, bool PUSH = false, bool LEAN = false, bool NORM = false, bool ASYM = false,
+          bool ONE = false>
 __global__ void __launch_bounds__(128, 5) gemv_mma_kernel_small(const MmaParams p) {
-  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM>(p);
+  gemv_mma_body<BITS, NT, RB, SEG64, PUSH, LEAN, NORM, ASYM, ONE>(p);
 }
 
 template <int BITS, int NT, int RB, bool SEG64>
@@ -746,10 +791,21 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
                                    : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true>;
     // (measured: 1-2 % faster with one batch tile, 2-5 % slower with two, where it is not used)
     if constexpr (NT == 1) {
-      if (p.qs && p.qz)
+      if (p.qs && p.qz) {
         kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, true>
                                        : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, true>;
+        // one activation row (and no test of a copy that never lands, which needs the copy): its own build
+        if (p.m == 1 && !p.stall_test)
+          kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, true, true>
+                                         : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, true, true>;
+      }
     }
+  }
+  if constexpr (BITS == 4 && !SEG64 && NT == 1) {
+    // one activation row through the general build (fused activation, reduction through the workspace)
+    if (p.m == 1 && !p.stall_test && (p.act || !(p.cluster || grid.x == 1)))
+      kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, 1, RB, false, false, false, false, false, true>
+                                     : gemv_mma_kernel<4, 1, RB, false, false, false, false, false, true>;
   }
   if (p.norm_w) {
     // the build with the fused residual add + RMS norm: the same layers, in-cluster reduction or no split
@@ -762,10 +818,16 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
   }
   if (p.push.world) {
     // the sending build: 4-bit layers with groups of 128 and more (what the decoder's row-parallel layers are)
-    if constexpr (BITS == 4 && !SEG64)
+    if constexpr (BITS == 4 && !SEG64) {
       kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, NT, RB, false, true> : gemv_mma_kernel<4, NT, RB, false, true>;
-    else
+      if constexpr (NT == 1) {
+        if (p.m == 1 && !p.stall_test)
+          kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, 1, RB, false, true, false, false, false, true>
+                                         : gemv_mma_kernel<4, 1, RB, false, true, false, false, false, true>;
+      }
+    } else {
       return cudaErrorNotSupported;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
