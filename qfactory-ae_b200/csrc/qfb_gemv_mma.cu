@@ -172,7 +172,7 @@ template <int RB> struct ScaleZero {
 //         build of its own; launched with in-cluster reduction or no split only.
 // ASYM  = the layer is known to have scales and zero points (the common case: their null checks and the
 //         symmetric / group-less fold leave the loop)
-// ONE   = one activation row (m = 1; a lean build with scales and zero points): the threads fetch the slice with
+// ONE   = one activation row (m = 1): the threads fetch the slice with
 //         plain loads and sum it on the way in (one barrier and one pass less than the bulk copy + all-ones MMA
 //         that serve every m), and only batch column 0 is folded and reduced
 template <int BITS, int NT, int RB, bool SEG64, bool PUSH, bool LEAN, bool NORM, bool ASYM, bool ONE>
@@ -791,10 +791,13 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
                                    : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true>;
     // (measured: 1-2 % faster with one batch tile, 2-5 % slower with two, where it is not used)
     if constexpr (NT == 1) {
+      // one activation row (and no test of a copy that never lands, which needs the copy): its own build
+      if (p.m == 1 && !p.stall_test)
+        kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, false, true>
+                                       : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, false, true>;
       if (p.qs && p.qz) {
         kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, true>
                                        : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, true>;
-        // one activation row (and no test of a copy that never lands, which needs the copy): its own build
         if (p.m == 1 && !p.stall_test)
           kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, NT, RB, SEG64, false, true, false, true, true>
                                          : gemv_mma_kernel<BITS, NT, RB, SEG64, false, true, false, true, true>;
