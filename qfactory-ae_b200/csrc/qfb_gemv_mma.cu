@@ -804,11 +804,12 @@ static cudaError_t launch_cfg(const MmaParams& p, dim3 grid, int block, size_t s
       }
     }
   }
-  if constexpr (BITS == 4 && !SEG64 && NT == 1) {
-    // one activation row through the general build (fused activation, reduction through the workspace)
+  if constexpr (NT == 1) {
+    // one activation row through the general build (fused activation, reduction through the workspace): every
+    // path of one row sums its activations the same way, so they keep giving the same bits
     if (p.m == 1 && !p.stall_test && (p.act || !(p.cluster || grid.x == 1)))
-      kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<4, 1, RB, false, false, false, false, false, true>
-                                     : gemv_mma_kernel<4, 1, RB, false, false, false, false, false, true>;
+      kern = block <= kMmaSmallBlock ? gemv_mma_kernel_small<BITS, 1, RB, SEG64, false, false, false, false, true>
+                                     : gemv_mma_kernel<BITS, 1, RB, SEG64, false, false, false, false, true>;
   }
   if (p.norm_w) {
     // the build with the fused residual add + RMS norm: the same layers, in-cluster reduction or no split
